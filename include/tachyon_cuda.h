@@ -1,0 +1,120 @@
+/* tachyon_cuda.h: C ABI of the B200 (sm_100a) backend for Tachyon's Granite
+ * mixture-of-experts block.
+ *
+ * This is the interface a `src/gpu/cuda/mod.rs` in Tachyon binds with
+ * `extern "C"`, the way `src/gpu/mod.rs:115-145` binds the Metal shim
+ * (`src/gpu/shim.m`). Plain pointers and sizes only. One thread drives a
+ * context at a time (Tachyon's `Backend` is `Send`, not `Sync`:
+ * src/engine.rs:8, src/gpu/mod.rs:440-442), so nothing here locks.
+ *
+ * Status codes: 0 = ok, negative = failure; the message is kept per context
+ * and read with tc_last_error(). There is no CPU fallback: every entry point
+ * that computes runs CUDA kernels or fails.
+ */
+#ifndef TACHYON_CUDA_H
+#define TACHYON_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tc_ctx tc_ctx;
+typedef struct tc_matrix tc_matrix;
+typedef struct tc_moe_layer tc_moe_layer;
+typedef struct tc_graph tc_graph;
+
+/* Storage kinds of Tachyon's `Matrix` enum (src/weights.rs:58-79). */
+enum { TC_BF16 = 0, TC_Q8 = 1, TC_Q4 = 2 };
+
+/* ---- context: replaces tm_create / tm_destroy / tm_device_name
+ *      (src/gpu/mod.rs:116-124, src/gpu/shim.m:33-70). */
+tc_ctx *tc_create(int device_ordinal, char *err, size_t errlen);
+void tc_destroy(tc_ctx *ctx);
+void tc_device_name(tc_ctx *ctx, char *out, size_t len);
+/* Copies the context's last error message into `out`; returns its length. */
+size_t tc_last_error(tc_ctx *ctx, char *out, size_t len);
+/* Waits for the context's stream; also reports a kernel's bounded wait that
+ * ran out (replaces tm_end's error return, src/gpu/mod.rs:144, 1049-1053). */
+int tc_sync(tc_ctx *ctx);
+/* The context's stream as a cudaStream_t, for callers that enqueue their own work. */
+void *tc_stream(tc_ctx *ctx);
+
+/* ---- device buffers: replace tm_buffer / tm_buffer_contents / tm_buffer_free
+ *      (src/gpu/mod.rs:125-127). HBM is not host-visible, hence the copies. */
+void *tc_malloc(tc_ctx *ctx, size_t bytes);
+void tc_free(tc_ctx *ctx, void *dev);
+int tc_upload(tc_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int tc_download(tc_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+int tc_memset(tc_ctx *ctx, void *dst_dev, int value, size_t bytes);
+
+/* ---- weights: replaces GpuMatrix::upload (src/gpu/mod.rs:222-251). Takes the
+ * buffers of a `Matrix` byte for byte:
+ *   TC_BF16: scales = NULL;                       data = u16[rows*cols]
+ *   TC_Q8:   scales = u16 f16 [rows*cols/32];     data = i8[rows*cols]
+ *   TC_Q4:   scales = u32 [rows*ceil(cols/256)*5]; data = u8[rows*cols/2]
+ * cols must be a multiple of 32 (as src/gpu/mod.rs:241-243 requires). */
+tc_matrix *tc_matrix_upload(tc_ctx *ctx, int kind, size_t rows, size_t cols, const void *scales,
+                            size_t scales_bytes, const void *data, size_t data_bytes);
+void tc_matrix_free(tc_matrix *m);
+
+/* ---- the MoE block: replaces GpuBackend::moe (src/gpu/mod.rs:651-702) with
+ * the arithmetic of the CPU path (src/model.rs:462-521).
+ * router: TC_BF16 [experts, hidden]; gate_up: [experts*2*inter, hidden];
+ * down: [experts*hidden, inter]; both TC_Q8 or TC_Q4. max_tokens bounds `t`
+ * of later forwards (scratch is sized from it, here, not during a forward). */
+tc_moe_layer *tc_moe_layer_create(tc_ctx *ctx, int hidden, int experts, int experts_per_token,
+                                  int inter, const tc_matrix *router, const tc_matrix *gate_up,
+                                  const tc_matrix *down, int max_tokens);
+void tc_moe_layer_free(tc_moe_layer *layer);
+/* A bias added to every token's router logits before top-k (NULL clears it).
+ * Tachyon's router has none (src/model.rs:473); the routing-skew workload
+ * adds one on both the CPU and the GPU side. bias_host: f32[experts]. */
+int tc_moe_set_router_bias(tc_moe_layer *layer, const float *bias_host);
+/* y[t,hidden] += moe(x[t,hidden]); x is the normed input (`s.xb`), y the
+ * residual stream (`s.x`): src/model.rs:671-681. Device pointers; enqueued on
+ * the context's stream, returns without waiting. */
+int tc_moe_forward(tc_moe_layer *layer, const float *x_dev, int t, float *y_dev);
+/* The same through host buffers: copies x and y in, runs, copies y back, waits. */
+int tc_moe_forward_host(tc_moe_layer *layer, const float *x_host, int t, float *y_host);
+/* Routing of the last forward, copied to the host (any pointer may be NULL):
+ * ids u32[t*k] and gates f32[t*k] in descending score order per token
+ * (src/model.rs:448-457), counts u32[experts] = tokens per expert
+ * (src/model.rs:474-482), logits f32[t*experts]. Waits for the stream. */
+int tc_moe_last_routing(tc_moe_layer *layer, uint32_t *ids, float *gates, uint32_t *counts,
+                        float *logits);
+
+/* Dispatch of the last forward, copied to the host (either may be NULL):
+ * offsets u32[experts+1] = first expert-contiguous slot of each expert, and
+ * perm u32[t*k] = for each expert-contiguous slot, token*k + pick. Within an
+ * expert, slots are in ascending token order: the per-expert lists of
+ * src/model.rs:474-482. Waits for the stream. */
+int tc_moe_last_dispatch(tc_moe_layer *layer, uint32_t *offsets, uint32_t *perm);
+
+/* ---- the pre-MoE norm: kernels::rmsnorm (src/kernels.rs:522-528) per row,
+ * as src/model.rs:662-667 applies it. out may alias x. */
+int tc_rmsnorm(tc_ctx *ctx, const float *x_dev, const float *weight_dev, float eps, int t, int n,
+               float *out_dev);
+
+/* ---- stream capture: one launch for a whole stack of blocks at a fixed
+ * batch size. Everything enqueued on the context's stream between begin and
+ * end is recorded, not run. */
+int tc_capture_begin(tc_ctx *ctx);
+tc_graph *tc_capture_end(tc_ctx *ctx);
+int tc_graph_launch(tc_graph *g);
+void tc_graph_free(tc_graph *g);
+
+/* ---- timing on the context's stream with CUDA events. */
+int tc_timer_start(tc_ctx *ctx);
+/* Records the stop event, waits for it, returns milliseconds (negative on error). */
+float tc_timer_stop_ms(tc_ctx *ctx);
+
+/* Number of kernel launches this context has enqueued so far. */
+uint64_t tc_launch_count(tc_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TACHYON_CUDA_H */

@@ -1,0 +1,490 @@
+// The C ABI (include/tachyon_cuda.h): context, device buffers, weight upload,
+// the MoE block and stream capture. Host-side only; kernels live in the other
+// files of this directory.
+#include "../../include/tachyon_cuda.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+struct tc_ctx {
+    int device = 0;
+    int sms = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    std::string name;
+    std::string error;
+    tc::Workspace ws;
+    std::vector<void*> ws_allocs;
+    uint64_t launches = 0;
+    bool capturing = false;
+    uint64_t launches_before_capture = 0;
+    float* host_x = nullptr;  // device staging for the host-buffer entry point
+    float* host_y = nullptr;
+    size_t host_elems = 0;
+};
+
+struct tc_matrix {
+    tc_ctx* ctx;
+    tc::MatrixDev dev;
+    void* scales_alloc;
+    void* data_alloc;
+};
+
+struct tc_moe_layer {
+    tc_ctx* ctx;
+    tc::MoeDims dims;
+    const tc_matrix *router, *gate_up, *down;
+    float* bias = nullptr;
+    int max_tokens;
+    int last_t = 0;
+};
+
+struct tc_graph {
+    tc_ctx* ctx;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+    uint64_t launches;  // kernels recorded in the graph
+};
+
+namespace {
+
+int fail(tc_ctx* ctx, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->error = buf;
+    return -1;
+}
+
+bool cuda_ok(tc_ctx* ctx, cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return true;
+    fail(ctx, "%s: %s", what, cudaGetErrorString(e));
+    return false;
+}
+
+void copy_message(const std::string& s, char* out, size_t len) {
+    if (!out || len == 0) return;
+    size_t n = s.size() < len - 1 ? s.size() : len - 1;
+    memcpy(out, s.data(), n);
+    out[n] = 0;
+}
+
+size_t pad8(size_t v) { return (v + 7) / 8 * 8; }
+
+template <class T>
+bool ws_alloc(tc_ctx* ctx, T*& p, size_t elems) {
+    void* raw = nullptr;
+    if (!cuda_ok(ctx, cudaMalloc(&raw, elems * sizeof(T) + 256), "cudaMalloc(workspace)")) return false;
+    ctx->ws_allocs.push_back(raw);
+    p = static_cast<T*>(raw);
+    return true;
+}
+
+void ws_release(tc_ctx* ctx) {
+    for (void* p : ctx->ws_allocs) cudaFree(p);
+    ctx->ws_allocs.clear();
+    ctx->ws = tc::Workspace{};
+}
+
+// Grows the context's scratch so a layer of these dimensions fits.
+bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
+    tc::Workspace& w = ctx->ws;
+    if (w.max_tokens >= max_tokens && w.hidden >= d.hidden && w.experts >= d.experts &&
+        w.topk >= d.topk && w.inter >= d.inter)
+        return true;
+    tc::MoeDims n{std::max(w.hidden, d.hidden), std::max(w.experts, d.experts),
+                  std::max(w.topk, d.topk), std::max(w.inter, d.inter)};
+    int T = std::max(w.max_tokens, max_tokens);
+    cudaStreamSynchronize(ctx->stream);
+    ws_release(ctx);
+    size_t slots = size_t(T) * n.topk;
+    size_t blocks = (size_t(T) + 255) / 256;
+    bool ok = ws_alloc(ctx, w.logits, size_t(T) * n.experts) && ws_alloc(ctx, w.ids, slots) &&
+              ws_alloc(ctx, w.gates, slots) && ws_alloc(ctx, w.xq, size_t(T) * n.hidden) &&
+              ws_alloc(ctx, w.xs, size_t(T) * pad8(n.hidden / 32)) &&
+              ws_alloc(ctx, w.xsum, size_t(T) * pad8(n.hidden / 32)) &&
+              ws_alloc(ctx, w.counts, size_t(n.experts)) &&
+              ws_alloc(ctx, w.offsets, size_t(n.experts) + 1) && ws_alloc(ctx, w.perm, slots) &&
+              ws_alloc(ctx, w.pos, slots) && ws_alloc(ctx, w.block_hist, blocks * n.experts) &&
+              ws_alloc(ctx, w.hidden_f, slots * n.inter) && ws_alloc(ctx, w.hq, slots * n.inter) &&
+              ws_alloc(ctx, w.hs, slots * pad8(n.inter / 32)) &&
+              ws_alloc(ctx, w.hsum, slots * pad8(n.inter / 32)) &&
+              ws_alloc(ctx, w.out, slots * n.hidden) && ws_alloc(ctx, w.status, size_t(1));
+    if (!ok) {
+        ws_release(ctx);
+        return false;
+    }
+    cudaMemset(w.status, 0, sizeof(int));
+    w.max_tokens = T;
+    w.hidden = n.hidden;
+    w.experts = n.experts;
+    w.topk = n.topk;
+    w.inter = n.inter;
+    return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
+    auto bail = [&](const std::string& m) -> tc_ctx* {
+        copy_message(m, err, errlen);
+        return nullptr;
+    };
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) return bail(std::string("no CUDA device: ") + cudaGetErrorString(e));
+    if (device_ordinal < 0 || device_ordinal >= count) return bail("device ordinal out of range");
+    if ((e = cudaSetDevice(device_ordinal)) != cudaSuccess)
+        return bail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+    cudaDeviceProp prop;
+    if ((e = cudaGetDeviceProperties(&prop, device_ordinal)) != cudaSuccess)
+        return bail(std::string("cudaGetDeviceProperties: ") + cudaGetErrorString(e));
+    if (prop.major != 10)
+        return bail(std::string("this library is built for sm_100a only; found ") + prop.name);
+    tc_ctx* ctx = new tc_ctx;
+    ctx->device = device_ordinal;
+    ctx->sms = prop.multiProcessorCount;
+    ctx->name = prop.name;
+    tc::init_kernels();
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev_start) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev_stop) != cudaSuccess) {
+        delete ctx;
+        return bail("could not create the stream or events");
+    }
+    return ctx;
+}
+
+void tc_destroy(tc_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ws_release(ctx);
+    if (ctx->host_x) cudaFree(ctx->host_x);
+    if (ctx->host_y) cudaFree(ctx->host_y);
+    cudaEventDestroy(ctx->ev_start);
+    cudaEventDestroy(ctx->ev_stop);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+void tc_device_name(tc_ctx* ctx, char* out, size_t len) { copy_message(ctx->name, out, len); }
+
+size_t tc_last_error(tc_ctx* ctx, char* out, size_t len) {
+    copy_message(ctx->error, out, len);
+    return ctx->error.size();
+}
+
+void* tc_stream(tc_ctx* ctx) { return ctx->stream; }
+
+int tc_sync(tc_ctx* ctx) {
+    if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return -1;
+    if (ctx->ws.status) {
+        int status = 0;
+        if (!cuda_ok(ctx, cudaMemcpy(&status, ctx->ws.status, sizeof status, cudaMemcpyDeviceToHost),
+                     "status readback"))
+            return -1;
+        if (status != 0) {
+            cudaMemset(ctx->ws.status, 0, sizeof(int));
+            return fail(ctx, "a kernel gave up a bounded wait (status %d)", status);
+        }
+    }
+    return 0;
+}
+
+void* tc_malloc(tc_ctx* ctx, size_t bytes) {
+    void* p = nullptr;
+    cudaSetDevice(ctx->device);
+    if (!cuda_ok(ctx, cudaMalloc(&p, bytes ? bytes : 1), "cudaMalloc")) return nullptr;
+    return p;
+}
+
+void tc_free(tc_ctx* ctx, void* dev) {
+    if (!dev) return;
+    cudaSetDevice(ctx->device);
+    cudaFree(dev);
+}
+
+int tc_upload(tc_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!cuda_ok(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream), "upload"))
+        return -1;
+    return cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "upload sync") ? 0 : -1;
+}
+
+int tc_download(tc_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!cuda_ok(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream),
+                 "download"))
+        return -1;
+    return cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "download sync") ? 0 : -1;
+}
+
+int tc_memset(tc_ctx* ctx, void* dst, int value, size_t bytes) {
+    return cuda_ok(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream), "memset") ? 0 : -1;
+}
+
+tc_matrix* tc_matrix_upload(tc_ctx* ctx, int kind, size_t rows, size_t cols, const void* scales,
+                            size_t scales_bytes, const void* data, size_t data_bytes) {
+    if (cols % 32 != 0) {
+        fail(ctx, "GPU matrices need a multiple of 32 columns, not %zu", cols);
+        return nullptr;
+    }
+    size_t want_scales = 0, want_data = 0;
+    switch (kind) {
+        case TC_BF16:
+            want_data = rows * cols * 2;
+            break;
+        case TC_Q8:
+            want_scales = rows * (cols / 32) * 2;
+            want_data = rows * cols;
+            break;
+        case TC_Q4:
+            want_scales = rows * ((cols / 32 + 7) / 8 * 5) * 4;
+            want_data = rows * cols / 2;
+            break;
+        default:
+            fail(ctx, "unknown matrix kind %d", kind);
+            return nullptr;
+    }
+    if (scales_bytes != want_scales || data_bytes != want_data) {
+        fail(ctx, "matrix buffers are %zu+%zu bytes, expected %zu+%zu for %zux%zu kind %d",
+             scales_bytes, data_bytes, want_scales, want_data, rows, cols, kind);
+        return nullptr;
+    }
+    cudaSetDevice(ctx->device);
+    tc_matrix* m = new tc_matrix{ctx, {kind, rows, cols, nullptr, nullptr}, nullptr, nullptr};
+    // Padded so that staged copies of a partial last chunk stay inside the allocation.
+    if (want_scales) {
+        if (!cuda_ok(ctx, cudaMalloc(&m->scales_alloc, want_scales + 256), "cudaMalloc(scales)") ||
+            !cuda_ok(ctx, cudaMemcpy(m->scales_alloc, scales, want_scales, cudaMemcpyHostToDevice),
+                     "scales upload")) {
+            tc_matrix_free(m);
+            return nullptr;
+        }
+    }
+    if (!cuda_ok(ctx, cudaMalloc(&m->data_alloc, want_data + 256), "cudaMalloc(weights)") ||
+        !cuda_ok(ctx, cudaMemcpy(m->data_alloc, data, want_data, cudaMemcpyHostToDevice),
+                 "weights upload")) {
+        tc_matrix_free(m);
+        return nullptr;
+    }
+    m->dev.scales = m->scales_alloc;
+    m->dev.data = m->data_alloc;
+    return m;
+}
+
+void tc_matrix_free(tc_matrix* m) {
+    if (!m) return;
+    cudaSetDevice(m->ctx->device);
+    if (m->scales_alloc) cudaFree(m->scales_alloc);
+    if (m->data_alloc) cudaFree(m->data_alloc);
+    delete m;
+}
+
+tc_moe_layer* tc_moe_layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inter,
+                                  const tc_matrix* router, const tc_matrix* gate_up,
+                                  const tc_matrix* down, int max_tokens) {
+    auto bad = [&](const char* why) -> tc_moe_layer* {
+        fail(ctx, "tc_moe_layer_create: %s", why);
+        return nullptr;
+    };
+    if (!router || !gate_up || !down) return bad("a matrix is null");
+    if (hidden <= 0 || hidden % 32 || inter <= 0 || inter % 32)
+        return bad("hidden and intermediate sizes must be positive multiples of 32");
+    if (experts <= 0 || experts > tc::MAX_EXPERTS) return bad("between 1 and 256 experts");
+    if (k <= 0 || k > tc::MAX_TOPK || k > experts) return bad("between 1 and min(32, experts) experts per token");
+    if (max_tokens <= 0) return bad("max_tokens must be positive");
+    if (router->dev.kind != TC_BF16 || router->dev.rows != size_t(experts) ||
+        router->dev.cols != size_t(hidden))
+        return bad("the router must be bf16 [experts, hidden]");
+    if (gate_up->dev.kind == TC_BF16 || down->dev.kind == TC_BF16)
+        return bad("expert matrices must be 8-bit or 4-bit");
+    if (gate_up->dev.rows != size_t(experts) * 2 * inter || gate_up->dev.cols != size_t(hidden))
+        return bad("gate_up must be [experts*2*inter, hidden]");
+    if (down->dev.rows != size_t(experts) * hidden || down->dev.cols != size_t(inter))
+        return bad("down must be [experts*hidden, inter]");
+    cudaSetDevice(ctx->device);
+    tc::MoeDims d{hidden, experts, k, inter};
+    if (!ws_reserve(ctx, d, max_tokens)) return nullptr;
+    tc_moe_layer* l = new tc_moe_layer{ctx, d, router, gate_up, down, nullptr, max_tokens, 0};
+    return l;
+}
+
+void tc_moe_layer_free(tc_moe_layer* layer) {
+    if (!layer) return;
+    if (layer->bias) cudaFree(layer->bias);
+    delete layer;
+}
+
+int tc_moe_set_router_bias(tc_moe_layer* layer, const float* bias_host) {
+    tc_ctx* ctx = layer->ctx;
+    if (!bias_host) {
+        if (layer->bias) cudaFree(layer->bias);
+        layer->bias = nullptr;
+        return 0;
+    }
+    if (!layer->bias &&
+        !cuda_ok(ctx, cudaMalloc(&layer->bias, layer->dims.experts * sizeof(float)), "cudaMalloc(bias)"))
+        return -1;
+    return tc_upload(ctx, layer->bias, bias_host, layer->dims.experts * sizeof(float));
+}
+
+int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
+    tc_ctx* ctx = layer->ctx;
+    if (t <= 0) return fail(ctx, "empty batch");
+    if (t > layer->max_tokens) return fail(ctx, "%d tokens, layer was created for %d", t, layer->max_tokens);
+    const tc::MoeDims& d = layer->dims;
+    tc::Workspace& ws = ctx->ws;
+    cudaStream_t s = ctx->stream;
+    int n = 0;
+    n += tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias, x, t,
+                          ws, s);
+    n += tc::launch_dispatch(d, t, ws, s);
+    n += tc::launch_gate_up(d, layer->gate_up->dev, t, ws, ctx->sms, s);
+    n += tc::launch_quant_hidden(d, t, ws, s);
+    n += tc::launch_down(d, layer->down->dev, t, ws, ctx->sms, s);
+    n += tc::launch_combine(d, t, ws, y, s);
+    ctx->launches += n;
+    layer->last_t = t;
+    if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+    return 0;
+}
+
+int tc_moe_forward_host(tc_moe_layer* layer, const float* x_host, int t, float* y_host) {
+    tc_ctx* ctx = layer->ctx;
+    if (t <= 0) return fail(ctx, "empty batch");
+    size_t elems = size_t(t) * layer->dims.hidden;
+    if (elems > ctx->host_elems) {
+        cudaStreamSynchronize(ctx->stream);
+        if (ctx->host_x) cudaFree(ctx->host_x);
+        if (ctx->host_y) cudaFree(ctx->host_y);
+        ctx->host_x = ctx->host_y = nullptr;
+        ctx->host_elems = 0;
+        if (!cuda_ok(ctx, cudaMalloc(&ctx->host_x, elems * 4), "cudaMalloc(staging)") ||
+            !cuda_ok(ctx, cudaMalloc(&ctx->host_y, elems * 4), "cudaMalloc(staging)"))
+            return -1;
+        ctx->host_elems = elems;
+    }
+    cudaStream_t s = ctx->stream;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(ctx->host_x, x_host, elems * 4, cudaMemcpyHostToDevice, s), "x upload") ||
+        !cuda_ok(ctx, cudaMemcpyAsync(ctx->host_y, y_host, elems * 4, cudaMemcpyHostToDevice, s), "y upload"))
+        return -1;
+    if (tc_moe_forward(layer, ctx->host_x, t, ctx->host_y) != 0) return -1;
+    if (!cuda_ok(ctx, cudaMemcpyAsync(y_host, ctx->host_y, elems * 4, cudaMemcpyDeviceToHost, s), "y download"))
+        return -1;
+    return tc_sync(ctx);
+}
+
+int tc_moe_last_routing(tc_moe_layer* layer, uint32_t* ids, float* gates, uint32_t* counts,
+                        float* logits) {
+    tc_ctx* ctx = layer->ctx;
+    if (tc_sync(ctx) != 0) return -1;
+    const tc::MoeDims& d = layer->dims;
+    size_t slots = size_t(layer->last_t) * d.topk;
+    auto get = [&](void* dst, const void* src, size_t bytes) {
+        return !dst || cuda_ok(ctx, cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost), "routing readback");
+    };
+    if (!get(ids, ctx->ws.ids, slots * 4) || !get(gates, ctx->ws.gates, slots * 4) ||
+        !get(counts, ctx->ws.counts, size_t(d.experts) * 4) ||
+        !get(logits, ctx->ws.logits, size_t(layer->last_t) * d.experts * 4))
+        return -1;
+    return 0;
+}
+
+int tc_moe_last_dispatch(tc_moe_layer* layer, uint32_t* offsets, uint32_t* perm) {
+    tc_ctx* ctx = layer->ctx;
+    if (tc_sync(ctx) != 0) return -1;
+    const tc::MoeDims& d = layer->dims;
+    if (offsets && !cuda_ok(ctx, cudaMemcpy(offsets, ctx->ws.offsets, size_t(d.experts + 1) * 4,
+                                            cudaMemcpyDeviceToHost), "dispatch readback"))
+        return -1;
+    if (perm && !cuda_ok(ctx, cudaMemcpy(perm, ctx->ws.perm, size_t(layer->last_t) * d.topk * 4,
+                                         cudaMemcpyDeviceToHost), "dispatch readback"))
+        return -1;
+    return 0;
+}
+
+int tc_rmsnorm(tc_ctx* ctx, const float* x, const float* w, float eps, int t, int n, float* out) {
+    if (t <= 0 || n <= 0) return fail(ctx, "rmsnorm over nothing");
+    ctx->launches += tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream);
+    if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "rmsnorm launch")) return -1;
+    return 0;
+}
+
+int tc_capture_begin(tc_ctx* ctx) {
+    if (ctx->capturing) return fail(ctx, "a capture is already open");
+    if (!cuda_ok(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal),
+                 "cudaStreamBeginCapture"))
+        return -1;
+    ctx->capturing = true;
+    ctx->launches_before_capture = ctx->launches;
+    return 0;
+}
+
+tc_graph* tc_capture_end(tc_ctx* ctx) {
+    if (!ctx->capturing) {
+        fail(ctx, "no capture is open");
+        return nullptr;
+    }
+    ctx->capturing = false;
+    ctx->launches = ctx->launches_before_capture;  // recorded, not run
+    cudaGraph_t graph = nullptr;
+    if (!cuda_ok(ctx, cudaStreamEndCapture(ctx->stream, &graph), "cudaStreamEndCapture")) return nullptr;
+    cudaGraphExec_t exec = nullptr;
+    if (!cuda_ok(ctx, cudaGraphInstantiate(&exec, graph, 0), "cudaGraphInstantiate")) {
+        cudaGraphDestroy(graph);
+        return nullptr;
+    }
+    size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    std::vector<cudaGraphNode_t> list(nodes);
+    uint64_t kernels = 0;
+    if (nodes && cudaGraphGetNodes(graph, list.data(), &nodes) == cudaSuccess) {
+        for (size_t i = 0; i < nodes; i++) {
+            cudaGraphNodeType ty;
+            if (cudaGraphNodeGetType(list[i], &ty) == cudaSuccess && ty == cudaGraphNodeTypeKernel)
+                kernels++;
+        }
+    }
+    return new tc_graph{ctx, graph, exec, kernels};
+}
+
+int tc_graph_launch(tc_graph* g) {
+    tc_ctx* ctx = g->ctx;
+    if (!cuda_ok(ctx, cudaGraphLaunch(g->exec, ctx->stream), "cudaGraphLaunch")) return -1;
+    ctx->launches += g->launches;
+    return 0;
+}
+
+void tc_graph_free(tc_graph* g) {
+    if (!g) return;
+    cudaGraphExecDestroy(g->exec);
+    cudaGraphDestroy(g->graph);
+    delete g;
+}
+
+int tc_timer_start(tc_ctx* ctx) {
+    return cuda_ok(ctx, cudaEventRecord(ctx->ev_start, ctx->stream), "cudaEventRecord") ? 0 : -1;
+}
+
+float tc_timer_stop_ms(tc_ctx* ctx) {
+    if (!cuda_ok(ctx, cudaEventRecord(ctx->ev_stop, ctx->stream), "cudaEventRecord") ||
+        !cuda_ok(ctx, cudaEventSynchronize(ctx->ev_stop), "cudaEventSynchronize"))
+        return -1.0f;
+    float ms = 0.0f;
+    if (!cuda_ok(ctx, cudaEventElapsedTime(&ms, ctx->ev_start, ctx->ev_stop), "cudaEventElapsedTime"))
+        return -1.0f;
+    return ms;
+}
+
+uint64_t tc_launch_count(tc_ctx* ctx) { return ctx->launches; }
+
+}  // extern "C"

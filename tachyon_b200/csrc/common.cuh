@@ -1,0 +1,91 @@
+// Internal declarations shared by the kernel files and the C ABI.
+//
+// Compile every file with -fmad=false: the CPU path this backend reproduces
+// rounds a*b before adding c unless its source asks for a fused multiply-add
+// (src/kernels_x86.rs uses _mm256_fmadd_ps, src/kernels.rs:427 mul_add), so
+// the kernels spell fmaf() where the reference fuses and plain * and +
+// everywhere else.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tc {
+
+constexpr int QK = 32;          // values per quantization block (src/kernels.rs:13)
+constexpr int SUPER = 8;        // 4-bit blocks per packed super-block (src/kernels.rs:165)
+constexpr int SUPER_WORDS = 5;  // words per super-block (src/kernels.rs:167)
+
+constexpr int MAX_EXPERTS = 256;
+constexpr int MAX_TOPK = 32;
+
+// Error codes a kernel may leave in the context's status word.
+enum : int {
+    ERR_NONE = 0,
+    ERR_COPY_WAIT_TIMEOUT = 1,  // a staged weight copy did not arrive within the spin limit
+};
+
+struct MatrixDev {
+    int kind;
+    size_t rows, cols;
+    const void* scales;  // Q8: f16 [rows, cols/32]; Q4: u32 [rows, words]
+    const void* data;    // BF16: u16; Q8: i8; Q4: u8 packed nibbles
+};
+
+// Per-context scratch, sized at layer creation for max_tokens.
+struct Workspace {
+    int max_tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;
+    float* logits = nullptr;      // [T, E]
+    uint32_t* ids = nullptr;      // [T, k] descending score order
+    float* gates = nullptr;       // [T, k]
+    int8_t* xq = nullptr;         // [T, H] activations, 8-bit per 32-block
+    float* xs = nullptr;          // [T, pad8(H/32)] their scales, zero padded
+    float* xsum = nullptr;        // [T, pad8(H/32)] scale * sum of quants (4-bit offsets)
+    uint32_t* counts = nullptr;   // [E] tokens per expert
+    uint32_t* offsets = nullptr;  // [E+1] first sorted slot of each expert
+    uint32_t* perm = nullptr;     // [T*k] sorted slot -> token*k + j
+    uint32_t* pos = nullptr;      // [T*k] token*k + j -> sorted slot
+    uint32_t* block_hist = nullptr;  // [blocks, E] dispatch: per-block histograms / bases
+    float* hidden_f = nullptr;    // [T*k, I] silu(gate)*up, sorted order
+    int8_t* hq = nullptr;         // [T*k, I]
+    float* hs = nullptr;          // [T*k, pad8(I/32)]
+    float* hsum = nullptr;        // [T*k, pad8(I/32)]
+    float* out = nullptr;         // [T*k, H] expert outputs, sorted order
+    int* status = nullptr;        // device status word
+};
+
+struct MoeDims {
+    int hidden, experts, topk, inter;
+};
+
+// Opts the kernels that need it into large dynamic shared memory (once per device).
+void init_kernels();
+
+// ---- launchers (each enqueues on `stream` and returns the number of kernels launched)
+
+// Router logits (bf16 weights, f32 activations), top-k, gating softmax, and
+// 8-bit quantization of each token's row.
+int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x, int t,
+                 Workspace& ws, cudaStream_t stream);
+
+// Per-expert histogram, prefix scan and stable permutation of the t*k slots.
+int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
+
+// gate_up rows of each expert times its tokens, SwiGLU, into ws.hidden_f.
+int launch_gate_up(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
+                   cudaStream_t stream);
+
+// 8-bit quantization of ws.hidden_f rows into ws.hq / ws.hs / ws.hsum.
+int launch_quant_hidden(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
+
+// down rows of each expert times its tokens' hidden rows, into ws.out.
+int launch_down(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
+                cudaStream_t stream);
+
+// y[i] += sum over the token's experts, ascending expert index, gate * out.
+int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);
+
+int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, float* out,
+                   cudaStream_t stream);
+
+}  // namespace tc

@@ -1,0 +1,327 @@
+"""ctypes binding of ``libtachyon_cuda.so`` (include/tachyon_cuda.h) and the thin
+host-side objects over it. The names follow Tachyon's GPU backend
+(src/gpu/mod.rs): a ``Context`` owns the device, ``DeviceMatrix`` is
+``GpuMatrix``, ``MoeLayer.forward`` is ``GpuBackend::moe``.
+
+There is no CPU fallback: loading fails loudly if the library is missing, and
+every compute call runs CUDA kernels or raises ``TachyonCudaError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from .weights import KIND_BF16, Matrix
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libtachyon_cuda.so")
+
+# Every symbol include/tachyon_cuda.h declares: (restype, argtypes).
+_vp, _sz, _i, _f, _u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_float, C.c_uint64
+SYMBOLS = {
+    "tc_create": (_vp, [_i, C.c_char_p, _sz]),
+    "tc_destroy": (None, [_vp]),
+    "tc_device_name": (None, [_vp, C.c_char_p, _sz]),
+    "tc_last_error": (_sz, [_vp, C.c_char_p, _sz]),
+    "tc_sync": (_i, [_vp]),
+    "tc_stream": (_vp, [_vp]),
+    "tc_malloc": (_vp, [_vp, _sz]),
+    "tc_free": (None, [_vp, _vp]),
+    "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
+    "tc_download": (_i, [_vp, _vp, _vp, _sz]),
+    "tc_memset": (_i, [_vp, _vp, _i, _sz]),
+    "tc_matrix_upload": (_vp, [_vp, _i, _sz, _sz, _vp, _sz, _vp, _sz]),
+    "tc_matrix_free": (None, [_vp]),
+    "tc_moe_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
+    "tc_moe_layer_free": (None, [_vp]),
+    "tc_moe_set_router_bias": (_i, [_vp, _vp]),
+    "tc_moe_forward": (_i, [_vp, _vp, _i, _vp]),
+    "tc_moe_forward_host": (_i, [_vp, _vp, _i, _vp]),
+    "tc_moe_last_routing": (_i, [_vp, _vp, _vp, _vp, _vp]),
+    "tc_moe_last_dispatch": (_i, [_vp, _vp, _vp]),
+    "tc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp]),
+    "tc_capture_begin": (_i, [_vp]),
+    "tc_capture_end": (_vp, [_vp]),
+    "tc_graph_launch": (_i, [_vp]),
+    "tc_graph_free": (None, [_vp]),
+    "tc_timer_start": (_i, [_vp]),
+    "tc_timer_stop_ms": (_f, [_vp]),
+    "tc_launch_count": (_u64, [_vp]),
+}
+
+
+class TachyonCudaError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the shared library (built in-tree by ``tachyon_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise TachyonCudaError(
+                f"{LIB_PATH} is missing: build it with `python -m tachyon_b200.build` "
+                "(there is no CPU fallback)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        return a.ctypes.data_as(C.c_void_p)
+    return C.c_void_p(int(a))
+
+
+class Context:
+    """One device, one stream (``tc_ctx``). Driven by one thread at a time."""
+
+    def __init__(self, device: int = 0):
+        self.lib = load()
+        err = C.create_string_buffer(1024)
+        self.handle = self.lib.tc_create(device, err, len(err))
+        if not self.handle:
+            raise TachyonCudaError(f"CUDA setup failed: {err.value.decode()}")
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.tc_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc, what: str):
+        if rc != 0:
+            buf = C.create_string_buffer(1024)
+            self.lib.tc_last_error(self.handle, buf, len(buf))
+            raise TachyonCudaError(f"{what}: {buf.value.decode()}")
+
+    def last_error(self) -> str:
+        buf = C.create_string_buffer(1024)
+        self.lib.tc_last_error(self.handle, buf, len(buf))
+        return buf.value.decode()
+
+    @property
+    def name(self) -> str:
+        buf = C.create_string_buffer(256)
+        self.lib.tc_device_name(self.handle, buf, len(buf))
+        return buf.value.decode()
+
+    def sync(self):
+        self._check(self.lib.tc_sync(self.handle), "tc_sync")
+
+    def stream(self) -> int:
+        return self.lib.tc_stream(self.handle) or 0
+
+    def malloc(self, nbytes: int) -> int:
+        p = self.lib.tc_malloc(self.handle, nbytes)
+        if not p:
+            raise TachyonCudaError(f"tc_malloc({nbytes}): {self.last_error()}")
+        return p
+
+    def free(self, dev: int):
+        self.lib.tc_free(self.handle, dev)
+
+    def upload(self, dev: int, host: np.ndarray):
+        host = np.ascontiguousarray(host)
+        self._check(self.lib.tc_upload(self.handle, dev, _ptr(host), host.nbytes), "tc_upload")
+
+    def download(self, host: np.ndarray, dev: int):
+        assert host.flags["C_CONTIGUOUS"]
+        self._check(self.lib.tc_download(self.handle, _ptr(host), dev, host.nbytes), "tc_download")
+
+    def memset(self, dev: int, value: int, nbytes: int):
+        self._check(self.lib.tc_memset(self.handle, dev, value, nbytes), "tc_memset")
+
+    def to_device(self, host: np.ndarray) -> "DeviceArray":
+        arr = DeviceArray(self, host.shape, host.dtype)
+        self.upload(arr.ptr, host)
+        return arr
+
+    def empty(self, shape, dtype=np.float32) -> "DeviceArray":
+        return DeviceArray(self, shape, dtype)
+
+    def rmsnorm(self, x: "DeviceArray", weight: "DeviceArray", eps: float, out: "DeviceArray"):
+        t, n = x.shape
+        self._check(self.lib.tc_rmsnorm(self.handle, x.ptr, weight.ptr, eps, t, n, out.ptr), "tc_rmsnorm")
+
+    def capture_begin(self):
+        self._check(self.lib.tc_capture_begin(self.handle), "tc_capture_begin")
+
+    def capture_end(self) -> "Graph":
+        g = self.lib.tc_capture_end(self.handle)
+        if not g:
+            raise TachyonCudaError(f"tc_capture_end: {self.last_error()}")
+        return Graph(self, g)
+
+    def timer_start(self):
+        self._check(self.lib.tc_timer_start(self.handle), "tc_timer_start")
+
+    def timer_stop_ms(self) -> float:
+        ms = self.lib.tc_timer_stop_ms(self.handle)
+        if ms < 0:
+            raise TachyonCudaError(f"tc_timer_stop_ms: {self.last_error()}")
+        return ms
+
+    def launch_count(self) -> int:
+        return int(self.lib.tc_launch_count(self.handle))
+
+
+class DeviceArray:
+    """A typed device buffer (``tc_malloc``), freed with its owner."""
+
+    def __init__(self, ctx: Context, shape, dtype):
+        self.ctx = ctx
+        self.shape = tuple(int(s) for s in (shape if hasattr(shape, "__len__") else (shape,)))
+        self.dtype = np.dtype(dtype)
+        self.nbytes = int(np.prod(self.shape)) * self.dtype.itemsize
+        self.ptr = ctx.malloc(max(self.nbytes, 1))
+
+    def get(self) -> np.ndarray:
+        out = np.empty(self.shape, self.dtype)
+        if self.nbytes:
+            self.ctx.download(out, self.ptr)
+        return out
+
+    def set(self, host: np.ndarray):
+        host = np.ascontiguousarray(host, self.dtype)
+        assert host.nbytes == self.nbytes
+        self.ctx.upload(self.ptr, host)
+
+    def free(self):
+        if self.ptr and self.ctx.handle:
+            self.ctx.free(self.ptr)
+        self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Graph:
+    def __init__(self, ctx: Context, handle):
+        self.ctx, self.handle = ctx, handle
+
+    def launch(self):
+        self.ctx._check(self.ctx.lib.tc_graph_launch(self.handle), "tc_graph_launch")
+
+    def free(self):
+        if self.handle:
+            self.ctx.lib.tc_graph_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class DeviceMatrix:
+    """A ``Matrix`` uploaded byte for byte (``GpuMatrix::upload``, src/gpu/mod.rs:222-251)."""
+
+    def __init__(self, ctx: Context, m: Matrix):
+        self.ctx, self.kind, self.rows, self.cols = ctx, m.kind, m.rows, m.cols
+        scales = None if m.scales is None else np.ascontiguousarray(m.scales)
+        data = np.ascontiguousarray(m.data)
+        self.nbytes = data.nbytes + (0 if scales is None else scales.nbytes)
+        self.handle = ctx.lib.tc_matrix_upload(
+            ctx.handle, m.kind, m.rows, m.cols, _ptr(scales), 0 if scales is None else scales.nbytes,
+            _ptr(data), data.nbytes)
+        if not self.handle:
+            raise TachyonCudaError(f"tc_matrix_upload: {ctx.last_error()}")
+
+    def free(self):
+        if self.handle and self.ctx.handle:
+            self.ctx.lib.tc_matrix_free(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class MoeLayer:
+    """One Granite MoE block on the device (``tc_moe_layer``)."""
+
+    def __init__(self, ctx: Context, router: Matrix, gate_up: Matrix, down: Matrix, experts_per_token: int,
+                 max_tokens: int):
+        assert router.kind == KIND_BF16
+        self.ctx = ctx
+        self.hidden, self.experts = router.cols, router.rows
+        self.inter, self.topk = down.cols, experts_per_token
+        self.max_tokens = max_tokens
+        self.router = DeviceMatrix(ctx, router)
+        self.gate_up = DeviceMatrix(ctx, gate_up)
+        self.down = DeviceMatrix(ctx, down)
+        self.weight_bytes = self.router.nbytes + self.gate_up.nbytes + self.down.nbytes
+        self.handle = ctx.lib.tc_moe_layer_create(
+            ctx.handle, self.hidden, self.experts, self.topk, self.inter, self.router.handle,
+            self.gate_up.handle, self.down.handle, max_tokens)
+        if not self.handle:
+            raise TachyonCudaError(f"tc_moe_layer_create: {ctx.last_error()}")
+
+    def set_router_bias(self, bias):
+        b = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        self.ctx._check(self.ctx.lib.tc_moe_set_router_bias(self.handle, _ptr(b)), "tc_moe_set_router_bias")
+
+    def forward(self, x: DeviceArray, y: DeviceArray, t: int | None = None):
+        """y[t, hidden] += moe(x[t, hidden]) on the device; returns without waiting."""
+        t = x.shape[0] if t is None else t
+        self.ctx._check(self.ctx.lib.tc_moe_forward(self.handle, x.ptr, t, y.ptr), "tc_moe_forward")
+
+    def forward_host(self, x: np.ndarray, y: np.ndarray):
+        """The same through host buffers (copies in and out, waits); y is updated in place."""
+        x = np.ascontiguousarray(x, np.float32)
+        assert y.dtype == np.float32 and y.flags["C_CONTIGUOUS"] and y.shape == x.shape
+        self.ctx._check(self.ctx.lib.tc_moe_forward_host(self.handle, _ptr(x), x.shape[0], _ptr(y)),
+                        "tc_moe_forward_host")
+
+    def last_routing(self, t: int):
+        ids = np.empty((t, self.topk), np.uint32)
+        gates = np.empty((t, self.topk), np.float32)
+        counts = np.empty(self.experts, np.uint32)
+        logits = np.empty((t, self.experts), np.float32)
+        self.ctx._check(self.ctx.lib.tc_moe_last_routing(self.handle, _ptr(ids), _ptr(gates), _ptr(counts),
+                                                       _ptr(logits)), "tc_moe_last_routing")
+        return ids, gates, counts, logits
+
+    def last_dispatch(self, t: int):
+        offsets = np.empty(self.experts + 1, np.uint32)
+        perm = np.empty(t * self.topk, np.uint32)
+        self.ctx._check(self.ctx.lib.tc_moe_last_dispatch(self.handle, _ptr(offsets), _ptr(perm)),
+                        "tc_moe_last_dispatch")
+        return offsets, perm
+
+    def free(self):
+        if getattr(self, "handle", None) and self.ctx.handle:
+            self.ctx.lib.tc_moe_layer_free(self.handle)
+        self.handle = None
+        for m in (self.router, self.gate_up, self.down):
+            m.free()
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
