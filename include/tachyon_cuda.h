@@ -49,6 +49,11 @@ void tc_free(tc_ctx *ctx, void *dev);
 int tc_upload(tc_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
 int tc_download(tc_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
 int tc_memset(tc_ctx *ctx, void *dst_dev, int value, size_t bytes);
+/* Device-to-device copy on the context's stream (not waited for). */
+int tc_copy(tc_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+/* Page-locked host memory, so uploads and downloads run at full PCIe rate. */
+void *tc_host_alloc(tc_ctx *ctx, size_t bytes);
+void tc_host_free(tc_ctx *ctx, void *host);
 
 /* ---- weights: replaces GpuMatrix::upload (src/gpu/mod.rs:222-251). Takes the
  * buffers of a `Matrix` byte for byte:
@@ -110,6 +115,15 @@ void tc_graph_free(tc_graph *g);
 int tc_timer_start(tc_ctx *ctx);
 /* Records the stop event, waits for it, returns milliseconds (negative on error). */
 float tc_timer_stop_ms(tc_ctx *ctx);
+
+/* ---- per-kernel timing. While enabled (and outside a capture), every kernel
+ * the library enqueues is bracketed by CUDA events on the context's stream.
+ * tc_profile_read() waits, then adds up milliseconds and launches per stage
+ * since the last read: stage 0 route, 1 dispatch, 2 gate_up, 3 quantize
+ * hidden, 4 down, 5 combine, 6 rmsnorm (TC_PROFILE_STAGES entries each). */
+#define TC_PROFILE_STAGES 8
+int tc_profile_enable(tc_ctx *ctx, int on);
+int tc_profile_read(tc_ctx *ctx, float *ms, uint64_t *launches);
 
 /* Number of kernel launches this context has enqueued so far. */
 uint64_t tc_launch_count(tc_ctx *ctx);

@@ -23,6 +23,11 @@ struct tc_ctx {
     uint64_t launches = 0;
     bool capturing = false;
     uint64_t launches_before_capture = 0;
+    bool profiling = false;
+    std::vector<cudaEvent_t> ev_pool;                      // reused across reads
+    size_t ev_used = 0;
+    struct Span { int stage; size_t a, b; int launches; };
+    std::vector<Span> spans;
     float* host_x = nullptr;  // device staging for the host-buffer entry point
     float* host_y = nullptr;
     size_t host_elems = 0;
@@ -77,6 +82,33 @@ void copy_message(const std::string& s, char* out, size_t len) {
 }
 
 size_t pad8(size_t v) { return (v + 7) / 8 * 8; }
+
+size_t next_event(tc_ctx* ctx) {
+    if (ctx->ev_used == ctx->ev_pool.size()) {
+        cudaEvent_t e;
+        cudaEventCreate(&e);
+        ctx->ev_pool.push_back(e);
+    }
+    return ctx->ev_used++;
+}
+
+// Runs one launcher, bracketed by events when profiling outside a capture.
+template <class F>
+int staged(tc_ctx* ctx, int stage, F launch) {
+    const bool timed = ctx->profiling && !ctx->capturing;
+    size_t a = 0;
+    if (timed) {
+        a = next_event(ctx);
+        cudaEventRecord(ctx->ev_pool[a], ctx->stream);
+    }
+    int n = launch();
+    if (timed) {
+        size_t b = next_event(ctx);
+        cudaEventRecord(ctx->ev_pool[b], ctx->stream);
+        ctx->spans.push_back({stage, a, b, n});
+    }
+    return n;
+}
 
 template <class T>
 bool ws_alloc(tc_ctx* ctx, T*& p, size_t elems) {
@@ -171,6 +203,7 @@ void tc_destroy(tc_ctx* ctx) {
     ws_release(ctx);
     if (ctx->host_x) cudaFree(ctx->host_x);
     if (ctx->host_y) cudaFree(ctx->host_y);
+    for (cudaEvent_t e : ctx->ev_pool) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev_start);
     cudaEventDestroy(ctx->ev_stop);
     cudaStreamDestroy(ctx->stream);
@@ -229,6 +262,44 @@ int tc_download(tc_ctx* ctx, void* dst, const void* src, size_t bytes) {
 
 int tc_memset(tc_ctx* ctx, void* dst, int value, size_t bytes) {
     return cuda_ok(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream), "memset") ? 0 : -1;
+}
+
+int tc_copy(tc_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    return cuda_ok(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream), "copy") ? 0 : -1;
+}
+
+void* tc_host_alloc(tc_ctx* ctx, size_t bytes) {
+    void* p = nullptr;
+    if (!cuda_ok(ctx, cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault), "cudaHostAlloc")) return nullptr;
+    return p;
+}
+
+void tc_host_free(tc_ctx* ctx, void* host) {
+    (void)ctx;
+    if (host) cudaFreeHost(host);
+}
+
+int tc_profile_enable(tc_ctx* ctx, int on) {
+    ctx->profiling = on != 0;
+    return 0;
+}
+
+int tc_profile_read(tc_ctx* ctx, float* ms, uint64_t* launches) {
+    if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return -1;
+    for (int i = 0; i < TC_PROFILE_STAGES; i++) {
+        if (ms) ms[i] = 0.0f;
+        if (launches) launches[i] = 0;
+    }
+    for (const auto& sp : ctx->spans) {
+        float t = 0.0f;
+        if (!cuda_ok(ctx, cudaEventElapsedTime(&t, ctx->ev_pool[sp.a], ctx->ev_pool[sp.b]), "cudaEventElapsedTime"))
+            return -1;
+        if (ms) ms[sp.stage] += t;
+        if (launches) launches[sp.stage] += sp.launches;
+    }
+    ctx->spans.clear();
+    ctx->ev_used = 0;
+    return 0;
 }
 
 tc_matrix* tc_matrix_upload(tc_ctx* ctx, int kind, size_t rows, size_t cols, const void* scales,
@@ -345,13 +416,15 @@ int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
     tc::Workspace& ws = ctx->ws;
     cudaStream_t s = ctx->stream;
     int n = 0;
-    n += tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias, x, t,
-                          ws, s);
-    n += tc::launch_dispatch(d, t, ws, s);
-    n += tc::launch_gate_up(d, layer->gate_up->dev, t, ws, ctx->sms, s);
-    n += tc::launch_quant_hidden(d, t, ws, s);
-    n += tc::launch_down(d, layer->down->dev, t, ws, ctx->sms, s);
-    n += tc::launch_combine(d, t, ws, y, s);
+    n += staged(ctx, 0, [&] {
+        return tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
+                                x, t, ws, s);
+    });
+    n += staged(ctx, 1, [&] { return tc::launch_dispatch(d, t, ws, s); });
+    n += staged(ctx, 2, [&] { return tc::launch_gate_up(d, layer->gate_up->dev, t, ws, ctx->sms, s); });
+    n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
+    n += staged(ctx, 4, [&] { return tc::launch_down(d, layer->down->dev, t, ws, ctx->sms, s); });
+    n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
     ctx->launches += n;
     layer->last_t = t;
     if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
@@ -414,7 +487,7 @@ int tc_moe_last_dispatch(tc_moe_layer* layer, uint32_t* offsets, uint32_t* perm)
 
 int tc_rmsnorm(tc_ctx* ctx, const float* x, const float* w, float eps, int t, int n, float* out) {
     if (t <= 0 || n <= 0) return fail(ctx, "rmsnorm over nothing");
-    ctx->launches += tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream);
+    ctx->launches += staged(ctx, 6, [&] { return tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream); });
     if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "rmsnorm launch")) return -1;
     return 0;
 }

@@ -32,6 +32,11 @@ SYMBOLS = {
     "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
     "tc_download": (_i, [_vp, _vp, _vp, _sz]),
     "tc_memset": (_i, [_vp, _vp, _i, _sz]),
+    "tc_copy": (_i, [_vp, _vp, _vp, _sz]),
+    "tc_host_alloc": (_vp, [_vp, _sz]),
+    "tc_host_free": (None, [_vp, _vp]),
+    "tc_profile_enable": (_i, [_vp, _i]),
+    "tc_profile_read": (_i, [_vp, _vp, _vp]),
     "tc_matrix_upload": (_vp, [_vp, _i, _sz, _sz, _vp, _sz, _vp, _sz]),
     "tc_matrix_free": (None, [_vp]),
     "tc_moe_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
@@ -148,6 +153,31 @@ class Context:
 
     def memset(self, dev: int, value: int, nbytes: int):
         self._check(self.lib.tc_memset(self.handle, dev, value, nbytes), "tc_memset")
+
+    def copy(self, dst: "DeviceArray", src: "DeviceArray"):
+        assert dst.nbytes == src.nbytes
+        self._check(self.lib.tc_copy(self.handle, dst.ptr, src.ptr, src.nbytes), "tc_copy")
+
+    def pinned(self, shape, dtype=np.float32) -> np.ndarray:
+        """A numpy array over page-locked host memory (kept alive by the context)."""
+        dtype = np.dtype(dtype)
+        n = int(np.prod(shape))
+        p = self.lib.tc_host_alloc(self.handle, n * dtype.itemsize)
+        if not p:
+            raise TachyonCudaError(f"tc_host_alloc: {self.last_error()}")
+        buf = (C.c_byte * (n * dtype.itemsize)).from_address(p)
+        return np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+    PROFILE_STAGES = ("route", "dispatch", "gate_up", "quant_hidden", "down", "combine", "rmsnorm", "other")
+
+    def profile_enable(self, on: bool):
+        self._check(self.lib.tc_profile_enable(self.handle, int(on)), "tc_profile_enable")
+
+    def profile_read(self) -> dict:
+        ms = np.zeros(8, np.float32)
+        n = np.zeros(8, np.uint64)
+        self._check(self.lib.tc_profile_read(self.handle, _ptr(ms), _ptr(n)), "tc_profile_read")
+        return {name: (float(ms[i]), int(n[i])) for i, name in enumerate(self.PROFILE_STAGES)}
 
     def to_device(self, host: np.ndarray) -> "DeviceArray":
         arr = DeviceArray(self, host.shape, host.dtype)
