@@ -42,6 +42,15 @@ int tc_sync(tc_ctx *ctx);
 /* The context's stream as a cudaStream_t, for callers that enqueue their own work. */
 void *tc_stream(tc_ctx *ctx);
 
+/* How the expert products add up a row's 32-element blocks (src/kernels_x86.rs:79-129).
+ * TC_ARITH_FAST (default): one fma chain per output over the exact integer
+ *   block sums, blocks in order; the same on every kernel, so a token's result
+ *   does not depend on its batch. Differs from the CPU path by float rounding only.
+ * TC_ARITH_CPU_LANES: the CPU path's own eight-lane order and hsum tree:
+ *   bit-identical to Tachyon's AVX2 kernels, at about five times the instructions. */
+enum { TC_ARITH_FAST = 0, TC_ARITH_CPU_LANES = 1 };
+int tc_set_arithmetic(tc_ctx *ctx, int mode);
+
 /* ---- device buffers: replace tm_buffer / tm_buffer_contents / tm_buffer_free
  *      (src/gpu/mod.rs:125-127). HBM is not host-visible, hence the copies. */
 void *tc_malloc(tc_ctx *ctx, size_t bytes);

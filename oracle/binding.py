@@ -87,6 +87,7 @@ def _declare(L: C.CDLL) -> None:
         "to_moe": (None, [sz, sz, sz, sz, vp, i32, vp, vp, i32, vp, vp, vp, sz, vp, vp, vp, vp, vp, vp, i32]),
         "to_add_inplace": (None, [vp, vp, sz]),
         "to_default_threads": (i32, []),
+        "to_set_arith": (None, [i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -283,6 +284,18 @@ def route(scores, k: int):
     gates = np.empty(k, np.float32)
     lib().to_route(_p(scores), scores.size, k, _p(ids), _p(gates))
     return ids, gates
+
+
+class fast_arithmetic_model:
+    """Context manager: inside it, quantized matmuls (and so ``moe``) use the
+    single-fma-chain order of the CUDA backend's fast kernels instead of the
+    reference's eight-lane order. A model of the GPU, not of Tachyon."""
+
+    def __enter__(self):
+        lib().to_set_arith(1)
+
+    def __exit__(self, *exc):
+        lib().to_set_arith(0)
 
 
 def default_threads() -> int:

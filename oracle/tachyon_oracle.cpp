@@ -526,6 +526,42 @@ float dot_q4_scalar(const float* ws, size_t nb, const uint8_t* wq, const float* 
     return total;
 }
 
+// ------------------------------------------------- model of the GPU's fast arithmetic
+//
+// NOT a restatement of the reference: the CUDA backend's default ("fast")
+// arithmetic folds a block's eight AVX lanes into one exact integer sum and
+// keeps a single fma chain per output, blocks in order. These two functions
+// state that order on the CPU so the fast kernels can be pinned bit for bit;
+// how far it sits from the reference order above is what the tolerance tests
+// measure.
+float dot_q8_chain(const float* ws, size_t nb, const int8_t* wq, const float* xs, const int8_t* xq) {
+    float acc = 0.0f;
+    for (size_t b = 0; b < nb; b++) {
+        int32_t s = 0;
+        for (int j = 0; j < QK; j++) s += int32_t(wq[b * QK + j]) * int32_t(xq[b * QK + j]);
+        acc = std::fmaf(float(s), ws[b] * xs[b], acc);
+    }
+    return acc;
+}
+
+float dot_q4_chain(const float* ws, const float* cs, size_t nb, const uint8_t* wq, const float* xs,
+                   const int8_t* xq, const float* sums) {
+    float acc = 0.0f, off = 0.0f;
+    for (size_t b = 0; b < nb; b++) {
+        int32_t s = 0;
+        for (int j = 0; j < QK / 2; j++) {
+            uint8_t byte = wq[b * QK / 2 + j];
+            s += (int32_t(byte & 0xF) - 8) * int32_t(xq[b * QK + j]);
+            s += (int32_t(byte >> 4) - 8) * int32_t(xq[b * QK + j + QK / 2]);
+        }
+        acc = std::fmaf(float(s), ws[b] * xs[b], acc);
+        off = std::fmaf(cs[b], sums[b], off);
+    }
+    return acc + off;
+}
+
+int g_arith = 0;  // 0: the reference's lane order; 1: the chain model above
+
 // ------------------------------------------------- offsets (kernels.rs:392-432)
 
 // Eight lanes, one per block of a super-block, fma'd over super-blocks, then
@@ -748,6 +784,26 @@ void int_matmul(Pool& pool, const MatrixView& m, size_t row0, size_t rows, const
     const int8_t* q8 = static_cast<const int8_t*>(m.data);
     const uint8_t* q4d = static_cast<const uint8_t*>(m.data);
 
+    if (g_arith == 1) {
+        pool.parallel_for(rows, grain, [&](size_t ra, size_t rb) {
+            std::vector<float> d(padded), c(padded);
+            for (size_t r = ra; r < rb; r++) {
+                size_t row = row0 + r;
+                if (!q4)
+                    for (size_t b = 0; b < nb; b++) d[b] = f16_finite(s8[row * nb + b]);
+                else
+                    unpack_q4(s4 + row * words, padded, d.data(), c.data());
+                for (size_t i = 0; i < t; i++)
+                    out[i * rows + r] =
+                        q4 ? dot_q4_chain(d.data(), c.data(), nb, q4d + row * cols / 2,
+                                          xs.data() + i * nb, xq.data() + i * cols,
+                                          sums.data() + i * padded)
+                           : dot_q8_chain(d.data(), nb, q8 + row * cols, xs.data() + i * nb,
+                                          xq.data() + i * cols);
+            }
+        });
+        return;
+    }
     pool.parallel_for(rows, grain, [&](size_t ra, size_t rb) {
         if (t == 1) {
             for (size_t r = ra; r < rb; r++) {
@@ -1096,6 +1152,9 @@ void to_moe(size_t hidden, size_t experts, size_t k, size_t inter, const uint16_
 void to_add_inplace(float* x, const float* p, size_t n) {
     for (size_t i = 0; i < n; i++) x[i] += p[i];
 }
+
+// 0 (default): the reference's arithmetic. 1: the model of the GPU's fast order.
+void to_set_arith(int mode) { g_arith = mode; }
 
 int to_default_threads() {
     // src/pool.rs:71-88 on Linux: all cores, less two when there are more than four.

@@ -24,6 +24,7 @@ struct tc_ctx {
     bool capturing = false;
     uint64_t launches_before_capture = 0;
     bool profiling = false;
+    int arith = tc::ARITH_FAST;
     std::vector<cudaEvent_t> ev_pool;                      // reused across reads
     size_t ev_used = 0;
     struct Span { int stage; size_t a, b; int launches; };
@@ -186,7 +187,8 @@ tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
     ctx->device = device_ordinal;
     ctx->sms = prop.multiProcessorCount;
     ctx->name = prop.name;
-    tc::init_kernels();
+    tc::init_kernels_exact();
+    tc::init_kernels_fast();
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_stop) != cudaSuccess) {
@@ -277,6 +279,12 @@ void* tc_host_alloc(tc_ctx* ctx, size_t bytes) {
 void tc_host_free(tc_ctx* ctx, void* host) {
     (void)ctx;
     if (host) cudaFreeHost(host);
+}
+
+int tc_set_arithmetic(tc_ctx* ctx, int mode) {
+    if (mode != TC_ARITH_FAST && mode != TC_ARITH_CPU_LANES) return fail(ctx, "unknown arithmetic mode %d", mode);
+    ctx->arith = mode;
+    return 0;
 }
 
 int tc_profile_enable(tc_ctx* ctx, int on) {
@@ -421,9 +429,16 @@ int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
                                 x, t, ws, s);
     });
     n += staged(ctx, 1, [&] { return tc::launch_dispatch(d, t, ws, s); });
-    n += staged(ctx, 2, [&] { return tc::launch_gate_up(d, layer->gate_up->dev, t, ws, ctx->sms, s); });
+    const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
+    n += staged(ctx, 2, [&] {
+        return lanes ? tc::launch_gate_up_exact(d, layer->gate_up->dev, t, ws, ctx->sms, s)
+                     : tc::launch_gate_up_fast(d, layer->gate_up->dev, t, ws, ctx->sms, s);
+    });
     n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
-    n += staged(ctx, 4, [&] { return tc::launch_down(d, layer->down->dev, t, ws, ctx->sms, s); });
+    n += staged(ctx, 4, [&] {
+        return lanes ? tc::launch_down_exact(d, layer->down->dev, t, ws, ctx->sms, s)
+                     : tc::launch_down_fast(d, layer->down->dev, t, ws, ctx->sms, s);
+    });
     n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
     ctx->launches += n;
     layer->last_t = t;

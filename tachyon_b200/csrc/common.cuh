@@ -58,8 +58,21 @@ struct MoeDims {
     int hidden, experts, topk, inter;
 };
 
-// Opts the kernels that need it into large dynamic shared memory (once per device).
-void init_kernels();
+// Opt the kernels that need it into large dynamic shared memory (once per device).
+void init_kernels_exact();
+void init_kernels_fast();
+
+// How the expert products add up a row's 32-element blocks.
+enum : int {
+    // One fma chain per output, blocks in order: acc = fma(float(block sum),
+    // ws*xs, acc). The same on every fast path, so a token's result does not
+    // depend on what it is batched with.
+    ARITH_FAST = 0,
+    // The CPU path's own order: eight float lanes per output, each block's sum
+    // split across them four products at a time, then the AVX2 hsum tree.
+    // Bit-identical to src/kernels_x86.rs; about five times the instructions.
+    ARITH_CPU_LANES = 1,
+};
 
 // ---- launchers (each enqueues on `stream` and returns the number of kernels launched)
 
@@ -72,15 +85,19 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
 int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
 
 // gate_up rows of each expert times its tokens, SwiGLU, into ws.hidden_f.
-int launch_gate_up(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
-                   cudaStream_t stream);
+int launch_gate_up_exact(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
+                         cudaStream_t stream);
+int launch_gate_up_fast(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
+                        cudaStream_t stream);
 
 // 8-bit quantization of ws.hidden_f rows into ws.hq / ws.hs / ws.hsum.
 int launch_quant_hidden(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
 
 // down rows of each expert times its tokens' hidden rows, into ws.out.
-int launch_down(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
-                cudaStream_t stream);
+int launch_down_exact(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
+                      cudaStream_t stream);
+int launch_down_fast(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
+                     cudaStream_t stream);
 
 // y[i] += sum over the token's experts, ascending expert index, gate * out.
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);

@@ -27,6 +27,7 @@ SYMBOLS = {
     "tc_last_error": (_sz, [_vp, C.c_char_p, _sz]),
     "tc_sync": (_i, [_vp]),
     "tc_stream": (_vp, [_vp]),
+    "tc_set_arithmetic": (_i, [_vp, _i]),
     "tc_malloc": (_vp, [_vp, _sz]),
     "tc_free": (None, [_vp, _vp]),
     "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
@@ -127,6 +128,12 @@ class Context:
         buf = C.create_string_buffer(256)
         self.lib.tc_device_name(self.handle, buf, len(buf))
         return buf.value.decode()
+
+    ARITH_FAST, ARITH_CPU_LANES = 0, 1
+
+    def set_arithmetic(self, mode: int):
+        """ARITH_FAST (default) or ARITH_CPU_LANES (bit-identical to the CPU path)."""
+        self._check(self.lib.tc_set_arithmetic(self.handle, mode), "tc_set_arithmetic")
 
     def sync(self):
         self._check(self.lib.tc_sync(self.handle), "tc_sync")
