@@ -33,6 +33,7 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
     float* yr = y + size_t(token) * hidden;
     for (int c = tid * 4; c < hidden; c += COMBINE_THREADS * 4) {
         float4 proj = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
         for (int j = 0; j < topk; j++) {
             const float g = s_gate[j];
             const float4 v = *reinterpret_cast<const float4*>(out + size_t(s_pos[j]) * hidden + c);

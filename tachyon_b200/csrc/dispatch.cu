@@ -4,10 +4,13 @@
 // The CPU path pushes each token's picks onto per-expert lists while walking
 // tokens in order (src/model.rs:474-482), so within an expert the slots are in
 // ascending token order and counts[e] is the list length. This file produces
-// the same lists without a serial walk: a thread per token, a warp ballot per
-// expert for the rank of a token among the earlier tokens of its CTA that
-// picked the same expert, per-CTA histograms scanned across CTAs for the base,
-// and a warp-shuffle exclusive scan over experts for each expert's first slot.
+// the same lists without a serial walk. A CTA owns 256 consecutive tokens, a
+// thread per token. Each thread sets one bit per pick in a shared bit matrix
+// (expert x token); a token's rank among the CTA's earlier tokens that picked
+// the same expert is then a popcount of that expert's row below its own bit.
+// Per-CTA histograms (row popcounts) are scanned across CTAs for the CTA's
+// base, and a warp-shuffle exclusive scan over experts gives each expert's
+// first slot.
 //
 // Outputs: counts[E], offsets[E+1], perm[sorted slot] = token*k + j,
 // pos[token*k + j] = sorted slot.
@@ -20,22 +23,35 @@ namespace {
 constexpr int DISPATCH_THREADS = 256;
 constexpr int DISPATCH_WARPS = DISPATCH_THREADS / 32;
 
-// Ballot pass over every expert. Each thread owns one token (or none) with its
-// k picks in `mine`. For expert e the warp learns which lanes picked it;
-// `on_expert(e, ballot, j)` runs on every lane, with j = the lane's pick index
-// for e or -1.
-template <class F>
-__device__ __forceinline__ void for_each_expert(int experts, int topk, const uint32_t* mine,
-                                                bool has_token, F on_expert) {
-    for (int e = 0; e < experts; e++) {
-        int j = -1;
-        if (has_token) {
-            for (int q = 0; q < topk; q++)
-                if (mine[q] == uint32_t(e)) j = q;
-        }
-        unsigned ballot = __ballot_sync(0xffffffffu, j >= 0);
-        on_expert(e, ballot, j);
+// Sets this token's bits and returns with bits[e][w] complete (after a CTA barrier).
+__device__ __forceinline__ void mark_picks(uint32_t (*bits)[DISPATCH_WARPS], const uint32_t* ids,
+                                           int token, int t, int experts, int topk) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < experts * DISPATCH_WARPS; i += DISPATCH_THREADS) (&bits[0][0])[i] = 0;
+    __syncthreads();
+    if (token < t) {
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int q = 0; q < topk; q++)
+            atomicOr(&bits[ids[size_t(token) * topk + q]][warp], 1u << lane);
     }
+    __syncthreads();
+}
+
+__device__ __forceinline__ uint32_t row_count(const uint32_t (*bits)[DISPATCH_WARPS], int e) {
+    uint32_t n = 0;
+#pragma unroll
+    for (int w = 0; w < DISPATCH_WARPS; w++) n += __popc(bits[e][w]);
+    return n;
+}
+
+// Tokens of this CTA before `tid` that picked expert e.
+__device__ __forceinline__ uint32_t rank_in_cta(const uint32_t (*bits)[DISPATCH_WARPS], int e, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    uint32_t n = __popc(bits[e][warp] & ((1u << lane) - 1u));
+#pragma unroll
+    for (int w = 0; w < DISPATCH_WARPS; w++)
+        if (w < warp) n += __popc(bits[e][w]);
+    return n;
 }
 
 // Exclusive scan of counts[0..experts) into offsets[0..experts], by one warp:
@@ -71,63 +87,40 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
 dispatch_small_kernel(const uint32_t* __restrict__ ids, int t, int experts, int topk,
                       uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
                       uint32_t* __restrict__ perm, uint32_t* __restrict__ pos) {
-    __shared__ uint32_t wcount[DISPATCH_WARPS][MAX_EXPERTS];  // per-warp counts, then bases
+    __shared__ uint32_t bits[MAX_EXPERTS][DISPATCH_WARPS];
     __shared__ uint32_t scount[MAX_EXPERTS];
     __shared__ uint32_t soff[MAX_EXPERTS + 1];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool has = tid < t;
-    uint32_t mine[MAX_TOPK];
-    if (has)
-        for (int q = 0; q < topk; q++) mine[q] = ids[size_t(tid) * topk + q];
-    for_each_expert(experts, topk, mine, has, [&](int e, unsigned ballot, int) {
-        if (lane == 0) wcount[warp][e] = __popc(ballot);
-    });
-    __syncthreads();
+    const int tid = threadIdx.x;
+    mark_picks(bits, ids, tid, t, experts, topk);
     for (int e = tid; e < experts; e += DISPATCH_THREADS) {
-        uint32_t run = 0;
-        for (int w = 0; w < DISPATCH_WARPS; w++) {
-            uint32_t c = wcount[w][e];
-            wcount[w][e] = run;
-            run += c;
-        }
-        scount[e] = run;
-        counts[e] = run;
+        const uint32_t n = row_count(bits, e);
+        scount[e] = n;
+        counts[e] = n;
     }
     __syncthreads();
-    if (warp == 0) scan_experts(scount, soff, experts, lane);
+    if (tid < 32) scan_experts(scount, soff, experts, tid);
     __syncthreads();
     for (int e = tid; e <= experts; e += DISPATCH_THREADS) offsets[e] = soff[e];
-    const unsigned lt = (1u << lane) - 1u;
-    for_each_expert(experts, topk, mine, has, [&](int e, unsigned ballot, int j) {
-        if (j >= 0) {
-            uint32_t p = soff[e] + wcount[warp][e] + __popc(ballot & lt);
-            uint32_t slot = uint32_t(tid) * topk + j;
+    if (tid < t) {
+        for (int q = 0; q < topk; q++) {
+            const uint32_t slot = uint32_t(tid) * topk + q;
+            const int e = ids[slot];
+            const uint32_t p = soff[e] + rank_in_cta(bits, e, tid);
             perm[p] = slot;
             pos[slot] = p;
         }
-    });
+    }
 }
 
 // Large batches, pass 1: each CTA's histogram of its DISPATCH_THREADS tokens.
 __global__ void __launch_bounds__(DISPATCH_THREADS)
 dispatch_count_kernel(const uint32_t* __restrict__ ids, int t, int experts, int topk,
                       uint32_t* __restrict__ block_hist) {
-    __shared__ uint32_t wcount[DISPATCH_WARPS][MAX_EXPERTS];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int token = blockIdx.x * DISPATCH_THREADS + tid;
-    const bool has = token < t;
-    uint32_t mine[MAX_TOPK];
-    if (has)
-        for (int q = 0; q < topk; q++) mine[q] = ids[size_t(token) * topk + q];
-    for_each_expert(experts, topk, mine, has, [&](int e, unsigned ballot, int) {
-        if (lane == 0) wcount[warp][e] = __popc(ballot);
-    });
-    __syncthreads();
-    for (int e = tid; e < experts; e += DISPATCH_THREADS) {
-        uint32_t run = 0;
-        for (int w = 0; w < DISPATCH_WARPS; w++) run += wcount[w][e];
-        block_hist[size_t(blockIdx.x) * experts + e] = run;
-    }
+    __shared__ uint32_t bits[MAX_EXPERTS][DISPATCH_WARPS];
+    const int tid = threadIdx.x;
+    mark_picks(bits, ids, blockIdx.x * DISPATCH_THREADS + tid, t, experts, topk);
+    for (int e = tid; e < experts; e += DISPATCH_THREADS)
+        block_hist[size_t(blockIdx.x) * experts + e] = row_count(bits, e);
 }
 
 // Pass 2 (one CTA): per expert, scan the CTA histograms into CTA bases; then
@@ -160,35 +153,20 @@ dispatch_permute_kernel(const uint32_t* __restrict__ ids, int t, int experts, in
                         const uint32_t* __restrict__ block_base,
                         const uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm,
                         uint32_t* __restrict__ pos) {
-    __shared__ uint32_t wcount[DISPATCH_WARPS][MAX_EXPERTS];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ uint32_t bits[MAX_EXPERTS][DISPATCH_WARPS];
+    const int tid = threadIdx.x;
     const int token = blockIdx.x * DISPATCH_THREADS + tid;
-    const bool has = token < t;
-    uint32_t mine[MAX_TOPK];
-    if (has)
-        for (int q = 0; q < topk; q++) mine[q] = ids[size_t(token) * topk + q];
-    for_each_expert(experts, topk, mine, has, [&](int e, unsigned ballot, int) {
-        if (lane == 0) wcount[warp][e] = __popc(ballot);
-    });
-    __syncthreads();
-    for (int e = tid; e < experts; e += DISPATCH_THREADS) {
-        uint32_t run = offsets[e] + block_base[size_t(blockIdx.x) * experts + e];
-        for (int w = 0; w < DISPATCH_WARPS; w++) {
-            uint32_t c = wcount[w][e];
-            wcount[w][e] = run;
-            run += c;
-        }
-    }
-    __syncthreads();
-    const unsigned lt = (1u << lane) - 1u;
-    for_each_expert(experts, topk, mine, has, [&](int e, unsigned ballot, int j) {
-        if (j >= 0) {
-            uint32_t p = wcount[warp][e] + __popc(ballot & lt);
-            uint32_t slot = uint32_t(token) * topk + j;
+    mark_picks(bits, ids, token, t, experts, topk);
+    if (token < t) {
+        for (int q = 0; q < topk; q++) {
+            const uint32_t slot = uint32_t(token) * topk + q;
+            const int e = ids[slot];
+            const uint32_t p = offsets[e] + block_base[size_t(blockIdx.x) * experts + e] +
+                               rank_in_cta(bits, e, tid);
             perm[p] = slot;
             pos[slot] = p;
         }
-    });
+    }
 }
 
 }  // namespace

@@ -69,6 +69,7 @@ route_quant_kernel(const uint16_t* __restrict__ router, const float* __restrict_
             const bool valid = e < experts;
             const uint16_t* w = router + size_t(valid ? e : 0) * hidden;
             float acc = 0.0f;
+#pragma unroll 16
             for (int c = L; c < hidden; c += 16) acc = fmaf(bf16_bits_to_f32(w[c]), xrow[c], acc);
             // acc0 + acc1 lane-wise (lanes L and L+8), then the hsum tree.
             float v = acc + __shfl_down_sync(0xffffffffu, acc, 8, 16);
@@ -179,6 +180,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
     const float* xr = x + size_t(row) * n;
     float acc = 0.0f;
     int i = 0;
+#pragma unroll 16
     for (; i + 32 <= n; i += 32) {
         float v = xr[i + lane];
         acc = fmaf(v, v, acc);
@@ -201,6 +203,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
     const float ss = __fdiv_rn(s, float(n));
     const float inv = __fdiv_rn(1.0f, __fsqrt_rn(ss + eps));
     float* o = out + size_t(row) * n;
+#pragma unroll 8
     for (int c = lane; c < n; c += 32) o[c] = xr[c] * inv * w[c];
 }
 
