@@ -48,6 +48,8 @@ struct tc_moe_layer {
     float* bias = nullptr;
     int max_tokens;
     int last_t = 0;
+    uint8_t* gate_up_tiled = nullptr;  // the fast kernels' record layout of the two expert matrices
+    uint8_t* down_tiled = nullptr;
 };
 
 struct tc_graph {
@@ -393,13 +395,31 @@ tc_moe_layer* tc_moe_layer_create(tc_ctx* ctx, int hidden, int experts, int k, i
     cudaSetDevice(ctx->device);
     tc::MoeDims d{hidden, experts, k, inter};
     if (!ws_reserve(ctx, d, max_tokens)) return nullptr;
+    if (!tc::fast_path_fits(d, gate_up->dev, down->dev)) return bad("hidden or intermediate size too large for the staged-token buffers");
     tc_moe_layer* l = new tc_moe_layer{ctx, d, router, gate_up, down, nullptr, max_tokens, 0};
+    void *gu = nullptr, *dn = nullptr;
+    if (!cuda_ok(ctx, cudaMalloc(&gu, tc::tiled_bytes(d, gate_up->dev, true) + 256), "cudaMalloc(tiled gate_up)") ||
+        !cuda_ok(ctx, cudaMalloc(&dn, tc::tiled_bytes(d, down->dev, false) + 256), "cudaMalloc(tiled down)")) {
+        if (gu) cudaFree(gu);
+        delete l;
+        return nullptr;
+    }
+    l->gate_up_tiled = static_cast<uint8_t*>(gu);
+    l->down_tiled = static_cast<uint8_t*>(dn);
+    tc::tile_weights(d, gate_up->dev, true, l->gate_up_tiled, ctx->stream);
+    tc::tile_weights(d, down->dev, false, l->down_tiled, ctx->stream);
+    if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "weight tiling")) {
+        tc_moe_layer_free(l);
+        return nullptr;
+    }
     return l;
 }
 
 void tc_moe_layer_free(tc_moe_layer* layer) {
     if (!layer) return;
     if (layer->bias) cudaFree(layer->bias);
+    if (layer->gate_up_tiled) cudaFree(layer->gate_up_tiled);
+    if (layer->down_tiled) cudaFree(layer->down_tiled);
     delete layer;
 }
 
@@ -432,12 +452,12 @@ int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
     const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
     n += staged(ctx, 2, [&] {
         return lanes ? tc::launch_gate_up_exact(d, layer->gate_up->dev, t, ws, ctx->sms, s)
-                     : tc::launch_gate_up_fast(d, layer->gate_up->dev, t, ws, ctx->sms, s);
+                     : tc::launch_gate_up_fast(d, layer->gate_up->dev, layer->gate_up_tiled, t, ws, ctx->sms, s);
     });
     n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
     n += staged(ctx, 4, [&] {
         return lanes ? tc::launch_down_exact(d, layer->down->dev, t, ws, ctx->sms, s)
-                     : tc::launch_down_fast(d, layer->down->dev, t, ws, ctx->sms, s);
+                     : tc::launch_down_fast(d, layer->down->dev, layer->down_tiled, t, ws, ctx->sms, s);
     });
     n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
     ctx->launches += n;

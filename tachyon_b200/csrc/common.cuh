@@ -87,8 +87,14 @@ int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream)
 // gate_up rows of each expert times its tokens, SwiGLU, into ws.hidden_f.
 int launch_gate_up_exact(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
                          cudaStream_t stream);
-int launch_gate_up_fast(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
-                        cudaStream_t stream);
+int launch_gate_up_fast(const MoeDims& d, const MatrixDev& gate_up, const uint8_t* tiled, int t,
+                        Workspace& ws, int sms, cudaStream_t stream);
+
+// The fast kernels read weights re-tiled into per-(unit, 256-column chunk)
+// records; these size, check and build that copy when a layer is created.
+size_t tiled_bytes(const MoeDims& d, const MatrixDev& m, bool gate_up);
+bool fast_path_fits(const MoeDims& d, const MatrixDev& gate_up, const MatrixDev& down);
+void tile_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, uint8_t* tiled, cudaStream_t stream);
 
 // 8-bit quantization of ws.hidden_f rows into ws.hq / ws.hs / ws.hsum.
 int launch_quant_hidden(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
@@ -96,8 +102,8 @@ int launch_quant_hidden(const MoeDims& d, int t, Workspace& ws, cudaStream_t str
 // down rows of each expert times its tokens' hidden rows, into ws.out.
 int launch_down_exact(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
                       cudaStream_t stream);
-int launch_down_fast(const MoeDims& d, const MatrixDev& down, int t, Workspace& ws, int sms,
-                     cudaStream_t stream);
+int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, int t,
+                     Workspace& ws, int sms, cudaStream_t stream);
 
 // y[i] += sum over the token's experts, ascending expert index, gate * out.
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);

@@ -13,16 +13,22 @@
 // their per-block offsets with a second chain in the same loop:
 // off = fma(c[row,b], xs[token,b]*sum(xq), off) (src/weights.rs:491-520).
 //
-// This kernel is bound by HBM, not by the tensor pipe: at decode sizes every
+// The kernel is bound by HBM, not by the tensor pipe: at decode sizes every
 // selected expert's weights are read once and used for a handful of tokens.
-// So the design is about bytes in flight. Persistent CTAs, one per SM; the
-// units of work (16 weight rows of an expert with tokens) are cut into equal
-// contiguous ranges per CTA; each warp streams its units' rows through a deep
-// private ring of shared-memory stages with bulk async copies (one 256-byte
-// row chunk per lane) counted on an mbarrier per stage. Rows are padded by 16
-// bytes in shared memory so ldmatrix reads hit 32 distinct banks. Activations
-// are tiny and shared by every warp working on the expert: they are read
-// through L1. Every mbarrier wait has a spin limit.
+// So the design is about bytes in flight and about keeping the loop off global
+// memory:
+//  - Weights are re-tiled once, when a layer is created, into records of one
+//    unit (16 rows) x one 256-column chunk: 16 rows of [weights | that row's
+//    block scales], row stride 272 bytes (8-bit) or 144 bytes (4-bit). One
+//    record is one bulk async copy and lands in shared memory already padded
+//    so that ldmatrix reads hit 32 distinct banks.
+//  - Persistent CTAs, one per SM; the units of experts that have tokens are
+//    cut into equal contiguous ranges per CTA; each warp streams its units'
+//    records through a private ring of shared-memory stages, completion
+//    counted on an mbarrier per stage (every wait has a spin limit).
+//  - The tokens of the expert a CTA is working on (up to 32 at a time) are
+//    staged once per CTA: int8 rows by bulk copies, their scales transposed by
+//    plain loads.
 #include "experts_common.cuh"
 
 namespace tc {
@@ -31,24 +37,53 @@ namespace {
 
 constexpr int F_WARPS = 8;
 constexpr int F_THREADS = F_WARPS * 32;
-constexpr int F_KC = 256;         // columns per staged chunk
-constexpr int F_NBC = F_KC / QK;  // blocks per chunk
+constexpr int F_KC = 256;         // columns per record
+constexpr int F_NBC = F_KC / QK;  // blocks per record
 constexpr int F_ROWS = 16;        // weight rows per unit (one m16 tile)
-constexpr int F_GMAX = 4;         // token tiles of 8 held in registers (32 tokens)
+constexpr int F_GMAX = 4;         // token tiles of 8 held in registers
+constexpr int F_TOK = 8 * F_GMAX; // tokens staged per segment
+constexpr int F_MAX_STAGES = 8;
+constexpr size_t F_SMEM_LIMIT = 227 * 1024;
 
 template <int KIND>
-struct FStage {
-    static constexpr int W_CHUNK = KIND == 1 ? F_KC : F_KC / 2;
-    static constexpr int W_STRIDE = W_CHUNK + 16;
-    static constexpr int BYTES = F_ROWS * W_STRIDE;
-    static constexpr int STAGES = KIND == 1 ? 6 : 10;
+struct Rec {
+    // 8-bit: 16 rows x (256 weights + 8 f16 scales).
+    // 4-bit: 16 rows x (128 nibble bytes + words 0..3 of the super-block), then
+    //        word 4 of each row.
+    static constexpr int ROW_STRIDE = KIND == 1 ? F_KC + 16 : F_KC / 2 + 16;
+    static constexpr int BYTES = KIND == 1 ? F_ROWS * ROW_STRIDE : F_ROWS * ROW_STRIDE + F_ROWS * 4;
 };
 
+struct FastArgs {
+    ExpertArgs e;
+    const uint8_t* tiled;  // records [expert][unit][chunk]
+    int stages;            // ring depth per warp
+    int x_stride;          // bytes per staged activation row (cols + 16)
+    int nbp;               // pad8(cols / 32)
+};
+
+// Shared memory carve-up (offsets in bytes).
 template <int KIND>
-constexpr size_t fast_smem_bytes() {
-    return size_t(F_WARPS) * FStage<KIND>::STAGES * FStage<KIND>::BYTES +
-           size_t(F_WARPS) * FStage<KIND>::STAGES * sizeof(uint64_t) + MAX_EXPERTS * sizeof(int) + 16;
-}
+struct Layout {
+    int ring, bars, xq, xsT, xsumT, active, total;
+    __host__ __device__ Layout(int stages, int cols, int nbp) {
+        int o = 0;
+        ring = o;
+        o += F_WARPS * stages * Rec<KIND>::BYTES;
+        o = (o + 127) / 128 * 128;
+        xq = o;
+        o += F_TOK * (cols + 16);
+        xsT = o;
+        o += nbp * F_TOK * 4;
+        xsumT = o;
+        if (KIND == 2) o += nbp * F_TOK * 4;
+        active = o;
+        o += (MAX_EXPERTS + 4) * 4;
+        bars = o;
+        o += (F_WARPS * F_MAX_STAGES + 1) * 8;
+        total = o;
+    }
+};
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, int& r0, int& r1, int& r2, int& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -62,7 +97,7 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t addr, int& r0, int& r1) {
                  : "r"(addr));
 }
 
-// D = A(16x32 s8, row) * B(32x8 s8, col) + C, s32 accumulate.
+// D = A(16x32 s8, row) * B(32x8 s8, col) + c, s32 accumulate.
 __device__ __forceinline__ void mma_s8(int (&d)[4], int a0, int a1, int a2, int a3, int b0, int b1,
                                        int c) {
     asm volatile(
@@ -72,175 +107,165 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], int a0, int a1, int a2, int 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
 }
 
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+// A warp's place in its sequence of (expert, token segment, unit, chunk) steps.
+// Units are numbered over the experts that have tokens; a CTA owns [lo, hi).
 struct FCursor {
-    int a;        // index in the space of active units
-    int e, u;     // expert, unit within the expert
-    int sg0, c;   // first token of the 32-token super-group, column chunk
-    uint32_t m, base;
+    int ai;       // index into the active-expert list
+    int sg0;      // first token of the segment
+    int a;        // unit (in active-unit space)
+    int c;        // chunk
+    int seg_hi;   // end of this CTA's units of expert ai
+    uint32_t m;   // tokens of the expert
+    int e;        // expert id
     bool valid;
 };
 
 template <int KIND, bool GATE_UP>
-struct FWorker {
-    const ExpertArgs& a;
-    const int* active;  // shared: experts with tokens, ascending
-    const int lane, nchunks, hi;
+struct FWalker {
+    const FastArgs& f;
+    const int* active;
+    const int warp, lo, hi, nchunks, upe;
 
-    __device__ FWorker(const ExpertArgs& args, const int* act, int lane_, int hi_)
-        : a(args), active(act), lane(lane_), nchunks((args.cols + F_KC - 1) / F_KC), hi(hi_) {}
+    __device__ FWalker(const FastArgs& args, const int* act, int warp_, int lo_, int hi_)
+        : f(args), active(act), warp(warp_), lo(lo_), hi(hi_),
+          nchunks((args.e.cols + F_KC - 1) / F_KC), upe(args.e.units_per_expert) {}
 
-    __device__ void seek(FCursor& cur) const {
-        if (cur.a >= hi) {
-            cur.valid = false;
-            return;
+    // Positions at the warp's first unit of (ai, sg0) or of the next segment that has one.
+    __device__ void settle(FCursor& cur) const {
+        for (;;) {
+            if (cur.ai * upe >= hi) {
+                cur.valid = false;
+                return;
+            }
+            cur.e = active[cur.ai];
+            cur.m = f.e.counts[cur.e];
+            const int seg_lo = max(lo, cur.ai * upe);
+            cur.seg_hi = min(hi, (cur.ai + 1) * upe);
+            if (uint32_t(cur.sg0) < cur.m) {
+                cur.a = seg_lo + warp;
+                if (cur.a < cur.seg_hi) {
+                    cur.c = 0;
+                    cur.valid = true;
+                    return;
+                }
+                cur.sg0 += F_TOK;  // no unit for this warp here: same answer for every segment
+                continue;
+            }
+            cur.ai++;
+            cur.sg0 = 0;
         }
-        const int ai = cur.a / a.units_per_expert;
-        cur.e = active[ai];
-        cur.u = cur.a - ai * a.units_per_expert;
-        cur.m = a.counts[cur.e];
-        cur.base = a.offsets[cur.e];
-        cur.sg0 = 0;
-        cur.c = 0;
-        cur.valid = true;
     }
 
     __device__ void advance(FCursor& cur) const {
         if (++cur.c < nchunks) return;
         cur.c = 0;
-        cur.sg0 += 8 * F_GMAX;
-        if (uint32_t(cur.sg0) < cur.m) return;
         cur.a += F_WARPS;
-        seek(cur);
+        if (cur.a < cur.seg_hi) return;
+        cur.sg0 += F_TOK;
+        settle(cur);
     }
 
-    // Matrix row of tile row r (0..15), or -1 past the expert's last row.
-    __device__ int matrix_row(const FCursor& cur, int r) const {
-        if (GATE_UP) {
-            const int inter = a.rows_per_expert / 2;
-            const int col = cur.u * 8 + (r & 7);
-            if (col >= inter) return -1;
-            return cur.e * a.rows_per_expert + (r < 8 ? 0 : inter) + col;
-        }
-        const int row = cur.u * F_ROWS + r;
-        if (row >= a.rows_per_expert) return -1;
-        return cur.e * a.rows_per_expert + row;
-    }
-
-    // Activation row of the expert's j-th token (clamped to its last one).
-    __device__ uint32_t act_row(const FCursor& cur, int j) const {
-        const uint32_t p = cur.base + min(uint32_t(j), cur.m - 1);
-        return GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
-    }
-
-    __device__ void fill(uint8_t* stage, uint64_t* bar, const FCursor& cur) const {
-        using S = FStage<KIND>;
-        const int col0 = cur.c * F_KC;
-        const int cols_c = min(F_KC, a.cols - col0);
-        const uint32_t wbytes = KIND == 1 ? cols_c : cols_c / 2;
-        int row = -1;
-        if (lane < F_ROWS) row = matrix_row(cur, lane);
-        const unsigned rows_mask = __ballot_sync(0xffffffffu, row >= 0);
-        if (lane == 0) mbar_expect_tx(bar, __popc(rows_mask) * wbytes);
-        __syncwarp();
-        if (row >= 0) {
-            const uint8_t* src = a.wdata + (KIND == 1 ? size_t(row) * a.cols + col0
-                                                      : (size_t(row) * a.cols + col0) / 2);
-            bulk_copy(stage + lane * S::W_STRIDE, src, wbytes, bar);
-        }
+    __device__ const uint8_t* record(const FCursor& cur) const {
+        const int u = cur.a - cur.ai * upe;
+        return f.tiled + (size_t(cur.e * upe + u) * nchunks + cur.c) * Rec<KIND>::BYTES;
     }
 };
 
-// Per-chunk weight-side scales of the two rows (g, g+8) a thread accumulates.
-struct RowScales {
-    float d[2][F_NBC];  // block scale
-    float c[2][F_NBC];  // 4-bit block offset (unused for 8-bit)
-};
-
-template <int KIND>
-__device__ __forceinline__ void load_row_scales(const ExpertArgs& a, int row, int nb, int chunk,
-                                                int nblk, float (&d)[F_NBC], float (&c)[F_NBC]) {
-    if (row < 0) {
-#pragma unroll
-        for (int b = 0; b < F_NBC; b++) d[b] = c[b] = 0.0f;
-        return;
-    }
+// One record (16 rows x up to 8 blocks) against G tiles of 8 staged tokens.
+template <int KIND, int G>
+__device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t xsT_s, uint32_t xsumT_s,
+                                           int x_stride, int nblk, int blk0, int lane,
+                                           float (&acc)[F_GMAX][4], float (&off)[F_GMAX][4]) {
+    using R = Rec<KIND>;
+    const int g = lane >> 2, t = lane & 3;
+    const int mat = lane >> 3, mr = lane & 7;
+    // This thread's two rows' scales for the record's eight blocks.
+    float wd[2][F_NBC], wc[2][F_NBC];
     if (KIND == 1) {
-        const uint16_t* sp = reinterpret_cast<const uint16_t*>(a.wscales) + size_t(row) * nb + chunk * F_NBC;
-        if ((nb & 7) == 0) {
-            const uint4 h = *reinterpret_cast<const uint4*>(sp);
-            const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
 #pragma unroll
-            for (int b = 0; b < F_NBC; b++) d[b] = f16_bits_to_f32(uint16_t(hw[b >> 1] >> (16 * (b & 1))));
-        } else {
+        for (int h = 0; h < 2; h++) {
+            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC);
+            const uint32_t hw[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-            for (int b = 0; b < F_NBC; b++) d[b] = b < nblk ? f16_bits_to_f32(sp[b]) : 0.0f;
+            for (int b = 0; b < F_NBC; b++) wd[h][b] = f16_bits_to_f32(uint16_t(hw[b >> 1] >> (16 * (b & 1))));
         }
     } else {
-        const int words_per_row = (nb + SUPER - 1) / SUPER * SUPER_WORDS;
-        const uint32_t* wp = reinterpret_cast<const uint32_t*>(a.wscales) + size_t(row) * words_per_row +
-                             chunk * SUPER_WORDS;
-        const uint32_t w0 = wp[0], s01 = wp[1], s23 = wp[2], o01 = wp[3], o23 = wp[4];
-        const float step_d = f16_bits_to_f32(uint16_t(w0)), step_c = f16_bits_to_f32(uint16_t(w0 >> 16));
 #pragma unroll
-        for (int b = 0; b < F_NBC; b++) {
-            d[b] = step_d * float(((b < 4 ? s01 : s23) >> (8 * (b & 3))) & 0xFFu);
-            c[b] = step_c * float(int(int8_t(uint8_t((b < 4 ? o01 : o23) >> (8 * (b & 3))))));
+        for (int h = 0; h < 2; h++) {
+            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC / 2);
+            const uint32_t o23 = lds32(rec + F_ROWS * R::ROW_STRIDE + (g + 8 * h) * 4);
+            const float step_d = f16_bits_to_f32(uint16_t(s.x)), step_c = f16_bits_to_f32(uint16_t(s.x >> 16));
+#pragma unroll
+            for (int b = 0; b < F_NBC; b++) {
+                wd[h][b] = step_d * float(((b < 4 ? s.y : s.z) >> (8 * (b & 3))) & 0xFFu);
+                wc[h][b] = step_c * float(int(int8_t(uint8_t((b < 4 ? s.w : o23) >> (8 * (b & 3))))));
+            }
         }
     }
-}
-
-// One staged chunk of 16 weight rows against G tiles of 8 tokens.
-template <int KIND, int G>
-__device__ __forceinline__ void fast_chunk(const ExpertArgs& a, uint32_t stage_addr, int nblk, int lane,
-                                           int col0, int nbp, int chunk, const RowScales& rs,
-                                           const uint32_t (&rowB)[F_GMAX],
-                                           const uint32_t (&rowC)[F_GMAX][2], float (&acc)[F_GMAX][4],
-                                           float (&off)[F_GMAX][4]) {
-    using S = FStage<KIND>;
-    const int t = lane & 3;
-    // ldmatrix row addresses: matrix = lane/8, row-in-matrix = lane%8.
-    const int mat = lane >> 3, mr = lane & 7;
     uint32_t a_addr;
     if (KIND == 1)
-        a_addr = stage_addr + (mr + (mat & 1) * 8) * S::W_STRIDE + (mat >> 1) * 16;
+        a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE + (mat >> 1) * 16;
     else
-        a_addr = stage_addr + (mr + (mat & 1) * 8) * S::W_STRIDE;
+        a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE;
+    // B: token row (mr) of tile nt, 16-byte half (mat & 1) of block b + (mat >> 1).
+    const uint32_t b_addr = xq_s + mr * x_stride + blk0 * 32 + (mat & 1) * 16 + (mat >> 1) * 32;
 #pragma unroll
-    for (int b = 0; b < F_NBC; b++) {
+    for (int b = 0; b < F_NBC; b += 2) {
         if (b < nblk) {
-            int a0, a1, a2, a3;
-            if (KIND == 1) {
-                ldmatrix_x4(a_addr + b * 32, a0, a1, a2, a3);
-            } else {
-                // Word t of rows g and g+8: low nibbles are elements 4t..4t+3,
-                // high nibbles elements 16+4t..16+4t+3.
-                int w0, w1;
-                ldmatrix_x2(a_addr + b * 16, w0, w1);
-                a0 = nibbles_minus8(uint32_t(w0) & 0x0F0F0F0Fu);
-                a2 = nibbles_minus8((uint32_t(w0) >> 4) & 0x0F0F0F0Fu);
-                a1 = nibbles_minus8(uint32_t(w1) & 0x0F0F0F0Fu);
-                a3 = nibbles_minus8((uint32_t(w1) >> 4) & 0x0F0F0F0Fu);
+            int a[2][4];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                if (KIND == 1) {
+                    ldmatrix_x4(a_addr + (b + k) * 32, a[k][0], a[k][1], a[k][2], a[k][3]);
+                } else {
+                    // Word t of rows g and g+8: low nibbles are elements 4t..4t+3,
+                    // high nibbles elements 16+4t..16+4t+3.
+                    int w0, w1;
+                    ldmatrix_x2(a_addr + (b + k) * 16, w0, w1);
+                    a[k][0] = nibbles_minus8(uint32_t(w0) & 0x0F0F0F0Fu);
+                    a[k][2] = nibbles_minus8((uint32_t(w0) >> 4) & 0x0F0F0F0Fu);
+                    a[k][1] = nibbles_minus8(uint32_t(w1) & 0x0F0F0F0Fu);
+                    a[k][3] = nibbles_minus8((uint32_t(w1) >> 4) & 0x0F0F0F0Fu);
+                }
             }
 #pragma unroll
             for (int nt = 0; nt < G; nt++) {
-                const int8_t* xrow = a.xq + size_t(rowB[nt]) * a.cols + col0 + b * 32 + 4 * t;
-                const int b0 = *reinterpret_cast<const int*>(xrow);
-                const int b1 = *reinterpret_cast<const int*>(xrow + 16);
-                int d[4];
-                mma_s8(d, a0, a1, a2, a3, b0, b1, MAGIC_I);
-                const float xs0 = a.xs[size_t(rowC[nt][0]) * nbp + chunk * F_NBC + b];
-                const float xs1 = a.xs[size_t(rowC[nt][1]) * nbp + chunk * F_NBC + b];
-                acc[nt][0] = fmaf(__int_as_float(d[0]) - MAGIC_F, rs.d[0][b] * xs0, acc[nt][0]);
-                acc[nt][1] = fmaf(__int_as_float(d[1]) - MAGIC_F, rs.d[0][b] * xs1, acc[nt][1]);
-                acc[nt][2] = fmaf(__int_as_float(d[2]) - MAGIC_F, rs.d[1][b] * xs0, acc[nt][2]);
-                acc[nt][3] = fmaf(__int_as_float(d[3]) - MAGIC_F, rs.d[1][b] * xs1, acc[nt][3]);
-                if (KIND == 2) {
-                    const float su0 = a.xsum[size_t(rowC[nt][0]) * nbp + chunk * F_NBC + b];
-                    const float su1 = a.xsum[size_t(rowC[nt][1]) * nbp + chunk * F_NBC + b];
-                    off[nt][0] = fmaf(rs.c[0][b], su0, off[nt][0]);
-                    off[nt][1] = fmaf(rs.c[0][b], su1, off[nt][1]);
-                    off[nt][2] = fmaf(rs.c[1][b], su0, off[nt][2]);
-                    off[nt][3] = fmaf(rs.c[1][b], su1, off[nt][3]);
+                int bq[4];  // blocks b and b+1: {b lo, b hi, b+1 lo, b+1 hi}
+                ldmatrix_x4(b_addr + nt * 8 * x_stride + b * 32, bq[0], bq[1], bq[2], bq[3]);
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    if (b + k < nblk) {
+                        int d[4];
+                        mma_s8(d, a[k][0], a[k][1], a[k][2], a[k][3], bq[2 * k], bq[2 * k + 1], MAGIC_I);
+                        const float2 xs = lds_f2(xsT_s + ((blk0 + b + k) * F_TOK + nt * 8 + 2 * t) * 4);
+                        acc[nt][0] = fmaf(__int_as_float(d[0]) - MAGIC_F, wd[0][b + k] * xs.x, acc[nt][0]);
+                        acc[nt][1] = fmaf(__int_as_float(d[1]) - MAGIC_F, wd[0][b + k] * xs.y, acc[nt][1]);
+                        acc[nt][2] = fmaf(__int_as_float(d[2]) - MAGIC_F, wd[1][b + k] * xs.x, acc[nt][2]);
+                        acc[nt][3] = fmaf(__int_as_float(d[3]) - MAGIC_F, wd[1][b + k] * xs.y, acc[nt][3]);
+                        if (KIND == 2) {
+                            const float2 su = lds_f2(xsumT_s + ((blk0 + b + k) * F_TOK + nt * 8 + 2 * t) * 4);
+                            off[nt][0] = fmaf(wc[0][b + k], su.x, off[nt][0]);
+                            off[nt][1] = fmaf(wc[0][b + k], su.y, off[nt][1]);
+                            off[nt][2] = fmaf(wc[1][b + k], su.x, off[nt][2]);
+                            off[nt][3] = fmaf(wc[1][b + k], su.y, off[nt][3]);
+                        }
+                    }
                 }
             }
         }
@@ -248,17 +273,21 @@ __device__ __forceinline__ void fast_chunk(const ExpertArgs& a, uint32_t stage_a
 }
 
 template <int KIND, bool GATE_UP>
-__global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const ExpertArgs a) {
-    using S = FStage<KIND>;
-    constexpr int STAGES = S::STAGES;
+__global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArgs f) {
+    using R = Rec<KIND>;
+    const ExpertArgs& a = f.e;
     extern __shared__ __align__(128) uint8_t smem[];
+    const Layout<KIND> L(f.stages, a.cols, f.nbp);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint8_t* stages = smem + size_t(warp) * STAGES * S::BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + size_t(F_WARPS) * STAGES * S::BYTES) + warp * STAGES;
-    int* s_active = reinterpret_cast<int*>(smem + size_t(F_WARPS) * STAGES * (S::BYTES + sizeof(uint64_t)));
+    const int STAGES = f.stages;
+    uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
+    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L.bars) + F_WARPS * F_MAX_STAGES;
+    int* s_active = reinterpret_cast<int*>(smem + L.active);
     int* s_nactive = s_active + MAX_EXPERTS;
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
+        if (warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -275,146 +304,271 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const ExpertA
         if (lane == 0) *s_nactive = n;
     }
     __syncthreads();
-    const int total = *s_nactive * a.units_per_expert;
+    const int upe = a.units_per_expert;
+    const int total = *s_nactive * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
 
-    FWorker<KIND, GATE_UP> wk(a, s_active, lane, hi);
+    FWalker<KIND, GATE_UP> wk(f, s_active, warp, lo, hi);
     FCursor prod;
-    prod.a = lo + warp;
-    wk.seek(prod);
+    prod.ai = lo / upe;
+    prod.sg0 = 0;
+    wk.settle(prod);
     FCursor cons = prod;
 
     uint32_t fills = 0, takes = 0;
-    for (int s = 0; s < STAGES - 1 && prod.valid; s++) {
-        wk.fill(stages + (fills % STAGES) * S::BYTES, bars + fills % STAGES, prod);
+    auto fill_next = [&]() {
+        if (!prod.valid) return;
+        if (lane == 0) {
+            uint64_t* bar = bars + fills % STAGES;
+            mbar_expect_tx(bar, R::BYTES);
+            bulk_copy(ring + (fills % STAGES) * R::BYTES, wk.record(prod), R::BYTES, bar);
+        }
         fills++;
         wk.advance(prod);
-    }
+    };
+    for (int s = 0; s < STAGES - 1; s++) fill_next();
 
     const int g = lane >> 2, t = lane & 3;
     const int nb = a.cols / QK;
-    const int nbp = (nb + SUPER - 1) / SUPER * SUPER;
+    const uint32_t xq_s = smem_addr(smem + L.xq), xsT_s = smem_addr(smem + L.xsT),
+                   xsumT_s = smem_addr(smem + L.xsumT);
     float acc[F_GMAX][4], off[F_GMAX][4];
-    uint32_t rowB[F_GMAX], rowC[F_GMAX][2];
     bool ok = true;
-    while (cons.valid) {
-        if (prod.valid) {
-            wk.fill(stages + (fills % STAGES) * S::BYTES, bars + fills % STAGES, prod);
-            fills++;
-            wk.advance(prod);
-        }
-        const int row0 = wk.matrix_row(cons, g), row1 = wk.matrix_row(cons, g + 8);
-        const int nblk = min(F_NBC, nb - cons.c * F_NBC);
-        RowScales rs;
-        load_row_scales<KIND>(a, row0, nb, cons.c, nblk, rs.d[0], rs.c[0]);
-        load_row_scales<KIND>(a, row1, nb, cons.c, nblk, rs.d[1], rs.c[1]);
-        const int ntok = min(8 * F_GMAX, int(cons.m) - cons.sg0);
-        const int G = (ntok + 7) >> 3;
-        if (cons.c == 0) {
-#pragma unroll
-            for (int nt = 0; nt < F_GMAX; nt++) {
-                acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-                off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
-                rowB[nt] = wk.act_row(cons, cons.sg0 + nt * 8 + g);
-                rowC[nt][0] = wk.act_row(cons, cons.sg0 + nt * 8 + 2 * t);
-                rowC[nt][1] = wk.act_row(cons, cons.sg0 + nt * 8 + 2 * t + 1);
-            }
-        }
-        const uint32_t stage = takes % STAGES;
-        const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
-        if (!__all_sync(0xffffffffu, landed)) {
-            ok = false;
-            break;
-        }
-        const uint32_t st = smem_addr(stages + stage * S::BYTES);
-        const int col0 = cons.c * F_KC;
-        if (G == 1)
-            fast_chunk<KIND, 1>(a, st, nblk, lane, col0, nbp, cons.c, rs, rowB, rowC, acc, off);
-        else if (G == 2)
-            fast_chunk<KIND, 2>(a, st, nblk, lane, col0, nbp, cons.c, rs, rowB, rowC, acc, off);
-        else if (G == 3)
-            fast_chunk<KIND, 3>(a, st, nblk, lane, col0, nbp, cons.c, rs, rowB, rowC, acc, off);
-        else
-            fast_chunk<KIND, 4>(a, st, nblk, lane, col0, nbp, cons.c, rs, rowB, rowC, acc, off);
-        __syncwarp();
+    uint32_t xphase = 0;
 
-        if (cons.c == wk.nchunks - 1) {
+    // Segments (expert, 32 tokens) of this CTA's range, the same walk in every warp.
+    for (int ai = lo / upe; ok && lo < hi && ai * upe < hi; ai++) {
+        const int e = s_active[ai];
+        const uint32_t m = a.counts[e], base = a.offsets[e];
+        for (int sg0 = 0; ok && uint32_t(sg0) < m; sg0 += F_TOK) {
+            const int ntok = min(F_TOK, int(m) - sg0);
+            const int G = (ntok + 7) >> 3;
+            // ---- stage this segment's tokens (rows past ntok repeat the last one)
+            __syncthreads();  // everyone is done with the previous segment's tokens
+            if (warp == 0) {
+                if (lane == 0) mbar_expect_tx(xbar, uint32_t(G * 8) * a.cols);
+                __syncwarp();
+                if (lane < G * 8) {
+                    const uint32_t p = base + sg0 + min(lane, ntok - 1);
+                    const uint32_t row = GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
+                    bulk_copy(smem + L.xq + lane * f.x_stride, a.xq + size_t(row) * a.cols, a.cols, xbar);
+                }
+            }
+            for (int i = threadIdx.x; i < nb * G * 8; i += F_THREADS) {
+                const int b = i / (G * 8), j = i - b * (G * 8);  // token fastest: conflict-free stores
+                const uint32_t p = base + sg0 + min(j, ntok - 1);
+                const uint32_t row = GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
+                reinterpret_cast<float*>(smem + L.xsT)[b * F_TOK + j] = a.xs[size_t(row) * f.nbp + b];
+                if (KIND == 2)
+                    reinterpret_cast<float*>(smem + L.xsumT)[b * F_TOK + j] = a.xsum[size_t(row) * f.nbp + b];
+            }
+            __syncthreads();
+            {
+                const bool landed = mbar_wait_bounded(xbar, xphase & 1);
+                xphase++;
+                if (!__all_sync(0xffffffffu, landed)) ok = false;
+            }
+            // ---- this warp's units of the segment
+            while (ok && cons.valid && cons.ai == ai && cons.sg0 == sg0) {
+                fill_next();
+                if (cons.c == 0) {
 #pragma unroll
-            for (int nt = 0; nt < F_GMAX; nt++) {
+                    for (int nt = 0; nt < F_GMAX; nt++) {
+                        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+                        off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
+                    }
+                }
+                const uint32_t stage = takes % STAGES;
+                const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
+                if (!__all_sync(0xffffffffu, landed)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t rec = smem_addr(ring + stage * R::BYTES);
+                const int nblk = min(F_NBC, nb - cons.c * F_NBC);
+                const int blk0 = cons.c * F_NBC;
+                if (G == 1)
+                    fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                else if (G == 2)
+                    fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                else if (G == 3)
+                    fast_chunk<KIND, 3>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                else
+                    fast_chunk<KIND, 4>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                __syncwarp();
+
+                if (cons.c == wk.nchunks - 1) {
+                    const int u = cons.a - ai * upe;
 #pragma unroll
-                for (int i = 0; i < 2; i++) {
-                    const int j = cons.sg0 + nt * 8 + 2 * t + i;  // the expert's j-th token
-                    if (nt < G && uint32_t(j) < cons.m) {
-                        float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
-                        if (KIND == 2) {
-                            y0 = y0 + off[nt][i];
-                            y1 = y1 + off[nt][2 + i];
-                        }
-                        const size_t p = cons.base + j;
-                        if (GATE_UP) {
-                            if (row0 >= 0) {
-                                const float e = exp_poly(-y0);
-                                a.out[p * a.out_cols + cons.u * 8 + g] = __fdiv_rn(y0, 1.0f + e) * y1;
+                    for (int nt = 0; nt < F_GMAX; nt++) {
+#pragma unroll
+                        for (int i = 0; i < 2; i++) {
+                            const int j = nt * 8 + 2 * t + i;
+                            if (nt < G && j < ntok) {
+                                float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
+                                if (KIND == 2) {
+                                    y0 = y0 + off[nt][i];
+                                    y1 = y1 + off[nt][2 + i];
+                                }
+                                const size_t p = base + sg0 + j;
+                                if (GATE_UP) {
+                                    const int col = u * 8 + g;
+                                    if (col < a.out_cols) {
+                                        const float ex = exp_poly(-y0);
+                                        a.out[p * a.out_cols + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
+                                    }
+                                } else {
+                                    const int r0 = u * F_ROWS + g;
+                                    if (r0 < a.out_cols) a.out[p * a.out_cols + r0] = y0;
+                                    if (r0 + 8 < a.out_cols) a.out[p * a.out_cols + r0 + 8] = y1;
+                                }
                             }
-                        } else {
-                            if (row0 >= 0) a.out[p * a.out_cols + cons.u * F_ROWS + g] = y0;
-                            if (row1 >= 0) a.out[p * a.out_cols + cons.u * F_ROWS + g + 8] = y1;
                         }
                     }
                 }
+                takes++;
+                wk.advance(cons);
             }
+            // Keep the decision to stop uniform across the CTA's barriers.
+            ok = __syncthreads_and(ok);
         }
-        takes++;
-        wk.advance(cons);
     }
     if (!ok) {
-        if (lane == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
+        if (threadIdx.x == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
+        // Give copies already in flight a bounded chance to land before the
+        // shared memory they target is released.
         for (uint32_t k = takes; k < fills; k++) mbar_wait_bounded(bars + k % STAGES, (k / STAGES) & 1);
     }
 }
 
+// Builds the records from a matrix in Tachyon's row-major layout. One CTA per
+// record; rows or blocks past the matrix's edge are zero.
 template <int KIND, bool GATE_UP>
-void launch_fast(const ExpertArgs& a, int sms, cudaStream_t stream) {
-    const int total_units = a.experts * a.units_per_expert;
+__global__ void tile_weights_kernel(const uint8_t* __restrict__ wdata, const void* __restrict__ wscales,
+                                    int cols, int rows_per_expert, int upe, int nchunks,
+                                    uint8_t* __restrict__ tiled) {
+    using R = Rec<KIND>;
+    const size_t rec_index = blockIdx.x;
+    const int c = int(rec_index % nchunks);
+    const int u = int((rec_index / nchunks) % upe);
+    const int e = int(rec_index / nchunks / upe);
+    uint8_t* rec = tiled + rec_index * R::BYTES;
+    const int nb = cols / QK;
+    for (int i = threadIdx.x; i < R::BYTES / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(rec)[i] = 0;
+    __syncthreads();
+    for (int r = 0; r < F_ROWS; r++) {
+        int row;
+        if (GATE_UP) {
+            const int inter = rows_per_expert / 2, col = u * 8 + (r & 7);
+            row = col < inter ? e * rows_per_expert + (r < 8 ? 0 : inter) + col : -1;
+        } else {
+            const int rr = u * F_ROWS + r;
+            row = rr < rows_per_expert ? e * rows_per_expert + rr : -1;
+        }
+        if (row < 0) continue;
+        const int col0 = c * F_KC, cols_c = min(F_KC, cols - col0);
+        const int nblk = cols_c / QK;
+        if (KIND == 1) {
+            for (int i = threadIdx.x; i < cols_c; i += blockDim.x)
+                rec[r * R::ROW_STRIDE + i] = wdata[size_t(row) * cols + col0 + i];
+            const uint16_t* sp = reinterpret_cast<const uint16_t*>(wscales) + size_t(row) * nb + c * F_NBC;
+            for (int b = threadIdx.x; b < nblk; b += blockDim.x)
+                reinterpret_cast<uint16_t*>(rec + r * R::ROW_STRIDE + F_KC)[b] = sp[b];
+        } else {
+            for (int i = threadIdx.x; i < cols_c / 2; i += blockDim.x)
+                rec[r * R::ROW_STRIDE + i] = wdata[(size_t(row) * cols + col0) / 2 + i];
+            const int words_per_row = (nb + SUPER - 1) / SUPER * SUPER_WORDS;
+            const uint32_t* wp = reinterpret_cast<const uint32_t*>(wscales) + size_t(row) * words_per_row +
+                                 c * SUPER_WORDS;
+            if (threadIdx.x < 4)
+                reinterpret_cast<uint32_t*>(rec + r * R::ROW_STRIDE + F_KC / 2)[threadIdx.x] = wp[threadIdx.x];
+            if (threadIdx.x == 4) reinterpret_cast<uint32_t*>(rec + F_ROWS * R::ROW_STRIDE)[r] = wp[4];
+        }
+    }
+}
+
+template <int KIND>
+int pick_stages(int cols, int nbp) {
+    for (int s = F_MAX_STAGES; s >= 2; s--)
+        if (size_t(Layout<KIND>(s, cols, nbp).total) <= F_SMEM_LIMIT) return s;
+    return 0;
+}
+
+template <int KIND, bool GATE_UP>
+int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, cudaStream_t stream) {
+    FastArgs f;
+    f.e = e;
+    f.tiled = tiled;
+    f.nbp = (e.cols / QK + SUPER - 1) / SUPER * SUPER;
+    f.x_stride = e.cols + 16;
+    f.stages = pick_stages<KIND>(e.cols, f.nbp);
+    if (f.stages == 0) return -1;
+    const int total_units = e.experts * e.units_per_expert;
     int grid = min(sms, (total_units + F_WARPS - 1) / F_WARPS);
     if (grid < 1) grid = 1;
-    expert_fast_kernel<KIND, GATE_UP><<<grid, F_THREADS, fast_smem_bytes<KIND>(), stream>>>(a);
+    const Layout<KIND> L(f.stages, e.cols, f.nbp);
+    expert_fast_kernel<KIND, GATE_UP><<<grid, F_THREADS, L.total, stream>>>(f);
+    return 1;
+}
+
+template <int KIND, bool GATE_UP>
+void run_tiling(const ExpertArgs& e, uint8_t* tiled, cudaStream_t stream) {
+    const int nchunks = (e.cols + F_KC - 1) / F_KC;
+    const size_t recs = size_t(e.experts) * e.units_per_expert * nchunks;
+    tile_weights_kernel<KIND, GATE_UP><<<unsigned(recs), 128, 0, stream>>>(
+        e.wdata, e.wscales, e.cols, e.rows_per_expert, e.units_per_expert, nchunks, tiled);
 }
 
 }  // namespace
 
 void init_kernels_fast() {
-    cudaFuncSetAttribute(expert_fast_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         int(fast_smem_bytes<1>()));
-    cudaFuncSetAttribute(expert_fast_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         int(fast_smem_bytes<1>()));
-    cudaFuncSetAttribute(expert_fast_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         int(fast_smem_bytes<2>()));
-    cudaFuncSetAttribute(expert_fast_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         int(fast_smem_bytes<2>()));
+    const int lim = int(F_SMEM_LIMIT);
+    cudaFuncSetAttribute(expert_fast_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_fast_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_fast_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_fast_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
 }
 
-int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, int t, Workspace& ws, int sms,
-                        cudaStream_t stream) {
+size_t tiled_bytes(const MoeDims& d, const MatrixDev& m, bool gate_up) {
+    const int cols = gate_up ? d.hidden : d.inter;
+    const int upe = gate_up ? (d.inter + 7) / 8 : (d.hidden + 15) / 16;
+    const int nchunks = (cols + F_KC - 1) / F_KC;
+    const size_t rec = m.kind == 1 ? Rec<1>::BYTES : Rec<2>::BYTES;
+    return size_t(d.experts) * upe * nchunks * rec;
+}
+
+bool fast_path_fits(const MoeDims& d, const MatrixDev& gate_up, const MatrixDev& down) {
+    const int nbp_h = (d.hidden / QK + 7) / 8 * 8, nbp_i = (d.inter / QK + 7) / 8 * 8;
+    const int s1 = gate_up.kind == 1 ? pick_stages<1>(d.hidden, nbp_h) : pick_stages<2>(d.hidden, nbp_h);
+    const int s2 = down.kind == 1 ? pick_stages<1>(d.inter, nbp_i) : pick_stages<2>(d.inter, nbp_i);
+    return s1 >= 2 && s2 >= 2;
+}
+
+void tile_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, uint8_t* tiled, cudaStream_t stream) {
+    Workspace none;
+    const ExpertArgs e = gate_up ? gate_up_args(d, m, none) : down_args(d, m, none);
+    if (gate_up) {
+        if (m.kind == 1) run_tiling<1, true>(e, tiled, stream);
+        else run_tiling<2, true>(e, tiled, stream);
+    } else {
+        if (m.kind == 1) run_tiling<1, false>(e, tiled, stream);
+        else run_tiling<2, false>(e, tiled, stream);
+    }
+}
+
+int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, int t, Workspace& ws,
+                        int sms, cudaStream_t stream) {
     (void)t;
     const ExpertArgs a = gate_up_args(d, m, ws);
-    if (m.kind == 1)
-        launch_fast<1, true>(a, sms, stream);
-    else
-        launch_fast<2, true>(a, sms, stream);
-    return 1;
+    return m.kind == 1 ? launch_fast<1, true>(a, tiled, sms, stream) : launch_fast<2, true>(a, tiled, sms, stream);
 }
 
-int launch_down_fast(const MoeDims& d, const MatrixDev& m, int t, Workspace& ws, int sms,
-                     cudaStream_t stream) {
+int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, int t, Workspace& ws,
+                     int sms, cudaStream_t stream) {
     (void)t;
     const ExpertArgs a = down_args(d, m, ws);
-    if (m.kind == 1)
-        launch_fast<1, false>(a, sms, stream);
-    else
-        launch_fast<2, false>(a, sms, stream);
-    return 1;
+    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
 }
 
 }  // namespace tc

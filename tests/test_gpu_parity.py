@@ -29,6 +29,31 @@ def ctx():
     c.close()
 
 
+_WEIGHTS = {}
+
+
+def layer_weights(oracle, shape: MoeShape, seed: int):
+    """Seeded weights of a shape, cached across tests. 4-bit matrices go through
+    the oracle's multi-threaded quantizer: it produces the same bytes as the
+    numpy mirror (tests/test_host_mirror.py) in a fraction of the time."""
+    key = (shape.hidden, shape.experts, shape.inter, shape.fmt, seed)
+    if key not in _WEIGHTS:
+        if shape.fmt == "q4":
+            h, e, i = shape.hidden, shape.experts, shape.inter
+            router = workloads._normal_matrix(seed, synth.STREAM_ROUTER, 0, e, h, "bf16")
+
+            def q4(stream, rows, cols):
+                data = synth.normal(seed, stream, rows * cols, 0, scale=0.02)
+                s, q = oracle.quantize_q4_matrix(data, rows, cols, None, 8)
+                return weights.Matrix(weights.KIND_Q4, rows, cols, s, q)
+
+            _WEIGHTS[key] = workloads.LayerWeights(router, q4(synth.STREAM_GATE_UP, e * 2 * i, h),
+                                                   q4(synth.STREAM_DOWN, e * h, i))
+        else:
+            _WEIGHTS[key] = workloads.layer_weights(shape, seed=seed, threads=6)
+    return _WEIGHTS[key]
+
+
 def to_oracle(oracle, m: weights.Matrix):
     return oracle.OracleMatrix(m.kind, m.rows, m.cols, m.scales, m.data)
 
@@ -137,7 +162,7 @@ def test_single_block_64_tokens(oracle, ctx, fmt, arith):
     """64 tokens, hidden 1024, 32 experts, top-8, intermediate 512, inputs
     N(0,1) after RMSNorm (weight 1, eps 1e-6), seed 0."""
     shape = MoeShape("block", 1024, 32, 8, 512, fmt=fmt)
-    lw = workloads.layer_weights(shape, seed=0, threads=6)
+    lw = layer_weights(oracle, shape, 0)
     h = workloads.hidden_states(shape, 64, seed=0)
     hd, wd = ctx.to_device(h), ctx.to_device(np.ones(1024, np.float32))
     ctx.rmsnorm(hd, wd, 1e-6, hd)
@@ -170,7 +195,7 @@ def test_batching_never_changes_a_token(oracle, ctx, fmt, arith):
     """Each token alone gives exactly its result in the batch (the property
     src/weights.rs:704-713 asserts for the CPU matmul), in both arithmetic modes."""
     shape = MoeShape("inv", 512, 8, 2, 128, fmt=fmt)
-    lw = workloads.layer_weights(shape, seed=3, threads=2)
+    lw = layer_weights(oracle, shape, 3)
     x = workloads.hidden_states(shape, 85, seed=3)
     ctx.set_arithmetic(ctx.ARITH_CPU_LANES if arith == "lanes" else ctx.ARITH_FAST)
     layer = make_layer(ctx, lw, shape.topk, 85)
@@ -189,7 +214,7 @@ def test_routing_skew_with_bias_and_many_tokens_per_expert(oracle, ctx, arith):
     """A Zipf(1.2) router bias: a few experts take most tokens, so their groups
     span several 8-token register tiles, and t > 256 takes the multi-CTA dispatch."""
     shape = MoeShape("skew-small", 256, 64, 8, 64, fmt="q8")
-    lw = workloads.layer_weights(shape, seed=5, threads=2)
+    lw = layer_weights(oracle, shape, 5)
     bias = synth.zipf_router_bias(5, 64)
     for t in [1, 16, 256, 700]:
         x = workloads.hidden_states(shape, t, seed=5)
@@ -203,7 +228,7 @@ def test_routing_skew_with_bias_and_many_tokens_per_expert(oracle, ctx, arith):
 def test_granite_3b_shape_and_skew_shape(oracle, ctx, arith):
     """hidden 1536 / 40 experts (4-bit) and hidden 2048 / 64 experts / intermediate 1024 (8-bit)."""
     for shape, t in [(MoeShape("3b", 1536, 40, 8, 512, fmt="q4"), 12), (MoeShape("skew", 2048, 64, 8, 1024, fmt="q8"), 16)]:
-        lw = workloads.layer_weights(shape, seed=1, threads=6)
+        lw = layer_weights(oracle, shape, 1)
         x = workloads.hidden_states(shape, t, seed=1)
         check_block(oracle, ctx, shape, lw, x, arith=arith)
 
@@ -211,7 +236,7 @@ def test_granite_3b_shape_and_skew_shape(oracle, ctx, arith):
 def test_host_entry_point_and_graph_replay_equal_the_device_path(oracle, ctx):
     shape = MoeShape("e2e", 512, 16, 4, 128, fmt="q8")
     ctx.set_arithmetic(ctx.ARITH_FAST)
-    lw = workloads.layer_weights(shape, seed=2, threads=2)
+    lw = layer_weights(oracle, shape, 2)
     x = workloads.hidden_states(shape, 33, seed=2)
     y0 = workloads.hidden_states(shape, 33, seed=9)
     layer = make_layer(ctx, lw, shape.topk, 64)
