@@ -212,13 +212,11 @@ def main():
     y_host = ctx.pinned((args.batch, shape.hidden))
     x_in = ctx.to_device(x_host)
     x = ctx.empty((args.batch, shape.hidden))
-    xb = ctx.empty((args.batch, shape.hidden))
 
     def enqueue_stack():
         ctx.copy(x, x_in)
         for layer in layers:
-            ctx.rmsnorm(x, ones, EPS, xb)
-            layer.forward(xb, x)
+            layer.block(ones, EPS, x)  # x += moe(rmsnorm(x)): src/model.rs:662-681
 
     # ---- eager pass with per-kernel events: which kernel dominates, and its bandwidth
     enqueue_stack()
@@ -229,8 +227,7 @@ def main():
     for s in range(prof_steps):
         ctx.copy(x, x_in)
         for layer in layers:
-            ctx.rmsnorm(x, ones, EPS, xb)
-            layer.forward(xb, x)
+            layer.block(ones, EPS, x)
             if s == 0:
                 _, _, counts, _ = layer.last_routing(args.batch)
                 distinct.append(int(np.count_nonzero(counts)))

@@ -91,6 +91,10 @@ int tc_moe_set_router_bias(tc_moe_layer *layer, const float *bias_host);
  * residual stream (`s.x`): src/model.rs:671-681. Device pointers; enqueued on
  * the context's stream, returns without waiting. */
 int tc_moe_forward(tc_moe_layer *layer, const float *x_dev, int t, float *y_dev);
+/* The whole MLP block of a MoE layer on the residual stream, as
+ * src/model.rs:662-681 runs it: y[t,hidden] += moe(rmsnorm(y, norm_weight, eps)).
+ * The norm is fused into the router kernel (same arithmetic as tc_rmsnorm). */
+int tc_moe_block(tc_moe_layer *layer, const float *norm_weight_dev, float eps, int t, float *y_dev);
 /* The same through host buffers: copies x and y in, runs, copies y back, waits. */
 int tc_moe_forward_host(tc_moe_layer *layer, const float *x_host, int t, float *y_host);
 /* Routing of the last forward, copied to the host (any pointer may be NULL):

@@ -147,16 +147,19 @@ bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
               ws_alloc(ctx, w.xsum, size_t(T) * pad8(n.hidden / 32)) &&
               ws_alloc(ctx, w.counts, size_t(n.experts)) &&
               ws_alloc(ctx, w.offsets, size_t(n.experts) + 1) && ws_alloc(ctx, w.perm, slots) &&
-              ws_alloc(ctx, w.pos, slots) && ws_alloc(ctx, w.block_hist, blocks * n.experts) &&
+              ws_alloc(ctx, w.pos, slots) && ws_alloc(ctx, w.slot_token, slots) &&
+              ws_alloc(ctx, w.active, size_t(n.experts) + 1) && ws_alloc(ctx, w.block_hist, blocks * n.experts) &&
               ws_alloc(ctx, w.hidden_f, slots * n.inter) && ws_alloc(ctx, w.hq, slots * n.inter) &&
               ws_alloc(ctx, w.hs, slots * pad8(n.inter / 32)) &&
               ws_alloc(ctx, w.hsum, slots * pad8(n.inter / 32)) &&
-              ws_alloc(ctx, w.out, slots * n.hidden) && ws_alloc(ctx, w.status, size_t(1));
+              ws_alloc(ctx, w.out, slots * n.hidden) && ws_alloc(ctx, w.status, size_t(1)) &&
+              ws_alloc(ctx, w.ticket, size_t(1));
     if (!ok) {
         ws_release(ctx);
         return false;
     }
     cudaMemset(w.status, 0, sizeof(int));
+    cudaMemset(w.ticket, 0, sizeof(int));
     w.max_tokens = T;
     w.hidden = n.hidden;
     w.experts = n.experts;
@@ -436,7 +439,13 @@ int tc_moe_set_router_bias(tc_moe_layer* layer, const float* bias_host) {
     return tc_upload(ctx, layer->bias, bias_host, layer->dims.experts * sizeof(float));
 }
 
-int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
+}  // extern "C"
+
+namespace {
+
+// The block: route (+ optional norm), dispatch, experts, combine. x is the
+// normed input, or the residual stream itself when norm_w is given.
+int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float eps, int t, float* y) {
     tc_ctx* ctx = layer->ctx;
     if (t <= 0) return fail(ctx, "empty batch");
     if (t > layer->max_tokens) return fail(ctx, "%d tokens, layer was created for %d", t, layer->max_tokens);
@@ -446,15 +455,14 @@ int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
     int n = 0;
     n += staged(ctx, 0, [&] {
         return tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
-                                x, t, ws, s);
+                                x, norm_w, eps, t, ws, s);
     });
-    n += staged(ctx, 1, [&] { return tc::launch_dispatch(d, t, ws, s); });
     const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
     n += staged(ctx, 2, [&] {
         return lanes ? tc::launch_gate_up_exact(d, layer->gate_up->dev, t, ws, ctx->sms, s)
                      : tc::launch_gate_up_fast(d, layer->gate_up->dev, layer->gate_up_tiled, t, ws, ctx->sms, s);
     });
-    n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
+    if (lanes) n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
     n += staged(ctx, 4, [&] {
         return lanes ? tc::launch_down_exact(d, layer->down->dev, t, ws, ctx->sms, s)
                      : tc::launch_down_fast(d, layer->down->dev, layer->down_tiled, t, ws, ctx->sms, s);
@@ -464,6 +472,19 @@ int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
     layer->last_t = t;
     if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
     return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int tc_moe_forward(tc_moe_layer* layer, const float* x, int t, float* y) {
+    return moe_enqueue(layer, x, nullptr, 0.0f, t, y);
+}
+
+int tc_moe_block(tc_moe_layer* layer, const float* norm_weight, float eps, int t, float* y) {
+    if (!norm_weight) return fail(layer->ctx, "tc_moe_block needs the norm's weight");
+    return moe_enqueue(layer, y, norm_weight, eps, t, y);
 }
 
 int tc_moe_forward_host(tc_moe_layer* layer, const float* x_host, int t, float* y_host) {

@@ -45,6 +45,8 @@ struct Workspace {
     uint32_t* offsets = nullptr;  // [E+1] first sorted slot of each expert
     uint32_t* perm = nullptr;     // [T*k] sorted slot -> token*k + j
     uint32_t* pos = nullptr;      // [T*k] token*k + j -> sorted slot
+    uint32_t* slot_token = nullptr;  // [T*k] sorted slot -> token
+    int* active = nullptr;        // [E+1] experts with tokens, ascending; [E] = how many
     uint32_t* block_hist = nullptr;  // [blocks, E] dispatch: per-block histograms / bases
     float* hidden_f = nullptr;    // [T*k, I] silu(gate)*up, sorted order
     int8_t* hq = nullptr;         // [T*k, I]
@@ -52,6 +54,7 @@ struct Workspace {
     float* hsum = nullptr;        // [T*k, pad8(I/32)]
     float* out = nullptr;         // [T*k, H] expert outputs, sorted order
     int* status = nullptr;        // device status word
+    int* ticket = nullptr;        // arrival counter of the router CTAs (zero between launches)
 };
 
 struct MoeDims {
@@ -78,8 +81,11 @@ enum : int {
 
 // Router logits (bf16 weights, f32 activations), top-k, gating softmax, and
 // 8-bit quantization of each token's row.
-int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x, int t,
-                 Workspace& ws, cudaStream_t stream);
+// x is the block's normed input, or (norm_w set) the residual stream to be
+// RMS-normed first. Batches of up to 256 tokens are dispatched by the same
+// kernel; larger ones by launch_dispatch, which this then calls.
+int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x,
+                 const float* norm_w, float eps, int t, Workspace& ws, cudaStream_t stream);
 
 // Per-expert histogram, prefix scan and stable permutation of the t*k slots.
 int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);

@@ -9,7 +9,7 @@
 
 namespace tc {
 
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
 constexpr int MAGIC_I = 0x4B400000;  // bits of 12582912.0f = 1.5 * 2^23
 constexpr float MAGIC_F = 12582912.0f;
 
@@ -22,10 +22,12 @@ struct ExpertArgs {
     int units_per_expert;
     const uint32_t* counts;
     const uint32_t* offsets;
-    const uint32_t* perm;     // gate_up: sorted slot -> token*k+j (null for down)
+    const uint32_t* slot_token;  // gate_up: sorted slot -> token (null for down: rows are slots)
+    const int* active;        // experts with tokens, ascending; active[experts] = their number
     const int8_t* xq;         // activations [rows, cols]
     const float* xs;          // scales [rows, pad8(cols/32)]
     const float* xsum;        // [rows, pad8(cols/32)] (4-bit offsets)
+    const float* xf;          // when set: f32 activation rows [rows, cols] to quantize while staging
     float* out;               // gate_up: hidden_f [slots, inter]; down: out [slots, hidden]
     int out_cols;
     int* status;
@@ -42,7 +44,8 @@ inline ExpertArgs gate_up_args(const MoeDims& d, const MatrixDev& m, const Works
     a.units_per_expert = (d.inter + 7) / 8;  // 8 gate rows + the 8 matching up rows
     a.counts = ws.counts;
     a.offsets = ws.offsets;
-    a.perm = ws.perm;
+    a.slot_token = ws.slot_token;
+    a.active = ws.active;
     a.xq = ws.xq;
     a.xs = ws.xs;
     a.xsum = ws.xsum;
@@ -63,7 +66,8 @@ inline ExpertArgs down_args(const MoeDims& d, const MatrixDev& m, const Workspac
     a.units_per_expert = (d.hidden + 15) / 16;
     a.counts = ws.counts;
     a.offsets = ws.offsets;
-    a.perm = nullptr;
+    a.slot_token = nullptr;
+    a.active = ws.active;
     a.xq = ws.hq;
     a.xs = ws.hs;
     a.xsum = ws.hsum;
@@ -89,20 +93,26 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
+    // The last operand is a suspend-time hint in nanoseconds: the thread may
+    // sleep in hardware until the phase completes or that much time passes.
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_addr(bar)), "r"(parity)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(4000u)
         : "memory");
     return ok != 0;
 }
 
-// Waits for a stage with a spin limit. Returns false if the limit ran out.
+// Waits for a stage with a spin limit. Returns false if the limit ran out
+// (2^20 probes of up to 4 us each, with a short sleep between them so that
+// waiting warps leave the issue slots to the ones that have data).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; i++)
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(100);
+    }
     return false;
 }
 

@@ -108,7 +108,7 @@ struct Worker {
     // The activation row of token j of the cursor's group.
     __device__ uint32_t act_row(const Cursor& cur, int j) const {
         const uint32_t p = cur.base + cur.g0 + j;
-        return GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
+        return GATE_UP ? a.slot_token[p] : p;
     }
 
     __device__ void fill(uint8_t* stage, uint64_t* bar, const Cursor& cur) const {

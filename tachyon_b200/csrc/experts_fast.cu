@@ -35,14 +35,15 @@ namespace tc {
 
 namespace {
 
-constexpr int F_WARPS = 8;
+constexpr int F_WARPS = 16;
 constexpr int F_THREADS = F_WARPS * 32;
 constexpr int F_KC = 256;         // columns per record
 constexpr int F_NBC = F_KC / QK;  // blocks per record
 constexpr int F_ROWS = 16;        // weight rows per unit (one m16 tile)
-constexpr int F_GMAX = 4;         // token tiles of 8 held in registers
+constexpr int F_GMAX = 2;         // token tiles of 8 held in registers
 constexpr int F_TOK = 8 * F_GMAX; // tokens staged per segment
-constexpr int F_MAX_STAGES = 8;
+constexpr int F_MAX_STAGES = 6;
+static_assert(F_TOK <= 32, "one lane of warp 0 stages one token row");
 constexpr size_t F_SMEM_LIMIT = 227 * 1024;
 
 template <int KIND>
@@ -65,7 +66,7 @@ struct FastArgs {
 // Shared memory carve-up (offsets in bytes).
 template <int KIND>
 struct Layout {
-    int ring, bars, xq, xsT, xsumT, active, total;
+    int ring, bars, xq, xsT, xsumT, active, rows, total;
     __host__ __device__ Layout(int stages, int cols, int nbp) {
         int o = 0;
         ring = o;
@@ -78,49 +79,93 @@ struct Layout {
         xsumT = o;
         if (KIND == 2) o += nbp * F_TOK * 4;
         active = o;
-        o += (MAX_EXPERTS + 4) * 4;
+        rows = o;
+        o += F_TOK * 4;
         bars = o;
         o += (F_WARPS * F_MAX_STAGES + 1) * 8;
         total = o;
     }
 };
 
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, int& r0, int& r1, int& r2, int& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-                 : "r"(addr));
+// Shared-memory reads below are plain (non-volatile) asm so the compiler may
+// interleave them across unrolled blocks; what keeps them behind the mbarrier
+// wait that made their data visible is the `token` operand, a value that wait
+// produced.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t token, int& r0, int& r1, int& r2, int& r3) {
+    asm("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4]; // %5"
+        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+        : "r"(addr), "r"(token));
 }
 
-__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, int& r0, int& r1) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-                 : "=r"(r0), "=r"(r1)
-                 : "r"(addr));
+__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t token, int& r0, int& r1) {
+    asm("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2]; // %3" : "=r"(r0), "=r"(r1) : "r"(addr), "r"(token));
 }
 
 // D = A(16x32 s8, row) * B(32x8 s8, col) + c, s32 accumulate.
 __device__ __forceinline__ void mma_s8(int (&d)[4], int a0, int a1, int a2, int a3, int b0, int b1,
                                        int c) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
         "{%10,%10,%10,%10};"
         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
 }
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+__device__ __forceinline__ uint32_t lds32(uint32_t addr, uint32_t token) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm("ld.shared.u32 %0, [%1]; // %2" : "=r"(v) : "r"(addr), "r"(token));
     return v;
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+__device__ __forceinline__ uint4 lds128(uint32_t addr, uint32_t token) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+        : "r"(addr), "r"(token));
     return v;
 }
-__device__ __forceinline__ float2 lds_f2(uint32_t addr) {
+__device__ __forceinline__ float2 lds_f2(uint32_t addr, uint32_t token) {
     float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    asm("ld.shared.v2.f32 {%0,%1}, [%2]; // %3" : "=f"(v.x), "=f"(v.y) : "r"(addr), "r"(token));
     return v;
+}
+
+// Two IEEE f32 operations per instruction (the results are those of the
+// scalar forms): a - m, a * b, fma(a, b, c) on register pairs.
+__device__ __forceinline__ float2 sub2(float2 a, float2 m) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rm, rr;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rm, {%4, %5};\n\t"
+        "sub.rn.f32x2 rr, ra, rm;\n\t"
+        "mov.b64 {%0, %1}, rr;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a.x), "f"(a.y), "f"(m.x), "f"(m.y));
+    return r;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rb, rr;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rr, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rr;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return r;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 r;
+    asm("{\n\t.reg .b64 ra, rb, rc, rr;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rr, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rr;\n\t}"
+        : "=f"(r.x), "=f"(r.y)
+        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return r;
+}
+
+// f16 bits of a weight scale (finite, as every scale Tachyon stores is) to f32
+// on the full-rate pipes: the bits shifted into place, times 2^112
+// (src/kernels.rs:127-130). Exact for normals and subnormals of either sign.
+__device__ __forceinline__ float f16_scale_to_f32(uint32_t h) {
+    return __uint_as_float(((h & 0x8000u) << 16) | ((h & 0x7FFFu) << 13)) * __uint_as_float(0x77800000u);
 }
 
 // A warp's place in its sequence of (expert, token segment, unit, chunk) steps.
@@ -190,8 +235,9 @@ struct FWalker {
 // One record (16 rows x up to 8 blocks) against G tiles of 8 staged tokens.
 template <int KIND, int G>
 __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t xsT_s, uint32_t xsumT_s,
-                                           int x_stride, int nblk, int blk0, int lane,
-                                           float (&acc)[F_GMAX][4], float (&off)[F_GMAX][4]) {
+                                           int x_stride, int nblk, int blk0, int lane, uint32_t wtok,
+                                           uint32_t xtok, float (&acc)[F_GMAX][4],
+                                           float (&off)[F_GMAX][4]) {
     using R = Rec<KIND>;
     const int g = lane >> 2, t = lane & 3;
     const int mat = lane >> 3, mr = lane & 7;
@@ -200,16 +246,16 @@ __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t
     if (KIND == 1) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC);
+            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC, wtok);
             const uint32_t hw[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-            for (int b = 0; b < F_NBC; b++) wd[h][b] = f16_bits_to_f32(uint16_t(hw[b >> 1] >> (16 * (b & 1))));
+            for (int b = 0; b < F_NBC; b++) wd[h][b] = f16_scale_to_f32((hw[b >> 1] >> (16 * (b & 1))) & 0xFFFFu);
         }
     } else {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC / 2);
-            const uint32_t o23 = lds32(rec + F_ROWS * R::ROW_STRIDE + (g + 8 * h) * 4);
+            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC / 2, wtok);
+            const uint32_t o23 = lds32(rec + F_ROWS * R::ROW_STRIDE + (g + 8 * h) * 4, wtok);
             const float step_d = f16_bits_to_f32(uint16_t(s.x)), step_c = f16_bits_to_f32(uint16_t(s.x >> 16));
 #pragma unroll
             for (int b = 0; b < F_NBC; b++) {
@@ -223,54 +269,101 @@ __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t
         a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE + (mat >> 1) * 16;
     else
         a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE;
-    // B: token row (mr) of tile nt, 16-byte half (mat & 1) of block b + (mat >> 1).
+    // B: token row (mr) of a tile, 16-byte half (mat & 1) of block b + (mat >> 1).
     const uint32_t b_addr = xq_s + mr * x_stride + blk0 * 32 + (mat & 1) * 16 + (mat >> 1) * 32;
+    // Four blocks at a time, in three phases so that the loads, the matrix
+    // instructions and the float chains of different blocks overlap: all
+    // operand loads, then all matrix instructions, then the scaling.
 #pragma unroll
-    for (int b = 0; b < F_NBC; b += 2) {
-        if (b < nblk) {
-            int a[2][4];
+    for (int h4 = 0; h4 < F_NBC; h4 += 4) {
+        if (h4 < nblk) {
+            int A[4][4];
 #pragma unroll
-            for (int k = 0; k < 2; k++) {
+            for (int k = 0; k < 4; k++) {
                 if (KIND == 1) {
-                    ldmatrix_x4(a_addr + (b + k) * 32, a[k][0], a[k][1], a[k][2], a[k][3]);
+                    ldmatrix_x4(a_addr + (h4 + k) * 32, wtok, A[k][0], A[k][1], A[k][2], A[k][3]);
                 } else {
                     // Word t of rows g and g+8: low nibbles are elements 4t..4t+3,
                     // high nibbles elements 16+4t..16+4t+3.
                     int w0, w1;
-                    ldmatrix_x2(a_addr + (b + k) * 16, w0, w1);
-                    a[k][0] = nibbles_minus8(uint32_t(w0) & 0x0F0F0F0Fu);
-                    a[k][2] = nibbles_minus8((uint32_t(w0) >> 4) & 0x0F0F0F0Fu);
-                    a[k][1] = nibbles_minus8(uint32_t(w1) & 0x0F0F0F0Fu);
-                    a[k][3] = nibbles_minus8((uint32_t(w1) >> 4) & 0x0F0F0F0Fu);
+                    ldmatrix_x2(a_addr + (h4 + k) * 16, wtok, w0, w1);
+                    A[k][0] = nibbles_minus8(uint32_t(w0) & 0x0F0F0F0Fu);
+                    A[k][2] = nibbles_minus8((uint32_t(w0) >> 4) & 0x0F0F0F0Fu);
+                    A[k][1] = nibbles_minus8(uint32_t(w1) & 0x0F0F0F0Fu);
+                    A[k][3] = nibbles_minus8((uint32_t(w1) >> 4) & 0x0F0F0F0Fu);
                 }
             }
 #pragma unroll
-            for (int nt = 0; nt < G; nt++) {
-                int bq[4];  // blocks b and b+1: {b lo, b hi, b+1 lo, b+1 hi}
-                ldmatrix_x4(b_addr + nt * 8 * x_stride + b * 32, bq[0], bq[1], bq[2], bq[3]);
+            for (int n0 = 0; n0 < G; n0 += 2) {
+                constexpr int PAIR = 2;
+                int B[PAIR][4][2];
+                float2 XS[PAIR][4], SU[PAIR][4];
 #pragma unroll
-                for (int k = 0; k < 2; k++) {
-                    if (b + k < nblk) {
-                        int d[4];
-                        mma_s8(d, a[k][0], a[k][1], a[k][2], a[k][3], bq[2 * k], bq[2 * k + 1], MAGIC_I);
-                        const float2 xs = lds_f2(xsT_s + ((blk0 + b + k) * F_TOK + nt * 8 + 2 * t) * 4);
-                        acc[nt][0] = fmaf(__int_as_float(d[0]) - MAGIC_F, wd[0][b + k] * xs.x, acc[nt][0]);
-                        acc[nt][1] = fmaf(__int_as_float(d[1]) - MAGIC_F, wd[0][b + k] * xs.y, acc[nt][1]);
-                        acc[nt][2] = fmaf(__int_as_float(d[2]) - MAGIC_F, wd[1][b + k] * xs.x, acc[nt][2]);
-                        acc[nt][3] = fmaf(__int_as_float(d[3]) - MAGIC_F, wd[1][b + k] * xs.y, acc[nt][3]);
-                        if (KIND == 2) {
-                            const float2 su = lds_f2(xsumT_s + ((blk0 + b + k) * F_TOK + nt * 8 + 2 * t) * 4);
-                            off[nt][0] = fmaf(wc[0][b + k], su.x, off[nt][0]);
-                            off[nt][1] = fmaf(wc[0][b + k], su.y, off[nt][1]);
-                            off[nt][2] = fmaf(wc[1][b + k], su.x, off[nt][2]);
-                            off[nt][3] = fmaf(wc[1][b + k], su.y, off[nt][3]);
+                for (int p = 0; p < PAIR; p++) {
+                    if (n0 + p < G) {
+                        const uint32_t row = b_addr + (n0 + p) * 8 * x_stride + h4 * 32;
+                        ldmatrix_x4(row, xtok, B[p][0][0], B[p][0][1], B[p][1][0], B[p][1][1]);
+                        ldmatrix_x4(row + 64, xtok, B[p][2][0], B[p][2][1], B[p][3][0], B[p][3][1]);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const uint32_t so = ((blk0 + h4 + k) * F_TOK + (n0 + p) * 8 + 2 * t) * 4;
+                            XS[p][k] = lds_f2(xsT_s + so, xtok);
+                            if (KIND == 2) SU[p][k] = lds_f2(xsumT_s + so, xtok);
                         }
                     }
                 }
+                int D[PAIR][4][4];
+#pragma unroll
+                for (int p = 0; p < PAIR; p++)
+                    if (n0 + p < G) {
+#pragma unroll
+                        for (int k = 0; k < 4; k++)
+                            mma_s8(D[p][k], A[k][0], A[k][1], A[k][2], A[k][3], B[p][k][0], B[p][k][1], MAGIC_I);
+                    }
+#pragma unroll
+                for (int p = 0; p < PAIR; p++)
+                    if (n0 + p < G) {
+                        const int nt = n0 + p;
+#pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            if (h4 + k < nblk) {
+                                const int b = h4 + k;
+                                const float2 magic = make_float2(MAGIC_F, MAGIC_F);
+#pragma unroll
+                                for (int h = 0; h < 2; h++) {  // rows g and g+8; tokens 2t, 2t+1 side by side
+                                    const float2 sum = sub2(make_float2(__int_as_float(D[p][k][2 * h]),
+                                                                        __int_as_float(D[p][k][2 * h + 1])), magic);
+                                    const float2 d = mul2(make_float2(wd[h][b], wd[h][b]), XS[p][k]);
+                                    const float2 r = fma2(sum, d, make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]));
+                                    acc[nt][2 * h] = r.x;
+                                    acc[nt][2 * h + 1] = r.y;
+                                    if (KIND == 2) {
+                                        const float2 o = fma2(make_float2(wc[h][b], wc[h][b]), SU[p][k],
+                                                              make_float2(off[nt][2 * h], off[nt][2 * h + 1]));
+                                        off[nt][2 * h] = o.x;
+                                        off[nt][2 * h + 1] = o.y;
+                                    }
+                                }
+                            }
+                        }
+                    }
             }
         }
     }
 }
+
+#ifdef TC_TIMELINE
+// Diagnostic build only: cycle stamps per (CTA, warp, event).
+__device__ long long g_timeline[148][F_WARPS][16];
+#define TL(k)                                                                       \
+    do {                                                                            \
+        if (GATE_UP && lane == 0 && blockIdx.x < 148) g_timeline[blockIdx.x][warp][k] = clock64(); \
+    } while (0)
+#else
+#define TL(k) \
+    do {      \
+    } while (0)
+#endif
 
 template <int KIND, bool GATE_UP>
 __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArgs f) {
@@ -280,34 +373,24 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
     const Layout<KIND> L(f.stages, a.cols, f.nbp);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int STAGES = f.stages;
+    TL(0);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
     uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L.bars) + F_WARPS * F_MAX_STAGES;
-    int* s_active = reinterpret_cast<int*>(smem + L.active);
-    int* s_nactive = s_active + MAX_EXPERTS;
+    uint32_t* s_rows = reinterpret_cast<uint32_t*>(smem + L.rows);
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
         if (warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    // Experts with tokens, in ascending order (warp 0).
-    if (warp == 0) {
-        int n = 0;
-        for (int e0 = 0; e0 < a.experts; e0 += 32) {
-            const int e = e0 + lane;
-            const bool on = e < a.experts && a.counts[e] > 0;
-            const unsigned ballot = __ballot_sync(0xffffffffu, on);
-            if (on) s_active[n + __popc(ballot & ((1u << lane) - 1u))] = e;
-            n += __popc(ballot);
-        }
-        if (lane == 0) *s_nactive = n;
-    }
     __syncthreads();
+    TL(1);
     const int upe = a.units_per_expert;
-    const int total = *s_nactive * upe;
+    const int total = a.active[a.experts] * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
+    const int* s_active = a.active;
 
     FWalker<KIND, GATE_UP> wk(f, s_active, warp, lo, hi);
     FCursor prod;
@@ -328,6 +411,8 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
         wk.advance(prod);
     };
     for (int s = 0; s < STAGES - 1; s++) fill_next();
+    TL(2);
+    int seg_index = 0;
 
     const int g = lane >> 2, t = lane & 3;
     const int nb = a.cols / QK;
@@ -335,7 +420,10 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                    xsumT_s = smem_addr(smem + L.xsumT);
     float acc[F_GMAX][4], off[F_GMAX][4];
     bool ok = true;
-    uint32_t xphase = 0;
+    uint32_t xphase = 0, xtok = 0;
+#ifdef TC_TIMELINE
+    long long tl_wait = 0, tl_compute = 0, tl_chunks = 0, tl_fill = 0, tl_epi = 0;
+#endif
 
     // Segments (expert, 32 tokens) of this CTA's range, the same walk in every warp.
     for (int ai = lo / upe; ok && lo < hi && ai * upe < hi; ai++) {
@@ -346,32 +434,80 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
             const int G = (ntok + 7) >> 3;
             // ---- stage this segment's tokens (rows past ntok repeat the last one)
             __syncthreads();  // everyone is done with the previous segment's tokens
-            if (warp == 0) {
-                if (lane == 0) mbar_expect_tx(xbar, uint32_t(G * 8) * a.cols);
-                __syncwarp();
-                if (lane < G * 8) {
+            if (!GATE_UP && a.xf) {
+                // The down projection's inputs are the SwiGLU rows in f32: quantize the
+                // segment's rows here, a warp per (token, 32-block), exactly as
+                // quantize_q8 does (src/kernels.rs:84-98, applied per gathered row by
+                // src/weights.rs:652-664), straight into the staged layout.
+                float* xsT = reinterpret_cast<float*>(smem + L.xsT);
+                float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
+                for (int task = warp; task < G * 8 * nb; task += F_WARPS) {
+                    const int j = task / nb, b = task - j * nb;
+                    const size_t row = base + sg0 + min(j, ntok - 1);
+                    const float v = a.xf[row * a.cols + b * QK + lane];
+                    float amax = fabsf(v);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    const float d = __fdiv_rn(amax, 127.0f);
+                    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                    const float rr = roundf(v * id);
+                    const int qv = (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                    reinterpret_cast<int8_t*>(smem + L.xq)[j * f.x_stride + b * QK + lane] = int8_t(qv);
+                    if (KIND == 2) {
+                        int qsum = qv;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+                        if (lane == 0) xsumT[b * F_TOK + j] = d * float(qsum);
+                    }
+                    if (lane == 0) xsT[b * F_TOK + j] = d;
+                }
+                __syncthreads();
+                // A value the compiler cannot know before the barrier: the staged reads depend on it.
+                asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
+            } else {
+                if (warp == 0) {
+                    if (lane == 0) mbar_expect_tx(xbar, uint32_t(G * 8) * a.cols);
                     const uint32_t p = base + sg0 + min(lane, ntok - 1);
-                    const uint32_t row = GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
-                    bulk_copy(smem + L.xq + lane * f.x_stride, a.xq + size_t(row) * a.cols, a.cols, xbar);
+                    const uint32_t row = GATE_UP ? a.slot_token[p] : p;
+                    if (lane < F_TOK) s_rows[lane] = row;  // s_rows holds F_TOK entries
+                    __syncwarp();
+                    if (lane < G * 8)
+                        bulk_copy(smem + L.xq + lane * f.x_stride, a.xq + size_t(row) * a.cols, a.cols, xbar);
+                }
+                __syncthreads();
+                {
+                    // Scales transposed to [block][token]; token fastest, so stores do not conflict.
+                    const int n = nb * G * 8;
+                    float* xsT = reinterpret_cast<float*>(smem + L.xsT);
+                    float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
+#pragma unroll 4
+                    for (int i = threadIdx.x; i < n; i += F_THREADS) {
+                        const int b = i / (G * 8), j = i - b * (G * 8);
+                        const size_t src = size_t(s_rows[j]) * f.nbp + b;
+                        xsT[b * F_TOK + j] = a.xs[src];
+                        if (KIND == 2) xsumT[b * F_TOK + j] = a.xsum[src];
+                    }
+                }
+                __syncthreads();
+                {
+                    const bool landed = mbar_wait_bounded(xbar, xphase & 1);
+                    xphase++;
+                    if (!__all_sync(0xffffffffu, landed)) ok = false;
+                    xtok = uint32_t(landed);
                 }
             }
-            for (int i = threadIdx.x; i < nb * G * 8; i += F_THREADS) {
-                const int b = i / (G * 8), j = i - b * (G * 8);  // token fastest: conflict-free stores
-                const uint32_t p = base + sg0 + min(j, ntok - 1);
-                const uint32_t row = GATE_UP ? a.perm[p] / uint32_t(a.topk) : p;
-                reinterpret_cast<float*>(smem + L.xsT)[b * F_TOK + j] = a.xs[size_t(row) * f.nbp + b];
-                if (KIND == 2)
-                    reinterpret_cast<float*>(smem + L.xsumT)[b * F_TOK + j] = a.xsum[size_t(row) * f.nbp + b];
-            }
-            __syncthreads();
-            {
-                const bool landed = mbar_wait_bounded(xbar, xphase & 1);
-                xphase++;
-                if (!__all_sync(0xffffffffu, landed)) ok = false;
-            }
+            if (seg_index < 3) TL(3 + 4 * seg_index);
+            bool first_chunk = true;
             // ---- this warp's units of the segment
             while (ok && cons.valid && cons.ai == ai && cons.sg0 == sg0) {
+#ifdef TC_TIMELINE
+                const long long tf0 = clock64();
+#endif
                 fill_next();
+#ifdef TC_TIMELINE
+                __syncwarp();
+                tl_fill += clock64() - tf0;
+#endif
                 if (cons.c == 0) {
 #pragma unroll
                     for (int nt = 0; nt < F_GMAX; nt++) {
@@ -380,23 +516,34 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                     }
                 }
                 const uint32_t stage = takes % STAGES;
+#ifdef TC_TIMELINE
+                const long long tw0 = clock64();
+#endif
                 const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
+#ifdef TC_TIMELINE
+                const long long tw1 = clock64();
+                tl_wait += tw1 - tw0;
+#endif
                 if (!__all_sync(0xffffffffu, landed)) {
                     ok = false;
                     break;
                 }
+                if (first_chunk && seg_index < 3) TL(4 + 4 * seg_index);
+                first_chunk = false;
+                const uint32_t wtok = uint32_t(landed);
                 const uint32_t rec = smem_addr(ring + stage * R::BYTES);
                 const int nblk = min(F_NBC, nb - cons.c * F_NBC);
                 const int blk0 = cons.c * F_NBC;
                 if (G == 1)
-                    fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
-                else if (G == 2)
-                    fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
-                else if (G == 3)
-                    fast_chunk<KIND, 3>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                    fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 else
-                    fast_chunk<KIND, 4>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, acc, off);
+                    fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 __syncwarp();
+#ifdef TC_TIMELINE
+                const long long te0 = clock64();
+                tl_compute += te0 - tw1;
+                tl_chunks++;
+#endif
 
                 if (cons.c == wk.nchunks - 1) {
                     const int u = cons.a - ai * upe;
@@ -429,11 +576,28 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                 }
                 takes++;
                 wk.advance(cons);
+#ifdef TC_TIMELINE
+                __syncwarp();
+                tl_epi += clock64() - te0;
+#endif
             }
+            if (seg_index < 3) TL(5 + 4 * seg_index);
             // Keep the decision to stop uniform across the CTA's barriers.
             ok = __syncthreads_and(ok);
+            if (seg_index < 3) TL(6 + 4 * seg_index);
+            seg_index++;
         }
     }
+    TL(15);
+#ifdef TC_TIMELINE
+    if (GATE_UP && lane == 0 && blockIdx.x < 148) {
+        g_timeline[blockIdx.x][warp][12] = tl_wait;
+        g_timeline[blockIdx.x][warp][13] = tl_compute;
+        g_timeline[blockIdx.x][warp][14] = tl_chunks;
+        g_timeline[blockIdx.x][warp][10] = tl_fill;
+        g_timeline[blockIdx.x][warp][11] = tl_epi;
+    }
+#endif
     if (!ok) {
         if (threadIdx.x == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
         // Give copies already in flight a bounded chance to land before the
@@ -505,7 +669,7 @@ int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, cudaStream_t
     f.stages = pick_stages<KIND>(e.cols, f.nbp);
     if (f.stages == 0) return -1;
     const int total_units = e.experts * e.units_per_expert;
-    int grid = min(sms, (total_units + F_WARPS - 1) / F_WARPS);
+    int grid = min(sms, total_units);
     if (grid < 1) grid = 1;
     const Layout<KIND> L(f.stages, e.cols, f.nbp);
     expert_fast_kernel<KIND, GATE_UP><<<grid, F_THREADS, L.total, stream>>>(f);
@@ -521,6 +685,12 @@ void run_tiling(const ExpertArgs& e, uint8_t* tiled, cudaStream_t stream) {
 }
 
 }  // namespace
+
+#ifdef TC_TIMELINE
+extern "C" int tc_debug_timeline(long long* out) {
+    return int(cudaMemcpyFromSymbol(out, g_timeline, sizeof(g_timeline)));
+}
+#endif
 
 void init_kernels_fast() {
     const int lim = int(F_SMEM_LIMIT);
@@ -567,7 +737,8 @@ int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* til
 int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, int t, Workspace& ws,
                      int sms, cudaStream_t stream) {
     (void)t;
-    const ExpertArgs a = down_args(d, m, ws);
+    ExpertArgs a = down_args(d, m, ws);
+    a.xf = ws.hidden_f;  // quantized while staged: no separate pass over the SwiGLU rows
     return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
 }
 

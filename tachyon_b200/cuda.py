@@ -44,6 +44,7 @@ SYMBOLS = {
     "tc_moe_layer_free": (None, [_vp]),
     "tc_moe_set_router_bias": (_i, [_vp, _vp]),
     "tc_moe_forward": (_i, [_vp, _vp, _i, _vp]),
+    "tc_moe_block": (_i, [_vp, _vp, _f, _i, _vp]),
     "tc_moe_forward_host": (_i, [_vp, _vp, _i, _vp]),
     "tc_moe_last_routing": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "tc_moe_last_dispatch": (_i, [_vp, _vp, _vp]),
@@ -326,6 +327,11 @@ class MoeLayer:
         """y[t, hidden] += moe(x[t, hidden]) on the device; returns without waiting."""
         t = x.shape[0] if t is None else t
         self.ctx._check(self.ctx.lib.tc_moe_forward(self.handle, x.ptr, t, y.ptr), "tc_moe_forward")
+
+    def block(self, norm_weight: DeviceArray, eps: float, y: DeviceArray, t: int | None = None):
+        """y[t, hidden] += moe(rmsnorm(y, norm_weight, eps)): the MLP block on the residual stream."""
+        t = y.shape[0] if t is None else t
+        self.ctx._check(self.ctx.lib.tc_moe_block(self.handle, norm_weight.ptr, eps, t, y.ptr), "tc_moe_block")
 
     def forward_host(self, x: np.ndarray, y: np.ndarray):
         """The same through host buffers (copies in and out, waits); y is updated in place."""

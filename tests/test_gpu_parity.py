@@ -263,6 +263,33 @@ def test_host_entry_point_and_graph_replay_equal_the_device_path(oracle, ctx):
     layer.free()
 
 
+@pytest.mark.parametrize("t", [5, 300])
+def test_block_with_fused_norm_equals_norm_then_forward(oracle, ctx, t):
+    """tc_moe_block (RMSNorm fused into the router kernel; for t <= 256 the
+    dispatch too) gives exactly what tc_rmsnorm followed by tc_moe_forward gives,
+    which is the oracle's rmsnorm -> moe -> residual add."""
+    shape = MoeShape("blk", 512, 16, 4, 128, fmt="q8")
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    lw = layer_weights(oracle, shape, 2)
+    y0 = workloads.hidden_states(shape, t, seed=4)
+    w = (1.0 + synth.normal(4, 2, 512, scale=0.1)).astype(np.float32)
+    layer = make_layer(ctx, lw, shape.topk, t)
+    wd = ctx.to_device(w)
+    ya, xb = ctx.to_device(y0), ctx.empty(y0.shape)
+    ctx.rmsnorm(ya, wd, 1e-6, xb)
+    layer.forward(xb, ya)
+    yb = ctx.to_device(y0)
+    layer.block(wd, 1e-6, yb)
+    ctx.sync()
+    assert np.array_equal(ya.get(), yb.get())
+    with oracle.fast_arithmetic_model():
+        ref = oracle_moe(oracle, lw, oracle.rmsnorm_rows(y0, w, 1e-6), shape.topk)
+    got, want = yb.get(), y0 + ref.proj
+    assert np.abs(got - want).max() <= OUT_ABS
+    assert np.mean(np.all(got == want, axis=1)) > 0.5
+    layer.free()
+
+
 def test_bad_arguments_are_refused(ctx):
     from tachyon_b200 import cuda
 
