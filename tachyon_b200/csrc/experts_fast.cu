@@ -377,7 +377,6 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
     uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L.bars) + F_WARPS * F_MAX_STAGES;
-    uint32_t* s_rows = reinterpret_cast<uint32_t*>(smem + L.rows);
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
         if (warp == 0) mbar_init(xbar, 1);
@@ -441,25 +440,40 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                 // src/weights.rs:652-664), straight into the staged layout.
                 float* xsT = reinterpret_cast<float*>(smem + L.xsT);
                 float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
-                for (int task = warp; task < G * 8 * nb; task += F_WARPS) {
+                // A thread per (token, 32-block): eight 16-byte loads in flight, the
+                // block's maximum and its 32 roundings in registers, no shuffles.
+                for (int task = threadIdx.x; task < G * 8 * nb; task += F_THREADS) {
                     const int j = task / nb, b = task - j * nb;
                     const size_t row = base + sg0 + min(j, ntok - 1);
-                    const float v = a.xf[row * a.cols + b * QK + lane];
-                    float amax = fabsf(v);
+                    const float4* src = reinterpret_cast<const float4*>(a.xf + row * a.cols + b * QK);
+                    float4 v[8];
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    for (int i = 0; i < 8; i++) v[i] = src[i];
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+                        amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
+                                     fabsf(v[i].w));
                     const float d = __fdiv_rn(amax, 127.0f);
                     const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-                    const float rr = roundf(v * id);
-                    const int qv = (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
-                    reinterpret_cast<int8_t*>(smem + L.xq)[j * f.x_stride + b * QK + lane] = int8_t(qv);
-                    if (KIND == 2) {
-                        int qsum = qv;
+                    auto q8 = [&](float x) {
+                        const float rr = roundf(x * id);
+                        return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                    };
+                    uint32_t packed[8];
+                    int qsum = 0;
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
-                        if (lane == 0) xsumT[b * F_TOK + j] = d * float(qsum);
+                    for (int i = 0; i < 8; i++) {
+                        const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+                        qsum += q0 + q1 + q2 + q3;
+                        packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) | (uint32_t(q2 & 0xFF) << 16) |
+                                    (uint32_t(q3 & 0xFF) << 24);
                     }
-                    if (lane == 0) xsT[b * F_TOK + j] = d;
+                    uint4* dst = reinterpret_cast<uint4*>(smem + L.xq + j * f.x_stride + b * QK);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    xsT[b * F_TOK + j] = d;
+                    if (KIND == 2) xsumT[b * F_TOK + j] = d * float(qsum);
                 }
                 __syncthreads();
                 // A value the compiler cannot know before the barrier: the staged reads depend on it.
@@ -469,21 +483,23 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                     if (lane == 0) mbar_expect_tx(xbar, uint32_t(G * 8) * a.cols);
                     const uint32_t p = base + sg0 + min(lane, ntok - 1);
                     const uint32_t row = GATE_UP ? a.slot_token[p] : p;
-                    if (lane < F_TOK) s_rows[lane] = row;  // s_rows holds F_TOK entries
                     __syncwarp();
                     if (lane < G * 8)
                         bulk_copy(smem + L.xq + lane * f.x_stride, a.xq + size_t(row) * a.cols, a.cols, xbar);
                 }
-                __syncthreads();
                 {
-                    // Scales transposed to [block][token]; token fastest, so stores do not conflict.
+                    // Scales transposed to [block][token]; token fastest, so stores do not
+                    // conflict. Each thread looks its token's row up itself (an L1 hit after
+                    // the first), so nothing here waits for another warp.
                     const int n = nb * G * 8;
                     float* xsT = reinterpret_cast<float*>(smem + L.xsT);
                     float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
-#pragma unroll 4
+#pragma unroll 2
                     for (int i = threadIdx.x; i < n; i += F_THREADS) {
                         const int b = i / (G * 8), j = i - b * (G * 8);
-                        const size_t src = size_t(s_rows[j]) * f.nbp + b;
+                        const uint32_t p = base + sg0 + min(j, ntok - 1);
+                        const uint32_t row = GATE_UP ? a.slot_token[p] : p;
+                        const size_t src = size_t(row) * f.nbp + b;
                         xsT[b * F_TOK + j] = a.xs[src];
                         if (KIND == 2) xsumT[b * F_TOK + j] = a.xsum[src];
                     }

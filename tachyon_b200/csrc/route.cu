@@ -92,6 +92,18 @@ struct RouteArgs {
     int* active;
 };
 
+#ifdef TC_TIMELINE
+__device__ long long g_route_tl[256][8];
+#define RTL(k)                                                                      \
+    do {                                                                            \
+        if (threadIdx.x == 0 && blockIdx.x < 256) g_route_tl[blockIdx.x][k] = clock64(); \
+    } while (0)
+#else
+#define RTL(k) \
+    do {       \
+    } while (0)
+#endif
+
 __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a) {
     extern __shared__ __align__(16) float smem[];
     float* xrow = smem;                 // [hidden] the block's input row (after the norm)
@@ -102,6 +114,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hidden = a.hidden, experts = a.experts, topk = a.topk;
     const float* xin = a.x + size_t(token) * hidden;
+    RTL(0);
     for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
         *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
     __syncthreads();
@@ -117,37 +130,48 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         __syncthreads();
     }
 
-    // ---- logits. Two threads per expert: one holds the dot's first 8-lane
-    // accumulator (elements 16j..16j+7), the other the second (16j+8..16j+15).
-    for (int e0 = 0; e0 < experts; e0 += ROUTE_THREADS / 2) {
-        const int e = e0 + (tid >> 1), half = tid & 1;
+    RTL(1);
+    // ---- logits. Four threads per expert, each holding four of the dot's
+    // sixteen float lanes: thread q owns elements 16j+4q..16j+4q+3, so q = 0,1
+    // hold the first 8-lane accumulator and q = 2,3 the second. The weights of
+    // a whole batch of steps are requested before the chains run, so the loads
+    // overlap instead of each waiting for the previous fma.
+    constexpr int BATCH = 16;
+    for (int e0 = 0; e0 < experts; e0 += ROUTE_THREADS / 4) {
+        const int e = e0 + (tid >> 2), q = tid & 3;
         const bool valid = e < experts;
-        const uint16_t* w = a.router + size_t(valid ? e : 0) * hidden + half * 8;
-        const float* xr = xrow + half * 8;
-        float acc[8];
+        const uint16_t* w = a.router + size_t(valid ? e : 0) * hidden + q * 4;
+        const float* xr = xrow + q * 4;
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int c0 = 0; c0 < hidden; c0 += 16 * BATCH) {
+            uint2 wv[BATCH];
 #pragma unroll
-        for (int l = 0; l < 8; l++) acc[l] = 0.0f;
-#pragma unroll 4
-        for (int c = 0; c + 16 <= hidden; c += 16) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(w + c);
-            const float4 x0 = *reinterpret_cast<const float4*>(xr + c);
-            const float4 x1 = *reinterpret_cast<const float4*>(xr + c + 4);
-            acc[0] = fmaf(bf16_lo(wv.x), x0.x, acc[0]);
-            acc[1] = fmaf(bf16_hi(wv.x), x0.y, acc[1]);
-            acc[2] = fmaf(bf16_lo(wv.y), x0.z, acc[2]);
-            acc[3] = fmaf(bf16_hi(wv.y), x0.w, acc[3]);
-            acc[4] = fmaf(bf16_lo(wv.z), x1.x, acc[4]);
-            acc[5] = fmaf(bf16_hi(wv.z), x1.y, acc[5]);
-            acc[6] = fmaf(bf16_lo(wv.w), x1.z, acc[6]);
-            acc[7] = fmaf(bf16_hi(wv.w), x1.w, acc[7]);
+            for (int u = 0; u < BATCH; u++)
+                wv[u] = c0 + 16 * u < hidden ? __ldg(reinterpret_cast<const uint2*>(w + c0 + 16 * u))
+                                             : make_uint2(0u, 0u);
+#pragma unroll
+            for (int u = 0; u < BATCH; u++) {
+                if (c0 + 16 * u < hidden) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xr + c0 + 16 * u);
+                    acc[0] = fmaf(bf16_lo(wv[u].x), xv.x, acc[0]);
+                    acc[1] = fmaf(bf16_hi(wv[u].x), xv.y, acc[1]);
+                    acc[2] = fmaf(bf16_lo(wv[u].y), xv.z, acc[2]);
+                    acc[3] = fmaf(bf16_hi(wv[u].y), xv.w, acc[3]);
+                }
+            }
         }
-        // acc0 + acc1 lane-wise, then the hsum tree: (v0+v4, ...) -> (s0+s2, s1+s3) -> sum.
-        float v[8];
+        // acc0 + acc1 lane-wise: lane l of the first accumulator (q = l/4) plus
+        // lane l of the second (q = 2 + l/4): the thread two to the right.
+        float v[4];
 #pragma unroll
-        for (int l = 0; l < 8; l++) v[l] = acc[l] + __shfl_xor_sync(0xffffffffu, acc[l], 1);
-        const float s0 = v[0] + v[4], s1 = v[1] + v[5], s2 = v[2] + v[6], s3 = v[3] + v[7];
-        float y = (s0 + s2) + (s1 + s3);
-        if (valid && half == 0) {
+        for (int l = 0; l < 4; l++) v[l] = acc[l] + __shfl_xor_sync(0xffffffffu, acc[l], 2);
+        // Now q = 0 holds v0..v3 and q = 1 holds v4..v7 (q = 2,3 hold copies).
+        // hsum: (v0+v4, v1+v5, v2+v6, v3+v7) -> (s0+s2, s1+s3) -> sum.
+        float sv[4];
+#pragma unroll
+        for (int l = 0; l < 4; l++) sv[l] = v[l] + __shfl_xor_sync(0xffffffffu, v[l], 1);
+        float y = (sv[0] + sv[2]) + (sv[1] + sv[3]);
+        if (valid && q == 0) {
             // The dot's scalar tail is an empty sum (hidden is a multiple of 32): hsum + 0.0.
             y = y + 0.0f;
             if (a.bias) y = y + a.bias[e];
@@ -156,48 +180,48 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
     __syncthreads();
+    RTL(2);
 
     // ---- top-k and gates: warp 0. Lane l holds experts l, l+32, ...
     if (warp == 0) {
         constexpr int SLOTS = MAX_EXPERTS / 32;
-        int keys[SLOTS];
+        const int nslots = (experts + 31) >> 5;
+        unsigned ukeys[SLOTS];  // order-preserving unsigned keys; 0 = not a candidate
         unsigned taken = 0;
 #pragma unroll
         for (int s = 0; s < SLOTS; s++) {
-            int e = lane + 32 * s;
-            keys[s] = e < experts ? total_key(slog[e]) : 0;
-            if (e >= experts) taken |= 1u << s;
+            const int e = lane + 32 * s;
+            // total_key is a signed order; flipping the sign bit makes it unsigned. +1 keeps 0 free
+            // (the all-ones key, -NaN's neighbour in this order, cannot occur: it would be key 2^32).
+            ukeys[s] = (s < nslots && e < experts) ? (unsigned(total_key(slog[e])) ^ 0x80000000u) : 0u;
+            if (!(s < nslots && e < experts)) taken |= 1u << s;
         }
         int my_id = 0;
         float my_val = 0.0f;
         for (int j = 0; j < topk; j++) {
-            int best_key = 0, best_idx = 0x7fffffff;
+            unsigned best_key = 0;
+            int best_idx = 0x7fffffff;
 #pragma unroll
             for (int s = 0; s < SLOTS; s++) {
-                if (!((taken >> s) & 1u)) {
-                    int idx = lane + 32 * s;
-                    if (best_idx == 0x7fffffff || keys[s] > best_key) {
-                        best_key = keys[s];
-                        best_idx = idx;
+                if (s < nslots && !((taken >> s) & 1u)) {
+                    if (best_idx == 0x7fffffff || ukeys[s] > best_key) {
+                        best_key = ukeys[s];
+                        best_idx = lane + 32 * s;
                     }
                 }
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                int ok = __shfl_xor_sync(0xffffffffu, best_key, o);
-                int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
-                bool other_better = (oi != 0x7fffffff) &&
-                                    (best_idx == 0x7fffffff || ok > best_key ||
-                                     (ok == best_key && oi < best_idx));
-                if (other_better) {
-                    best_key = ok;
-                    best_idx = oi;
-                }
-            }
-            if ((best_idx & 31) == lane) taken |= 1u << (best_idx >> 5);
+            // The largest key in the warp, then the lowest expert index among its holders.
+            const bool have = best_idx != 0x7fffffff;
+            const unsigned all_have = __ballot_sync(0xffffffffu, have);
+            const unsigned wmax = __reduce_max_sync(0xffffffffu, have ? best_key : 0u);
+            const bool tie = have && best_key == wmax;
+            const unsigned widx = __reduce_min_sync(0xffffffffu, tie ? unsigned(best_idx) : 0xffffffffu);
+            (void)all_have;
+            const int win = int(widx);
+            if ((win & 31) == lane) taken |= 1u << (win >> 5);
             if (lane == j) {
-                my_id = best_idx;
-                my_val = slog[best_idx];
+                my_id = win;
+                my_val = slog[win];
             }
         }
         const float mx = __shfl_sync(0xffffffffu, my_val, 0);
@@ -211,6 +235,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
 
+    RTL(3);
     // ---- 8-bit quantization of the row, a warp per 32-block.
     const int nb = hidden / QK;
     const int padded = (nb + SUPER - 1) / SUPER * SUPER;
@@ -242,11 +267,13 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     }
 
     // ---- the dispatch, by the last CTA to get here (batches of up to one CTA's worth of tokens).
+    RTL(4);
     if (a.fuse_dispatch) {
         __threadfence();  // this CTA's ids are visible before its ticket
         __syncthreads();
         if (tid == 0) s_last = atomicAdd(a.ticket, 1) == a.t - 1;
         __syncthreads();
+        RTL(5);
         if (s_last) {
             __threadfence();
             DispatchSmem& sm = *reinterpret_cast<DispatchSmem*>(smem);
@@ -255,7 +282,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
             if (tid == 0) *a.ticket = 0;  // ready for the next launch on this stream
         }
     }
+    RTL(6);
 }
+
 
 // One warp per row.
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, float eps, int t, int n,
@@ -272,6 +301,12 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
 }
 
 }  // namespace
+
+#ifdef TC_TIMELINE
+extern "C" int tc_debug_route_timeline(long long* out) {
+    return int(cudaMemcpyFromSymbol(out, g_route_tl, sizeof(g_route_tl)));
+}
+#endif
 
 int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x,
                  const float* norm_w, float eps, int t, Workspace& ws, cudaStream_t stream) {
