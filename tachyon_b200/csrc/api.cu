@@ -194,6 +194,7 @@ tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
     ctx->name = prop.name;
     tc::init_kernels_exact();
     tc::init_kernels_fast();
+    tc::init_kernels_route();
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_stop) != cudaSuccess) {

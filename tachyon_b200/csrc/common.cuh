@@ -64,6 +64,7 @@ struct MoeDims {
 // Opt the kernels that need it into large dynamic shared memory (once per device).
 void init_kernels_exact();
 void init_kernels_fast();
+void init_kernels_route();
 
 // How the expert products add up a row's 32-element blocks.
 enum : int {

@@ -23,27 +23,28 @@
 //    record is one bulk async copy and lands in shared memory already padded
 //    so that ldmatrix reads hit 32 distinct banks.
 //  - Persistent CTAs, one per SM; the units of experts that have tokens are
-//    cut into equal contiguous ranges per CTA; each warp streams its units'
-//    records through a private ring of shared-memory stages, completion
-//    counted on an mbarrier per stage (every wait has a spin limit).
-//  - The tokens of the expert a CTA is working on (up to 32 at a time) are
-//    staged once per CTA: int8 rows by bulk copies, their scales transposed by
-//    plain loads.
+//    cut into equal contiguous ranges per CTA, and a CTA's units go to its
+//    warps round-robin; each warp streams its units' records through a
+//    private ring of shared-memory stages, completion counted on an mbarrier
+//    per stage (every wait has a spin limit).
+//  - The tokens of the experts a CTA's range touches (two segments of up to
+//    16 tokens at a time, usually the whole range) are staged once per CTA:
+//    int8 rows by bulk copies, their scales transposed by plain loads; for the
+//    down projection the SwiGLU rows are quantized as they are staged.
 #include "experts_common.cuh"
 
 namespace tc {
 
 namespace {
 
-constexpr int F_WARPS = 16;
-constexpr int F_THREADS = F_WARPS * 32;
+constexpr int F_MAX_WARPS = 16;   // warps per CTA: 16, or fewer when that buys a deeper ring
+constexpr int F_XBUF = 2;         // segments whose tokens are staged at the same time
 constexpr int F_KC = 256;         // columns per record
 constexpr int F_NBC = F_KC / QK;  // blocks per record
 constexpr int F_ROWS = 16;        // weight rows per unit (one m16 tile)
 constexpr int F_GMAX = 2;         // token tiles of 8 held in registers
 constexpr int F_TOK = 8 * F_GMAX; // tokens staged per segment
 constexpr int F_MAX_STAGES = 6;
-static_assert(F_TOK <= 32, "one lane of warp 0 stages one token row");
 constexpr size_t F_SMEM_LIMIT = 227 * 1024;
 
 template <int KIND>
@@ -66,25 +67,26 @@ struct FastArgs {
 // Shared memory carve-up (offsets in bytes).
 template <int KIND>
 struct Layout {
-    int ring, bars, xq, xsT, xsumT, active, rows, total;
-    __host__ __device__ Layout(int stages, int cols, int nbp) {
+    int ring, bars, x0, xbytes, xs_off, xsum_off, total;
+    __host__ __device__ Layout(int nwarps, int stages, int cols, int nbp) {
         int o = 0;
         ring = o;
-        o += F_WARPS * stages * Rec<KIND>::BYTES;
+        o += nwarps * stages * Rec<KIND>::BYTES;
         o = (o + 127) / 128 * 128;
-        xq = o;
-        o += F_TOK * (cols + 16);
-        xsT = o;
-        o += nbp * F_TOK * 4;
-        xsumT = o;
-        if (KIND == 2) o += nbp * F_TOK * 4;
-        active = o;
-        rows = o;
-        o += F_TOK * 4;
+        x0 = o;
+        // One staged-token buffer: int8 rows, then scales [block][token], then (4-bit) block sums.
+        xs_off = F_TOK * (cols + 16);
+        xsum_off = xs_off + nbp * F_TOK * 4;
+        xbytes = xsum_off + (KIND == 2 ? nbp * F_TOK * 4 : 0);
+        xbytes = (xbytes + 127) / 128 * 128;
+        o += F_XBUF * xbytes;
         bars = o;
-        o += (F_WARPS * F_MAX_STAGES + 1) * 8;
+        o += (F_MAX_WARPS * F_MAX_STAGES + 1) * 8;
         total = o;
     }
+    __host__ __device__ int xq(int buf) const { return x0 + buf * xbytes; }
+    __host__ __device__ int xsT(int buf) const { return x0 + buf * xbytes + xs_off; }
+    __host__ __device__ int xsumT(int buf) const { return x0 + buf * xbytes + xsum_off; }
 };
 
 // Shared-memory reads below are plain (non-volatile) asm so the compiler may
@@ -170,6 +172,9 @@ __device__ __forceinline__ float f16_scale_to_f32(uint32_t h) {
 
 // A warp's place in its sequence of (expert, token segment, unit, chunk) steps.
 // Units are numbered over the experts that have tokens; a CTA owns [lo, hi).
+// Within a CTA the units of consecutive segments go to consecutive warps
+// (rotation), so that a range spanning two experts still gives every warp one
+// unit instead of giving the first few warps two.
 struct FCursor {
     int ai;       // index into the active-expert list
     int sg0;      // first token of the segment
@@ -181,29 +186,29 @@ struct FCursor {
     bool valid;
 };
 
-template <int KIND, bool GATE_UP>
+template <int KIND>
 struct FWalker {
     const FastArgs& f;
-    const int* active;
-    const int warp, lo, hi, nchunks, upe;
+    const int warp, nwarps, lo, hi, nchunks, upe;
 
-    __device__ FWalker(const FastArgs& args, const int* act, int warp_, int lo_, int hi_)
-        : f(args), active(act), warp(warp_), lo(lo_), hi(hi_),
+    __device__ FWalker(const FastArgs& args, int warp_, int nwarps_, int lo_, int hi_)
+        : f(args), warp(warp_), nwarps(nwarps_), lo(lo_), hi(hi_),
           nchunks((args.e.cols + F_KC - 1) / F_KC), upe(args.e.units_per_expert) {}
 
     // Positions at the warp's first unit of (ai, sg0) or of the next segment that has one.
     __device__ void settle(FCursor& cur) const {
         for (;;) {
-            if (cur.ai * upe >= hi) {
+            if (lo >= hi || cur.ai * upe >= hi) {
                 cur.valid = false;
                 return;
             }
-            cur.e = active[cur.ai];
+            cur.e = f.e.active[cur.ai];
             cur.m = f.e.counts[cur.e];
             const int seg_lo = max(lo, cur.ai * upe);
             cur.seg_hi = min(hi, (cur.ai + 1) * upe);
             if (uint32_t(cur.sg0) < cur.m) {
-                cur.a = seg_lo + warp;
+                const int rot = (seg_lo - lo) % nwarps;
+                cur.a = seg_lo + (warp - rot + nwarps) % nwarps;
                 if (cur.a < cur.seg_hi) {
                     cur.c = 0;
                     cur.valid = true;
@@ -220,7 +225,7 @@ struct FWalker {
     __device__ void advance(FCursor& cur) const {
         if (++cur.c < nchunks) return;
         cur.c = 0;
-        cur.a += F_WARPS;
+        cur.a += nwarps;
         if (cur.a < cur.seg_hi) return;
         cur.sg0 += F_TOK;
         settle(cur);
@@ -354,7 +359,7 @@ __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t
 
 #ifdef TC_TIMELINE
 // Diagnostic build only: cycle stamps per (CTA, warp, event).
-__device__ long long g_timeline[148][F_WARPS][16];
+__device__ long long g_timeline[148][F_MAX_WARPS][16];
 #define TL(k)                                                                       \
     do {                                                                            \
         if (GATE_UP && lane == 0 && blockIdx.x < 148) g_timeline[blockIdx.x][warp][k] = clock64(); \
@@ -365,21 +370,27 @@ __device__ long long g_timeline[148][F_WARPS][16];
     } while (0)
 #endif
 
+// One segment of the CTA's walk: an expert and up to F_TOK of its tokens.
+struct Segment {
+    int ai, e, sg0, ntok, G;
+    uint32_t m, base;
+    bool valid;
+};
+
 template <int KIND, bool GATE_UP>
-__global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArgs f) {
+__global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const FastArgs f) {
     using R = Rec<KIND>;
     const ExpertArgs& a = f.e;
     extern __shared__ __align__(128) uint8_t smem[];
-    const Layout<KIND> L(f.stages, a.cols, f.nbp);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+    const Layout<KIND> L(nwarps, f.stages, a.cols, f.nbp);
     const int STAGES = f.stages;
     TL(0);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
-    uint64_t* xbar = reinterpret_cast<uint64_t*>(smem + L.bars) + F_WARPS * F_MAX_STAGES;
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
-        if (warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -389,9 +400,8 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
     const int total = a.active[a.experts] * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
-    const int* s_active = a.active;
 
-    FWalker<KIND, GATE_UP> wk(f, s_active, warp, lo, hi);
+    FWalker<KIND> wk(f, warp, nwarps, lo, hi);
     FCursor prod;
     prod.ai = lo / upe;
     prod.sg0 = 0;
@@ -411,111 +421,155 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
     };
     for (int s = 0; s < STAGES - 1; s++) fill_next();
     TL(2);
-    int seg_index = 0;
 
     const int g = lane >> 2, t = lane & 3;
     const int nb = a.cols / QK;
-    const uint32_t xq_s = smem_addr(smem + L.xq), xsT_s = smem_addr(smem + L.xsT),
-                   xsumT_s = smem_addr(smem + L.xsumT);
     float acc[F_GMAX][4], off[F_GMAX][4];
     bool ok = true;
     uint32_t xphase = 0, xtok = 0;
 #ifdef TC_TIMELINE
     long long tl_wait = 0, tl_compute = 0, tl_chunks = 0, tl_fill = 0, tl_epi = 0;
+    int seg_index = 0;
 #endif
 
-    // Segments (expert, 32 tokens) of this CTA's range, the same walk in every warp.
-    for (int ai = lo / upe; ok && lo < hi && ai * upe < hi; ai++) {
-        const int e = s_active[ai];
-        const uint32_t m = a.counts[e], base = a.offsets[e];
-        for (int sg0 = 0; ok && uint32_t(sg0) < m; sg0 += F_TOK) {
-            const int ntok = min(F_TOK, int(m) - sg0);
-            const int G = (ntok + 7) >> 3;
-            // ---- stage this segment's tokens (rows past ntok repeat the last one)
-            __syncthreads();  // everyone is done with the previous segment's tokens
-            if (!GATE_UP && a.xf) {
-                // The down projection's inputs are the SwiGLU rows in f32: quantize the
-                // segment's rows here, a warp per (token, 32-block), exactly as
-                // quantize_q8 does (src/kernels.rs:84-98, applied per gathered row by
-                // src/weights.rs:652-664), straight into the staged layout.
-                float* xsT = reinterpret_cast<float*>(smem + L.xsT);
-                float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
-                // A thread per (token, 32-block): eight 16-byte loads in flight, the
-                // block's maximum and its 32 roundings in registers, no shuffles.
-                for (int task = threadIdx.x; task < G * 8 * nb; task += F_THREADS) {
-                    const int j = task / nb, b = task - j * nb;
-                    const size_t row = base + sg0 + min(j, ntok - 1);
-                    const float4* src = reinterpret_cast<const float4*>(a.xf + row * a.cols + b * QK);
-                    float4 v[8];
+    // The CTA's segments in order, the same walk in every thread.
+    Segment next;
+    next.ai = lo / upe;
+    next.sg0 = -F_TOK;
+    next.m = 0;
+    next.valid = lo < hi;
+    auto step_segment = [&](Segment& sgm) {
+        if (!sgm.valid) return;
+        sgm.sg0 += F_TOK;
+        while (uint32_t(sgm.sg0) >= sgm.m) {  // first call, or past this expert's tokens
+            if (sgm.m != 0) sgm.ai++;
+            if (sgm.ai * upe >= hi) {
+                sgm.valid = false;
+                return;
+            }
+            sgm.e = a.active[sgm.ai];
+            sgm.m = a.counts[sgm.e];
+            sgm.base = a.offsets[sgm.e];
+            sgm.sg0 = 0;
+        }
+        sgm.ntok = min(F_TOK, int(sgm.m) - sgm.sg0);
+        sgm.G = (sgm.ntok + 7) >> 3;
+    };
+    step_segment(next);
+
+    while (ok && next.valid) {
+        // ---- a group: up to F_XBUF segments whose tokens are staged together, so that
+        // warps working on different experts of this CTA's range run side by side.
+        Segment seg[F_XBUF];
+        int nseg = 0;
+        for (; nseg < F_XBUF && next.valid; nseg++) {
+            seg[nseg] = next;
+            step_segment(next);
+        }
+        __syncthreads();  // everyone is done with the previous group's tokens
+        if (!GATE_UP && a.xf) {
+            // The down projection's inputs are the SwiGLU rows in f32: quantize the
+            // segments' rows here exactly as quantize_q8 does (src/kernels.rs:84-98,
+            // applied per gathered row by src/weights.rs:652-664), straight into the
+            // staged layout. A thread per (token, 32-block): eight 16-byte loads in
+            // flight, the block's maximum and its 32 roundings in registers.
 #pragma unroll
-                    for (int i = 0; i < 8; i++) v[i] = src[i];
-                    float amax = 0.0f;
+            for (int sx = 0; sx < F_XBUF; sx++) {
+                if (sx < nseg) {
+                    const Segment& sg = seg[sx];
+                    float* xsT = reinterpret_cast<float*>(smem + L.xsT(sx));
+                    float* xsumT = reinterpret_cast<float*>(smem + L.xsumT(sx));
+                    for (int task = threadIdx.x; task < sg.G * 8 * nb; task += nthreads) {
+                        const int j = task / nb, b = task - j * nb;
+                        const size_t row = sg.base + sg.sg0 + min(j, sg.ntok - 1);
+                        const float4* src = reinterpret_cast<const float4*>(a.xf + row * a.cols + b * QK);
+                        float4 v[8];
 #pragma unroll
-                    for (int i = 0; i < 8; i++)
-                        amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
-                                     fabsf(v[i].w));
-                    const float d = __fdiv_rn(amax, 127.0f);
-                    const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-                    auto q8 = [&](float x) {
-                        const float rr = roundf(x * id);
-                        return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
-                    };
-                    uint32_t packed[8];
-                    int qsum = 0;
+                        for (int i = 0; i < 8; i++) v[i] = src[i];
+                        float amax = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
-                        qsum += q0 + q1 + q2 + q3;
-                        packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) | (uint32_t(q2 & 0xFF) << 16) |
-                                    (uint32_t(q3 & 0xFF) << 24);
+                        for (int i = 0; i < 8; i++)
+                            amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
+                                         fabsf(v[i].w));
+                        const float d = __fdiv_rn(amax, 127.0f);
+                        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                        auto q8 = [&](float x) {
+                            const float rr = roundf(x * id);
+                            return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                        };
+                        uint32_t packed[8];
+                        int qsum = 0;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+                            qsum += q0 + q1 + q2 + q3;
+                            packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) |
+                                        (uint32_t(q2 & 0xFF) << 16) | (uint32_t(q3 & 0xFF) << 24);
+                        }
+                        uint4* dst = reinterpret_cast<uint4*>(smem + L.xq(sx) + j * f.x_stride + b * QK);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        xsT[b * F_TOK + j] = d;
+                        if (KIND == 2) xsumT[b * F_TOK + j] = d * float(qsum);
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(smem + L.xq + j * f.x_stride + b * QK);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    xsT[b * F_TOK + j] = d;
-                    if (KIND == 2) xsumT[b * F_TOK + j] = d * float(qsum);
                 }
-                __syncthreads();
-                // A value the compiler cannot know before the barrier: the staged reads depend on it.
-                asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
-            } else {
-                if (warp == 0) {
-                    if (lane == 0) mbar_expect_tx(xbar, uint32_t(G * 8) * a.cols);
-                    const uint32_t p = base + sg0 + min(lane, ntok - 1);
-                    const uint32_t row = GATE_UP ? a.slot_token[p] : p;
-                    __syncwarp();
-                    if (lane < G * 8)
-                        bulk_copy(smem + L.xq + lane * f.x_stride, a.xq + size_t(row) * a.cols, a.cols, xbar);
+            }
+            __syncthreads();
+            // A value the compiler cannot know before the barrier: the staged reads depend on it.
+            asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
+        } else {
+            // Token rows by plain 16-byte loads, not bulk copies: the copy engine's queue
+            // already holds this CTA's first weight records, and a bulk copy issued now
+            // would wait behind all of them.
+#pragma unroll
+            for (int sx = 0; sx < F_XBUF; sx++) {
+                if (sx < nseg) {
+                    const Segment& sg = seg[sx];
+                    const int vec_per_row = a.cols / 16;
+                    const int n = sg.G * 8 * vec_per_row;
+#pragma unroll 4
+                    for (int i = threadIdx.x; i < n; i += nthreads) {
+                        const int j = i / vec_per_row, v = i - j * vec_per_row;
+                        const uint32_t p = sg.base + sg.sg0 + min(j, sg.ntok - 1);
+                        const uint32_t row = GATE_UP ? a.slot_token[p] : p;
+                        const uint4 val = *reinterpret_cast<const uint4*>(a.xq + size_t(row) * a.cols + v * 16);
+                        *reinterpret_cast<uint4*>(smem + L.xq(sx) + j * f.x_stride + v * 16) = val;
+                    }
                 }
-                {
+            }
+#pragma unroll
+            for (int sx = 0; sx < F_XBUF; sx++) {
+                if (sx < nseg) {
                     // Scales transposed to [block][token]; token fastest, so stores do not
-                    // conflict. Each thread looks its token's row up itself (an L1 hit after
-                    // the first), so nothing here waits for another warp.
-                    const int n = nb * G * 8;
-                    float* xsT = reinterpret_cast<float*>(smem + L.xsT);
-                    float* xsumT = reinterpret_cast<float*>(smem + L.xsumT);
+                    // conflict. Each thread looks its token's row up itself.
+                    const Segment& sg = seg[sx];
+                    const int n = nb * sg.G * 8;
+                    float* xsT = reinterpret_cast<float*>(smem + L.xsT(sx));
+                    float* xsumT = reinterpret_cast<float*>(smem + L.xsumT(sx));
 #pragma unroll 2
-                    for (int i = threadIdx.x; i < n; i += F_THREADS) {
-                        const int b = i / (G * 8), j = i - b * (G * 8);
-                        const uint32_t p = base + sg0 + min(j, ntok - 1);
+                    for (int i = threadIdx.x; i < n; i += nthreads) {
+                        const int b = i / (sg.G * 8), j = i - b * (sg.G * 8);
+                        const uint32_t p = sg.base + sg.sg0 + min(j, sg.ntok - 1);
                         const uint32_t row = GATE_UP ? a.slot_token[p] : p;
                         const size_t src = size_t(row) * f.nbp + b;
                         xsT[b * F_TOK + j] = a.xs[src];
                         if (KIND == 2) xsumT[b * F_TOK + j] = a.xsum[src];
                     }
                 }
-                __syncthreads();
-                {
-                    const bool landed = mbar_wait_bounded(xbar, xphase & 1);
-                    xphase++;
-                    if (!__all_sync(0xffffffffu, landed)) ok = false;
-                    xtok = uint32_t(landed);
-                }
             }
-            if (seg_index < 3) TL(3 + 4 * seg_index);
-            bool first_chunk = true;
-            // ---- this warp's units of the segment
-            while (ok && cons.valid && cons.ai == ai && cons.sg0 == sg0) {
+            __syncthreads();
+            asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
+        }
+#ifdef TC_TIMELINE
+        if (seg_index < 3) TL(3 + 4 * seg_index);
+        bool first_chunk = true;
+#endif
+        // ---- this warp's units of the group's segments
+        for (int sx = 0; sx < nseg; sx++) {
+            const Segment& sg = seg[sx];
+            const uint32_t xq_s = smem_addr(smem + L.xq(sx)), xsT_s = smem_addr(smem + L.xsT(sx)),
+                           xsumT_s = smem_addr(smem + L.xsumT(sx));
+            while (ok && cons.valid && cons.ai == sg.ai && cons.sg0 == sg.sg0) {
 #ifdef TC_TIMELINE
                 const long long tf0 = clock64();
 #endif
@@ -544,13 +598,15 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                     ok = false;
                     break;
                 }
+#ifdef TC_TIMELINE
                 if (first_chunk && seg_index < 3) TL(4 + 4 * seg_index);
                 first_chunk = false;
+#endif
                 const uint32_t wtok = uint32_t(landed);
                 const uint32_t rec = smem_addr(ring + stage * R::BYTES);
                 const int nblk = min(F_NBC, nb - cons.c * F_NBC);
                 const int blk0 = cons.c * F_NBC;
-                if (G == 1)
+                if (sg.G == 1)
                     fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 else
                     fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
@@ -562,19 +618,19 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
 #endif
 
                 if (cons.c == wk.nchunks - 1) {
-                    const int u = cons.a - ai * upe;
+                    const int u = cons.a - sg.ai * upe;
 #pragma unroll
                     for (int nt = 0; nt < F_GMAX; nt++) {
 #pragma unroll
                         for (int i = 0; i < 2; i++) {
                             const int j = nt * 8 + 2 * t + i;
-                            if (nt < G && j < ntok) {
+                            if (nt < sg.G && j < sg.ntok) {
                                 float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
                                 if (KIND == 2) {
                                     y0 = y0 + off[nt][i];
                                     y1 = y1 + off[nt][2 + i];
                                 }
-                                const size_t p = base + sg0 + j;
+                                const size_t p = sg.base + sg.sg0 + j;
                                 if (GATE_UP) {
                                     const int col = u * 8 + g;
                                     if (col < a.out_cols) {
@@ -597,12 +653,16 @@ __global__ void __launch_bounds__(F_THREADS, 1) expert_fast_kernel(const FastArg
                 tl_epi += clock64() - te0;
 #endif
             }
-            if (seg_index < 3) TL(5 + 4 * seg_index);
-            // Keep the decision to stop uniform across the CTA's barriers.
-            ok = __syncthreads_and(ok);
-            if (seg_index < 3) TL(6 + 4 * seg_index);
-            seg_index++;
         }
+#ifdef TC_TIMELINE
+        if (seg_index < 3) TL(5 + 4 * seg_index);
+#endif
+        // Keep the decision to stop uniform across the CTA's barriers.
+        ok = __syncthreads_and(ok);
+#ifdef TC_TIMELINE
+        if (seg_index < 3) TL(6 + 4 * seg_index);
+        seg_index++;
+#endif
     }
     TL(15);
 #ifdef TC_TIMELINE
@@ -668,11 +728,31 @@ __global__ void tile_weights_kernel(const uint8_t* __restrict__ wdata, const voi
     }
 }
 
+// Warps per CTA and ring depth: as many warps as possible while each still gets
+// a ring of at least three stages (two copies in flight behind the one in use).
 template <int KIND>
-int pick_stages(int cols, int nbp) {
-    for (int s = F_MAX_STAGES; s >= 2; s--)
-        if (size_t(Layout<KIND>(s, cols, nbp).total) <= F_SMEM_LIMIT) return s;
-    return 0;
+bool pick_config(int cols, int nbp, int& nwarps, int& stages) {
+    int best_w = 0, best_s = 0;
+    for (int w = F_MAX_WARPS; w >= 8; w -= 2) {
+        int s = 0;
+        for (int k = F_MAX_STAGES; k >= 2; k--)
+            if (size_t(Layout<KIND>(w, k, cols, nbp).total) <= F_SMEM_LIMIT) {
+                s = k;
+                break;
+            }
+        if (s >= 3) {
+            nwarps = w;
+            stages = s;
+            return true;
+        }
+        if (s > best_s) {
+            best_s = s;
+            best_w = w;
+        }
+    }
+    nwarps = best_w;
+    stages = best_s;
+    return best_s >= 2;
 }
 
 template <int KIND, bool GATE_UP>
@@ -682,13 +762,13 @@ int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, cudaStream_t
     f.tiled = tiled;
     f.nbp = (e.cols / QK + SUPER - 1) / SUPER * SUPER;
     f.x_stride = e.cols + 16;
-    f.stages = pick_stages<KIND>(e.cols, f.nbp);
-    if (f.stages == 0) return -1;
+    int nwarps = 0;
+    if (!pick_config<KIND>(e.cols, f.nbp, nwarps, f.stages)) return -1;
     const int total_units = e.experts * e.units_per_expert;
     int grid = min(sms, total_units);
     if (grid < 1) grid = 1;
-    const Layout<KIND> L(f.stages, e.cols, f.nbp);
-    expert_fast_kernel<KIND, GATE_UP><<<grid, F_THREADS, L.total, stream>>>(f);
+    const Layout<KIND> L(nwarps, f.stages, e.cols, f.nbp);
+    expert_fast_kernel<KIND, GATE_UP><<<grid, nwarps * 32, L.total, stream>>>(f);
     return 1;
 }
 
@@ -726,9 +806,10 @@ size_t tiled_bytes(const MoeDims& d, const MatrixDev& m, bool gate_up) {
 
 bool fast_path_fits(const MoeDims& d, const MatrixDev& gate_up, const MatrixDev& down) {
     const int nbp_h = (d.hidden / QK + 7) / 8 * 8, nbp_i = (d.inter / QK + 7) / 8 * 8;
-    const int s1 = gate_up.kind == 1 ? pick_stages<1>(d.hidden, nbp_h) : pick_stages<2>(d.hidden, nbp_h);
-    const int s2 = down.kind == 1 ? pick_stages<1>(d.inter, nbp_i) : pick_stages<2>(d.inter, nbp_i);
-    return s1 >= 2 && s2 >= 2;
+    int w = 0, st = 0;
+    const bool g = gate_up.kind == 1 ? pick_config<1>(d.hidden, nbp_h, w, st) : pick_config<2>(d.hidden, nbp_h, w, st);
+    const bool dn = down.kind == 1 ? pick_config<1>(d.inter, nbp_i, w, st) : pick_config<2>(d.inter, nbp_i, w, st);
+    return g && dn;
 }
 
 void tile_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, uint8_t* tiled, cudaStream_t stream) {

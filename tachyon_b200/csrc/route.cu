@@ -19,6 +19,7 @@
 // float; the CPU path calls libm's expf. The two agree except where expf
 // itself is not correctly rounded, hence the 1e-5 tolerance on gates.
 #include "dispatch_common.cuh"
+#include "experts_common.cuh"
 
 namespace tc {
 
@@ -70,6 +71,7 @@ __device__ __forceinline__ float sum_squares_avx_order(const float* xr, int n, i
     return __shfl_sync(0xffffffffu, s, 0);
 }
 
+constexpr size_t ROUTE_SMEM_LIMIT = 200 * 1024;
 constexpr int ROUTE_THREADS = DISPATCH_THREADS;  // the last CTA runs the dispatch with the same threads
 
 struct RouteArgs {
@@ -87,7 +89,9 @@ struct RouteArgs {
     float* xsum;
     // dispatch outputs, used when fused
     int fuse_dispatch;
+    int stage_router;      // the router matrix fits in shared memory beside the row: stage it with bulk copies
     int* ticket;
+    int* status;
     uint32_t *counts, *offsets, *perm, *pos, *slot_token;
     int* active;
 };
@@ -105,14 +109,31 @@ __device__ long long g_route_tl[256][8];
 #endif
 
 __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a) {
-    extern __shared__ __align__(16) float smem[];
+    extern __shared__ __align__(128) float smem[];
     float* xrow = smem;                 // [hidden] the block's input row (after the norm)
     float* slog = smem + a.hidden;      // [experts]
     __shared__ float s_inv;
     __shared__ int s_last;
+    __shared__ __align__(8) uint64_t s_wbar;
     const int token = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hidden = a.hidden, experts = a.experts, topk = a.topk;
+    // The router matrix, one bulk copy per row, into rows padded by 32 bytes (so the four-thread
+    // groups of a half-warp read distinct banks). Issued first: it lands while the row is normed.
+    const int wstride = 2 * hidden + 32;
+    uint8_t* wsm = reinterpret_cast<uint8_t*>(smem) + (size_t(hidden + experts) * 4 + 127) / 128 * 128;
+    if (a.stage_router) {
+        if (tid == 0) {
+            mbar_init(&s_wbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&s_wbar, uint32_t(experts) * 2u * uint32_t(hidden));
+        }
+        __syncthreads();
+        if (warp == 0)
+            for (int e = lane; e < experts; e += 32)
+                bulk_copy(wsm + size_t(e) * wstride, a.router + size_t(e) * hidden, 2 * hidden, &s_wbar);
+    }
     const float* xin = a.x + size_t(token) * hidden;
     RTL(0);
     for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
@@ -137,12 +158,26 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // a whole batch of steps are requested before the chains run, so the loads
     // overlap instead of each waiting for the previous fma.
     constexpr int BATCH = 16;
+    bool w_landed = true;
+    if (a.stage_router) w_landed = mbar_wait_bounded(&s_wbar, 0);
     for (int e0 = 0; e0 < experts; e0 += ROUTE_THREADS / 4) {
         const int e = e0 + (tid >> 2), q = tid & 3;
         const bool valid = e < experts;
         const uint16_t* w = a.router + size_t(valid ? e : 0) * hidden + q * 4;
         const float* xr = xrow + q * 4;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (a.stage_router && w_landed) {
+            const uint8_t* ws = wsm + size_t(valid ? e : 0) * wstride + q * 8;
+#pragma unroll 8
+            for (int c = 0; c < hidden; c += 16) {
+                const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
+                const float4 xv = *reinterpret_cast<const float4*>(xr + c);
+                acc[0] = fmaf(bf16_lo(wv.x), xv.x, acc[0]);
+                acc[1] = fmaf(bf16_hi(wv.x), xv.y, acc[1]);
+                acc[2] = fmaf(bf16_lo(wv.y), xv.z, acc[2]);
+                acc[3] = fmaf(bf16_hi(wv.y), xv.w, acc[3]);
+            }
+        } else
         for (int c0 = 0; c0 < hidden; c0 += 16 * BATCH) {
             uint2 wv[BATCH];
 #pragma unroll
@@ -268,6 +303,13 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
 
     // ---- the dispatch, by the last CTA to get here (batches of up to one CTA's worth of tokens).
     RTL(4);
+    if (a.stage_router && !w_landed) {
+        // The staged copy did not arrive within the spin limit (the logits came from
+        // global memory instead). Report it, and give the copy a last bounded chance to
+        // land before this shared memory is reused or released.
+        if (tid == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
+        mbar_wait_bounded(&s_wbar, 0);
+    }
     if (a.fuse_dispatch) {
         __threadfence();  // this CTA's ids are visible before its ticket
         __syncthreads();
@@ -302,6 +344,10 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
 
 }  // namespace
 
+void init_kernels_route() {
+    cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ROUTE_SMEM_LIMIT));
+}
+
 #ifdef TC_TIMELINE
 extern "C" int tc_debug_route_timeline(long long* out) {
     return int(cudaMemcpyFromSymbol(out, g_route_tl, sizeof(g_route_tl)));
@@ -328,13 +374,17 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.xsum = ws.xsum;
     a.fuse_dispatch = t <= DISPATCH_THREADS;
     a.ticket = ws.ticket;
+    a.status = ws.status;
     a.counts = ws.counts;
     a.offsets = ws.offsets;
     a.perm = ws.perm;
     a.pos = ws.pos;
     a.slot_token = ws.slot_token;
     a.active = ws.active;
-    size_t smem = size_t(d.hidden + d.experts) * sizeof(float);
+    size_t smem = (size_t(d.hidden + d.experts) * sizeof(float) + 127) / 128 * 128;
+    const size_t staged = smem + size_t(d.experts) * (2 * size_t(d.hidden) + 32);
+    a.stage_router = staged <= ROUTE_SMEM_LIMIT;
+    if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
     route_kernel<<<t, ROUTE_THREADS, smem, stream>>>(a);
     int launched = 1;
