@@ -111,6 +111,27 @@ int tc_moe_last_routing(tc_moe_layer *layer, uint32_t *ids, float *gates, uint32
  * src/model.rs:474-482. Waits for the stream. */
 int tc_moe_last_dispatch(tc_moe_layer *layer, uint32_t *offsets, uint32_t *perm);
 
+/* The token -> expert dispatch on its own, for callers that must not allocate.
+ * It has no counterpart in the reference. Tachyon's scheduler thread drives the
+ * backend inside its step loop (src/scheduler.rs:567-722) and a backend sized to
+ * fill the device with KV-cache blocks at start-up has no memory left to ask
+ * for later; cudaMalloc and cudaFree also stall the whole device while they
+ * run. This entry point therefore allocates and frees nothing: the one piece
+ * of scratch the three-pass dispatch needs (per-CTA histograms, 64 KiB) lives
+ * in an array inside the library, held by every GPU that loads it until the
+ * process exits.
+ *   ids_dev u32[t*k]: each token's experts (what tc_moe_last_routing returns).
+ *   Outputs (device, all required): counts u32[experts], offsets
+ *   u32[experts+1], perm u32[t*k], pos u32[t*k], slot_token u32[t*k], active
+ *   i32[experts+1] (experts with tokens, ascending; [experts] = their number).
+ * Limits: t <= 16384, experts <= 256; anything beyond is refused with a
+ * message. The first call on a device looks the array's address up: make it
+ * before any stream capture. All calls on a device share the array, so two
+ * calls whose kernels overlap on the GPU race; calls on one stream do not. */
+int tc_dispatch_static(tc_ctx *ctx, const uint32_t *ids_dev, int t, int experts, int experts_per_token,
+                       uint32_t *counts_dev, uint32_t *offsets_dev, uint32_t *perm_dev, uint32_t *pos_dev,
+                       uint32_t *slot_token_dev, int32_t *active_dev);
+
 /* ---- the pre-MoE norm: kernels::rmsnorm (src/kernels.rs:522-528) per row,
  * as src/model.rs:662-667 applies it. out may alias x. */
 int tc_rmsnorm(tc_ctx *ctx, const float *x_dev, const float *weight_dev, float eps, int t, int n,

@@ -542,6 +542,15 @@ int tc_moe_last_dispatch(tc_moe_layer* layer, uint32_t* offsets, uint32_t* perm)
     return 0;
 }
 
+int tc_dispatch_static(tc_ctx* ctx, const uint32_t* ids, int t, int experts, int topk, uint32_t* counts,
+                       uint32_t* offsets, uint32_t* perm, uint32_t* pos, uint32_t* slot_token, int* active) {
+    const char* why = tc::dispatch_static(ctx->device, ids, t, experts, topk, counts, offsets, perm, pos,
+                                          slot_token, active, ctx->stream);
+    if (why) return fail(ctx, "tc_dispatch_static: %s", why);
+    ctx->launches += 3;
+    return 0;
+}
+
 int tc_rmsnorm(tc_ctx* ctx, const float* x, const float* w, float eps, int t, int n, float* out) {
     if (t <= 0 || n <= 0) return fail(ctx, "rmsnorm over nothing");
     ctx->launches += staged(ctx, 6, [&] { return tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream); });

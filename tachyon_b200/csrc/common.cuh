@@ -91,6 +91,12 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
 // Per-expert histogram, prefix scan and stable permutation of the t*k slots.
 int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
 
+// The three-pass dispatch with its scratch in an array built into the library
+// (no allocation). Returns null, or why the call was refused.
+const char* dispatch_static(int device, const uint32_t* ids, int t, int experts, int topk,
+                            uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* pos,
+                            uint32_t* slot_token, int* active, cudaStream_t stream);
+
 // gate_up rows of each expert times its tokens, SwiGLU, into ws.hidden_f.
 int launch_gate_up_exact(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
                          cudaStream_t stream);

@@ -110,4 +110,60 @@ int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream)
     return 3;
 }
 
+// ---------------------------------------------------------------------------
+// Dispatch for callers that must not allocate.
+//
+// The three-pass dispatch above needs one piece of scratch besides its inputs
+// and outputs: the per-CTA histograms (block_hist). launch_dispatch() takes it
+// from the workspace a layer allocates when it is created. The entry point
+// below instead keeps it in the array that follows, which lives in the
+// library's image: every GPU that loads the library holds these 64 KiB until
+// the process exits, and no call ever allocates or frees anything.
+//
+// Limits that follow from the array's size: at most STATIC_MAX_TOKENS tokens
+// (64 CTAs of 256) and MAX_EXPERTS experts per call.
+//
+// The array is shared by every call on a device and keeps whatever the last
+// call left in it. Nothing in it has to start at zero: pass 1 overwrites every
+// entry that passes 2 and 3 read. Two calls whose kernels overlap on the GPU
+// (different streams, or different contexts on one device) would race on it.
+constexpr int STATIC_MAX_BLOCKS = 64;
+constexpr int STATIC_MAX_TOKENS = STATIC_MAX_BLOCKS * DISPATCH_THREADS;
+static __device__ __align__(256) uint32_t g_static_block_hist[STATIC_MAX_BLOCKS * MAX_EXPERTS];
+
+namespace {
+// In host code the array's name is only a stand-in; the device address comes
+// from the runtime, once per device, and is cached here.
+constexpr int MAX_DEVICES = 64;
+uint32_t* g_static_block_hist_dev[MAX_DEVICES] = {};
+}  // namespace
+
+const char* dispatch_static(int device, const uint32_t* ids, int t, int experts, int topk,
+                            uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* pos,
+                            uint32_t* slot_token, int* active, cudaStream_t stream) {
+    if (device < 0 || device >= MAX_DEVICES) return "device ordinal out of range";
+    if (!ids || !counts || !offsets || !perm || !pos || !slot_token || !active)
+        return "an input or output pointer is null";
+    if (experts < 1 || experts > MAX_EXPERTS) return "between 1 and 256 experts";
+    if (topk < 1 || topk > MAX_TOPK || topk > experts) return "between 1 and min(32, experts) experts per token";
+    if (t < 1) return "empty batch";
+    if (t > STATIC_MAX_TOKENS) return "more than 16384 tokens: beyond the built-in scratch array";
+    if (!g_static_block_hist_dev[device]) {
+        // First call on this device (make it before any stream capture): look the
+        // array's device address up, with this device current.
+        if (cudaSetDevice(device) != cudaSuccess) return "cudaSetDevice failed";
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_block_hist) != cudaSuccess || !p)
+            return "cudaGetSymbolAddress failed for the built-in scratch array";
+        g_static_block_hist_dev[device] = static_cast<uint32_t*>(p);
+    }
+    uint32_t* block_hist = g_static_block_hist_dev[device];
+    const int blocks = (t + DISPATCH_THREADS - 1) / DISPATCH_THREADS;
+    dispatch_count_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ids, t, experts, topk, block_hist);
+    dispatch_scan_kernel<<<1, DISPATCH_THREADS, 0, stream>>>(block_hist, blocks, experts, counts, offsets, active);
+    dispatch_permute_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ids, t, experts, topk, block_hist, offsets,
+                                                                     perm, pos, slot_token);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "a dispatch kernel failed to launch";
+}
+
 }  // namespace tc

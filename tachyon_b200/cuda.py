@@ -48,6 +48,7 @@ SYMBOLS = {
     "tc_moe_forward_host": (_i, [_vp, _vp, _i, _vp]),
     "tc_moe_last_routing": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "tc_moe_last_dispatch": (_i, [_vp, _vp, _vp]),
+    "tc_dispatch_static": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp]),
     "tc_capture_begin": (_i, [_vp]),
     "tc_capture_end": (_vp, [_vp]),
@@ -198,6 +199,15 @@ class Context:
     def rmsnorm(self, x: "DeviceArray", weight: "DeviceArray", eps: float, out: "DeviceArray"):
         t, n = x.shape
         self._check(self.lib.tc_rmsnorm(self.handle, x.ptr, weight.ptr, eps, t, n, out.ptr), "tc_rmsnorm")
+
+    def dispatch_static(self, ids: "DeviceArray", t: int, experts: int, topk: int, counts: "DeviceArray",
+                        offsets: "DeviceArray", perm: "DeviceArray", pos: "DeviceArray",
+                        slot_token: "DeviceArray", active: "DeviceArray"):
+        """The token -> expert dispatch with its scratch inside the library: allocates nothing.
+        At most 16384 tokens and 256 experts; every buffer is the caller's."""
+        self._check(self.lib.tc_dispatch_static(self.handle, ids.ptr, t, experts, topk, counts.ptr, offsets.ptr,
+                                                perm.ptr, pos.ptr, slot_token.ptr, active.ptr),
+                    "tc_dispatch_static")
 
     def capture_begin(self):
         self._check(self.lib.tc_capture_begin(self.handle), "tc_capture_begin")
