@@ -132,6 +132,22 @@ int tc_dispatch_static(tc_ctx *ctx, const uint32_t *ids_dev, int t, int experts,
                        uint32_t *counts_dev, uint32_t *offsets_dev, uint32_t *perm_dev, uint32_t *pos_dev,
                        uint32_t *slot_token_dev, int32_t *active_dev);
 
+/* ---- expert parallelism over the GPUs of one node (no counterpart in the
+ * reference, which is single-device). Experts are sharded in contiguous ranges,
+ * the remainder to the low ranks (tc_ep_expert_range); the router is
+ * replicated; each rank keeps its own tokens; one process drives one GPU.
+ * Rank 0 makes an id (tc_ep_unique_id, 128 bytes), the host passes it to every
+ * rank, each calls tc_ep_init (collective). A layer made with
+ * tc_moe_ep_layer_create takes the full router and THIS rank's rows of gate_up
+ * and down; tc_moe_forward / tc_moe_block on it exchange rows with two NCCL
+ * all-to-alls per block and give the same values as one GPU would. */
+int tc_ep_unique_id(char *out128);
+int tc_ep_init(tc_ctx *ctx, const char *id128, int rank, int size);
+int tc_ep_expert_range(int experts, int rank, int size, int *first, int *count);
+tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int experts_per_token, int inter,
+                                     const tc_matrix *router, const tc_matrix *gate_up_local,
+                                     const tc_matrix *down_local, int max_tokens);
+
 /* ---- the pre-MoE norm: kernels::rmsnorm (src/kernels.rs:522-528) per row,
  * as src/model.rs:662-667 applies it. out may alias x. */
 int tc_rmsnorm(tc_ctx *ctx, const float *x_dev, const float *weight_dev, float eps, int t, int n,

@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "ep.cuh"
 
 struct tc_ctx {
     int device = 0;
@@ -29,6 +30,7 @@ struct tc_ctx {
     size_t ev_used = 0;
     struct Span { int stage; size_t a, b; int launches; };
     std::vector<Span> spans;
+    tc::EpState ep;           // expert parallelism (size 1 until tc_ep_init)
     float* host_x = nullptr;  // device staging for the host-buffer entry point
     float* host_y = nullptr;
     size_t host_elems = 0;
@@ -50,6 +52,8 @@ struct tc_moe_layer {
     int last_t = 0;
     uint8_t* gate_up_tiled = nullptr;  // the fast kernels' record layout of the two expert matrices
     uint8_t* down_tiled = nullptr;
+    bool ep = false;                   // expert-parallel layer: gate_up/down hold this rank's experts only
+    tc::EpLayerBuffers epb;
 };
 
 struct tc_graph {
@@ -211,6 +215,7 @@ void tc_destroy(tc_ctx* ctx) {
     ws_release(ctx);
     if (ctx->host_x) cudaFree(ctx->host_x);
     if (ctx->host_y) cudaFree(ctx->host_y);
+    tc::ep_destroy(ctx->ep);
     for (cudaEvent_t e : ctx->ev_pool) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev_start);
     cudaEventDestroy(ctx->ev_stop);
@@ -374,13 +379,53 @@ void tc_matrix_free(tc_matrix* m) {
     delete m;
 }
 
+namespace {
+tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inter, const tc_matrix* router,
+                           const tc_matrix* gate_up, const tc_matrix* down, int max_tokens, bool ep);
+}
+
 tc_moe_layer* tc_moe_layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inter,
                                   const tc_matrix* router, const tc_matrix* gate_up,
                                   const tc_matrix* down, int max_tokens) {
+    return layer_create(ctx, hidden, experts, k, inter, router, gate_up, down, max_tokens, false);
+}
+
+tc_moe_layer* tc_moe_ep_layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inter,
+                                     const tc_matrix* router, const tc_matrix* gate_up_local,
+                                     const tc_matrix* down_local, int max_tokens) {
+    if (!ctx->ep.comm) {
+        fail(ctx, "tc_moe_ep_layer_create: call tc_ep_init first");
+        return nullptr;
+    }
+    return layer_create(ctx, hidden, experts, k, inter, router, gate_up_local, down_local, max_tokens, true);
+}
+
+int tc_ep_unique_id(char* out128) { return tc::ep_unique_id(out128) ? -1 : 0; }
+
+int tc_ep_init(tc_ctx* ctx, const char* id128, int rank, int size) {
+    cudaSetDevice(ctx->device);
+    const char* why = tc::ep_init(ctx->ep, id128, rank, size);
+    return why ? fail(ctx, "tc_ep_init: %s", why) : 0;
+}
+
+int tc_ep_expert_range(int experts, int rank, int size, int* first, int* count) {
+    if (size < 1 || rank < 0 || rank >= size) return -1;
+    tc::ep_expert_range(experts, rank, size, first, count);
+    return 0;
+}
+
+}  // extern "C"
+
+namespace {
+tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inter, const tc_matrix* router,
+                           const tc_matrix* gate_up, const tc_matrix* down, int max_tokens, bool ep) {
     auto bad = [&](const char* why) -> tc_moe_layer* {
         fail(ctx, "tc_moe_layer_create: %s", why);
         return nullptr;
     };
+    int local = experts, first = 0;
+    if (ep) tc::ep_expert_range(experts, ctx->ep.rank, ctx->ep.size, &first, &local);
+    (void)first;
     if (!router || !gate_up || !down) return bad("a matrix is null");
     if (hidden <= 0 || hidden % 32 || inter <= 0 || inter % 32)
         return bad("hidden and intermediate sizes must be positive multiples of 32");
@@ -392,36 +437,49 @@ tc_moe_layer* tc_moe_layer_create(tc_ctx* ctx, int hidden, int experts, int k, i
         return bad("the router must be bf16 [experts, hidden]");
     if (gate_up->dev.kind == TC_BF16 || down->dev.kind == TC_BF16)
         return bad("expert matrices must be 8-bit or 4-bit");
-    if (gate_up->dev.rows != size_t(experts) * 2 * inter || gate_up->dev.cols != size_t(hidden))
-        return bad("gate_up must be [experts*2*inter, hidden]");
-    if (down->dev.rows != size_t(experts) * hidden || down->dev.cols != size_t(inter))
-        return bad("down must be [experts*hidden, inter]");
+    if (gate_up->dev.rows != size_t(local) * 2 * inter || gate_up->dev.cols != size_t(hidden))
+        return bad("gate_up must be [experts*2*inter, hidden] (this rank's experts when expert-parallel)");
+    if (down->dev.rows != size_t(local) * hidden || down->dev.cols != size_t(inter))
+        return bad("down must be [experts*hidden, inter] (this rank's experts when expert-parallel)");
+    if (ep && local == 0) return bad("more ranks than experts");
     cudaSetDevice(ctx->device);
     tc::MoeDims d{hidden, experts, k, inter};
     if (!ws_reserve(ctx, d, max_tokens)) return nullptr;
     if (!tc::fast_path_fits(d, gate_up->dev, down->dev)) return bad("hidden or intermediate size too large for the staged-token buffers");
     tc_moe_layer* l = new tc_moe_layer{ctx, d, router, gate_up, down, nullptr, max_tokens, 0};
+    l->ep = ep;
+    tc::MoeDims dl = d;  // the shape of the matrices held here
+    dl.experts = local;
+    if (ep && !tc::ep_layer_alloc(l->epb, ctx->ep, d, max_tokens)) {
+        tc::ep_layer_free(l->epb);
+        delete l;
+        return bad("could not allocate the exchange buffers");
+    }
     void *gu = nullptr, *dn = nullptr;
-    if (!cuda_ok(ctx, cudaMalloc(&gu, tc::tiled_bytes(d, gate_up->dev, true) + 256), "cudaMalloc(tiled gate_up)") ||
-        !cuda_ok(ctx, cudaMalloc(&dn, tc::tiled_bytes(d, down->dev, false) + 256), "cudaMalloc(tiled down)")) {
+    if (!cuda_ok(ctx, cudaMalloc(&gu, tc::tiled_bytes(dl, gate_up->dev, true) + 256), "cudaMalloc(tiled gate_up)") ||
+        !cuda_ok(ctx, cudaMalloc(&dn, tc::tiled_bytes(dl, down->dev, false) + 256), "cudaMalloc(tiled down)")) {
         if (gu) cudaFree(gu);
         delete l;
         return nullptr;
     }
     l->gate_up_tiled = static_cast<uint8_t*>(gu);
     l->down_tiled = static_cast<uint8_t*>(dn);
-    tc::tile_weights(d, gate_up->dev, true, l->gate_up_tiled, ctx->stream);
-    tc::tile_weights(d, down->dev, false, l->down_tiled, ctx->stream);
+    tc::tile_weights(dl, gate_up->dev, true, l->gate_up_tiled, ctx->stream);
+    tc::tile_weights(dl, down->dev, false, l->down_tiled, ctx->stream);
     if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "weight tiling")) {
         tc_moe_layer_free(l);
         return nullptr;
     }
     return l;
 }
+}  // namespace
+
+extern "C" {
 
 void tc_moe_layer_free(tc_moe_layer* layer) {
     if (!layer) return;
     if (layer->bias) cudaFree(layer->bias);
+    if (layer->ep) tc::ep_layer_free(layer->epb);
     if (layer->gate_up_tiled) cudaFree(layer->gate_up_tiled);
     if (layer->down_tiled) cudaFree(layer->down_tiled);
     delete layer;
@@ -454,6 +512,17 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     tc::Workspace& ws = ctx->ws;
     cudaStream_t s = ctx->stream;
     int n = 0;
+    if (layer->ep) {
+        if (ctx->capturing) return fail(ctx, "the expert-parallel block reads exchange sizes on the host: it cannot be captured");
+        const char* why = tc::ep_forward(ctx->ep, layer->epb, d, static_cast<const uint16_t*>(layer->router->dev.data),
+                                         layer->bias, layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                         layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
+        ctx->launches += n;
+        layer->last_t = t;
+        if (why) return fail(ctx, "expert-parallel block: %s", why);
+        if (!cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+        return 0;
+    }
     n += staged(ctx, 0, [&] {
         return tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
                                 x, norm_w, eps, t, ws, s);

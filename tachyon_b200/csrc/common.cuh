@@ -119,6 +119,9 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
                      Workspace& ws, int sms, cudaStream_t stream);
 
 // y[i] += sum over the token's experts, ascending expert index, gate * out.
+int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
+                          const uint32_t* out_rows, int sms, cudaStream_t stream);
+
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);
 
 int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, float* out,

@@ -1,0 +1,285 @@
+// Expert parallelism over the GPUs of one node: experts are sharded by
+// contiguous ranges (the remainder to the low ranks), the router is replicated,
+// tokens stay data-parallel, and each MoE block exchanges rows twice with an
+// all-to-all-v over NCCL (NVLink / NVSwitch): quantized token rows out to the
+// ranks that own their experts, expert outputs back.
+//
+// Tachyon itself is single-device; this file has no counterpart there. What it
+// preserves is the block's arithmetic: every (token, expert) slot is computed by
+// the same kernels on the same quantized row as on one GPU, and the returning
+// rows are combined by the same kernel in the same ascending-expert order, so
+// the result is bit-identical to the single-GPU fast path.
+//
+// One block, on the context's stream:
+//   1. route + dispatch over ALL experts (slots sorted by global expert, so the
+//      slots bound for one rank are contiguous);
+//   2. gather the slots' int8 rows and scales into send order;
+//   3. all-gather the per-expert histograms, read them on the host (sizes of the
+//      variable-length exchange have to be known there);
+//   4. all-to-all-v of rows and scales;
+//   5. merge the received runs into per-local-expert lists;
+//   6. gate_up + SwiGLU, down (output rows written in receive order);
+//   7. all-to-all-v back; 8. combine.
+// No kernel here reads a peer's memory; NCCL moves the data.
+#include <dlfcn.h>
+#include <nccl.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "ep.cuh"
+#include "experts_common.cuh"
+
+namespace tc {
+
+namespace {
+
+struct NcclApi {
+    void* lib = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+NcclApi& nccl() {
+    static NcclApi api;
+    if (api.lib) return api;
+    // The soname resolves to a copy already in the process (PyTorch bundles one) or the system's.
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return api;
+    auto sym = [&](const char* name) { return dlsym(h, name); };
+    api.GetUniqueId = reinterpret_cast<decltype(api.GetUniqueId)>(sym("ncclGetUniqueId"));
+    api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
+    api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
+    api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
+    api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
+    api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
+    api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
+    api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
+    if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.Send && api.Recv &&
+        api.GroupStart && api.GroupEnd)
+        api.lib = h;
+    return api;
+}
+
+// send_xq[p] = xq[slot_token[p]], send_xs[p] = xs[slot_token[p]]: the slots' rows in
+// expert-contiguous (= destination-contiguous) order.
+__global__ void gather_rows_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+                                   const uint32_t* __restrict__ slot_token, int slots, int hidden, int nbp,
+                                   int8_t* __restrict__ send_xq, float* __restrict__ send_xs) {
+    const int vec = hidden / 16;
+    for (int p = blockIdx.x; p < slots; p += gridDim.x) {
+        const size_t row = slot_token[p];
+        const uint4* src = reinterpret_cast<const uint4*>(xq + row * hidden);
+        uint4* dst = reinterpret_cast<uint4*>(send_xq + size_t(p) * hidden);
+        for (int i = threadIdx.x; i < vec; i += blockDim.x) dst[i] = src[i];
+        for (int i = threadIdx.x; i < nbp; i += blockDim.x) send_xs[size_t(p) * nbp + i] = xs[row * nbp + i];
+    }
+}
+
+// From every rank's histogram over all experts: this rank's per-local-expert
+// counts, offsets and active list, and for each expert-contiguous slot its row
+// in the receive buffer (rows arrive grouped by source rank, and within a
+// source by expert). One CTA.
+__global__ void merge_received_kernel(const uint32_t* __restrict__ hist_all, int ranks, int experts,
+                                      int first, int local, uint32_t* __restrict__ counts,
+                                      uint32_t* __restrict__ offsets, int* __restrict__ active,
+                                      uint32_t* __restrict__ slot_row) {
+    __shared__ uint32_t s_off[MAX_EXPERTS + 1];
+    __shared__ uint32_t s_recv_off[64 + 1];
+    const int tid = threadIdx.x;
+    if (tid == 0) {
+        uint32_t run = 0;
+        for (int s = 0; s < ranks; s++) {
+            s_recv_off[s] = run;
+            for (int e = 0; e < local; e++) run += hist_all[size_t(s) * experts + first + e];
+        }
+        s_recv_off[ranks] = run;
+        uint32_t off = 0;
+        int n = 0;
+        for (int e = 0; e < local; e++) {
+            uint32_t c = 0;
+            for (int s = 0; s < ranks; s++) c += hist_all[size_t(s) * experts + first + e];
+            counts[e] = c;
+            s_off[e] = off;
+            offsets[e] = off;
+            off += c;
+            if (c) active[n++] = e;
+        }
+        s_off[local] = off;
+        offsets[local] = off;
+        active[local] = n;
+    }
+    __syncthreads();
+    // (expert, source) runs, one per thread at a time.
+    for (int run = tid; run < local * ranks; run += blockDim.x) {
+        const int e = run / ranks, s = run - e * ranks;
+        uint32_t before_sources = 0;  // slots of expert e from sources < s
+        for (int s2 = 0; s2 < s; s2++) before_sources += hist_all[size_t(s2) * experts + first + e];
+        uint32_t before_experts = 0;  // rows of source s for local experts < e
+        for (int e2 = 0; e2 < e; e2++) before_experts += hist_all[size_t(s) * experts + first + e2];
+        const uint32_t n = hist_all[size_t(s) * experts + first + e];
+        const uint32_t dst = s_off[e] + before_sources, src = s_recv_off[s] + before_experts;
+        for (uint32_t i = 0; i < n; i++) slot_row[dst + i] = src + i;
+    }
+}
+
+}  // namespace
+
+void ep_expert_range(int experts, int rank, int size, int* first, int* count) {
+    const int base = experts / size, rem = experts % size;
+    *first = rank * base + (rank < rem ? rank : rem);
+    *count = base + (rank < rem ? 1 : 0);
+}
+
+const char* ep_unique_id(char* out128) {
+    NcclApi& n = nccl();
+    if (!n.lib) return "libnccl.so.2 could not be loaded";
+    ncclUniqueId id;
+    if (n.GetUniqueId(&id) != ncclSuccess) return "ncclGetUniqueId failed";
+    memcpy(out128, id.internal, NCCL_UNIQUE_ID_BYTES);
+    return nullptr;
+}
+
+const char* ep_init(EpState& st, const char* id128, int rank, int size) {
+    NcclApi& n = nccl();
+    if (!n.lib) return "libnccl.so.2 could not be loaded";
+    if (size < 1 || size > 64 || rank < 0 || rank >= size) return "bad rank or size";
+    ncclUniqueId id;
+    memcpy(id.internal, id128, NCCL_UNIQUE_ID_BYTES);
+    if (n.CommInitRank(&st.comm, size, id, rank) != ncclSuccess) return "ncclCommInitRank failed";
+    st.rank = rank;
+    st.size = size;
+    return nullptr;
+}
+
+void ep_destroy(EpState& st) {
+    if (st.comm) nccl().CommDestroy(st.comm);
+    st.comm = nullptr;
+    if (st.hist_host) cudaFreeHost(st.hist_host);
+    st.hist_host = nullptr;
+}
+
+bool ep_layer_alloc(EpLayerBuffers& b, const EpState& st, const MoeDims& d, int max_tokens) {
+    ep_expert_range(d.experts, st.rank, st.size, &b.first, &b.local);
+    const size_t slots = size_t(max_tokens) * d.topk;
+    b.capacity = slots * st.size;  // every rank could send everything here
+    const size_t nbp_h = (d.hidden / QK + 7) / 8 * 8;
+    auto get = [&](auto*& p, size_t elems) {
+        void* raw = nullptr;
+        if (cudaMalloc(&raw, elems * sizeof(*p) + 256) != cudaSuccess) return false;
+        b.allocs.push_back(raw);
+        p = static_cast<std::remove_reference_t<decltype(p)>>(raw);
+        return true;
+    };
+    return get(b.send_xq, slots * d.hidden) && get(b.send_xs, slots * nbp_h) &&
+           get(b.recv_xq, b.capacity * d.hidden) && get(b.recv_xs, b.capacity * nbp_h) &&
+           get(b.hist_all, size_t(st.size) * d.experts) && get(b.counts, size_t(b.local) + 1) &&
+           get(b.offsets, size_t(b.local) + 2) && get(b.active, size_t(b.local) + 2) &&
+           get(b.slot_row, b.capacity) && get(b.hidden_f, b.capacity * d.inter) &&
+           get(b.out_recv, b.capacity * d.hidden);
+}
+
+void ep_layer_free(EpLayerBuffers& b) {
+    for (void* p : b.allocs) cudaFree(p);
+    b.allocs.clear();
+}
+
+// The block over expert-parallel ranks. `gate_up_tiled` / `down_tiled` hold this
+// rank's experts only; `local_dims` is the shape with experts = b.local.
+const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
+                       const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
+                       const MatrixDev& down, const uint8_t* down_tiled, const float* x,
+                       const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
+                       cudaStream_t stream, int* launches) {
+    NcclApi& n = nccl();
+    const int R = st.size;
+    const int nbp = (d.hidden / QK + 7) / 8 * 8;
+    const int slots = t * d.topk;
+    *launches += launch_route(d, router, bias, x, norm_w, eps, t, ws, stream);
+    gather_rows_kernel<<<min(slots, 148 * 8), 128, 0, stream>>>(ws.xq, ws.xs, ws.slot_token, slots, d.hidden,
+                                                               nbp, b.send_xq, b.send_xs);
+    *launches += 1;
+    // Histograms of every rank, and a copy on the host for the exchange sizes.
+    if (st.hist_host_elems < size_t(R) * d.experts) {
+        if (st.hist_host) cudaFreeHost(st.hist_host);
+        if (cudaHostAlloc(reinterpret_cast<void**>(&st.hist_host), size_t(R) * d.experts * 4, cudaHostAllocDefault) !=
+            cudaSuccess)
+            return "cudaHostAlloc failed";
+        st.hist_host_elems = size_t(R) * d.experts;
+    }
+    if (n.AllGather(ws.counts, b.hist_all, d.experts, ncclUint32, st.comm, stream) != ncclSuccess)
+        return "ncclAllGather failed";
+    cudaMemcpyAsync(st.hist_host, b.hist_all, size_t(R) * d.experts * 4, cudaMemcpyDeviceToHost, stream);
+    if (cudaStreamSynchronize(stream) != cudaSuccess) return "stream sync failed";
+
+    std::vector<size_t> send_off(R + 1, 0), recv_off(R + 1, 0);
+    for (int r = 0; r < R; r++) {
+        int first, cnt;
+        ep_expert_range(d.experts, r, R, &first, &cnt);
+        size_t s = 0;
+        for (int e = 0; e < cnt; e++) s += st.hist_host[size_t(st.rank) * d.experts + first + e];
+        send_off[r + 1] = send_off[r] + s;
+        size_t rc = 0;
+        for (int e = 0; e < b.local; e++) rc += st.hist_host[size_t(r) * d.experts + b.first + e];
+        recv_off[r + 1] = recv_off[r] + rc;
+    }
+    const size_t received = recv_off[R];
+    if (received > b.capacity) return "more rows received than the layer was sized for";
+
+    // Rows and scales out.
+    n.GroupStart();
+    for (int r = 0; r < R; r++) {
+        const size_t sc = send_off[r + 1] - send_off[r], rc = recv_off[r + 1] - recv_off[r];
+        if (sc) {
+            n.Send(b.send_xq + send_off[r] * d.hidden, sc * d.hidden, ncclInt8, r, st.comm, stream);
+            n.Send(b.send_xs + send_off[r] * nbp, sc * nbp, ncclFloat32, r, st.comm, stream);
+        }
+        if (rc) {
+            n.Recv(b.recv_xq + recv_off[r] * d.hidden, rc * d.hidden, ncclInt8, r, st.comm, stream);
+            n.Recv(b.recv_xs + recv_off[r] * nbp, rc * nbp, ncclFloat32, r, st.comm, stream);
+        }
+    }
+    if (n.GroupEnd() != ncclSuccess) return "dispatch all-to-all failed";
+
+    merge_received_kernel<<<1, 256, 0, stream>>>(b.hist_all, R, d.experts, b.first, b.local, b.counts,
+                                                 b.offsets, b.active, b.slot_row);
+    *launches += 1;
+    if (received) {
+        MoeDims ld = d;
+        ld.experts = b.local;
+        Workspace lw = ws;  // the local-expert view: received rows, merged lists
+        lw.counts = b.counts;
+        lw.offsets = b.offsets;
+        lw.active = b.active;
+        lw.slot_token = b.slot_row;
+        lw.xq = b.recv_xq;
+        lw.xs = b.recv_xs;
+        lw.hidden_f = b.hidden_f;
+        lw.out = b.out_recv;
+        *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, t, lw, sms, stream);
+        *launches += launch_down_fast_rows(ld, down, down_tiled, lw, b.slot_row, sms, stream);
+    }
+
+    // Outputs back to the ranks the slots came from, into their expert-contiguous order.
+    n.GroupStart();
+    for (int r = 0; r < R; r++) {
+        const size_t sc = send_off[r + 1] - send_off[r], rc = recv_off[r + 1] - recv_off[r];
+        if (rc) n.Send(b.out_recv + recv_off[r] * d.hidden, rc * d.hidden, ncclFloat32, r, st.comm, stream);
+        if (sc) n.Recv(ws.out + send_off[r] * d.hidden, sc * d.hidden, ncclFloat32, r, st.comm, stream);
+    }
+    if (n.GroupEnd() != ncclSuccess) return "combine all-to-all failed";
+    *launches += launch_combine(d, t, ws, y, stream);
+    return nullptr;
+}
+
+}  // namespace tc

@@ -30,6 +30,7 @@ struct ExpertArgs {
     const float* xf;          // when set: f32 activation rows [rows, cols] to quantize while staging
     float* out;               // gate_up: hidden_f [slots, inter]; down: out [slots, hidden]
     int out_cols;
+    const uint32_t* out_rows;  // when set: output row of sorted slot p (expert parallel: its row in the receive order)
     int* status;
 };
 

@@ -630,7 +630,8 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                                     y0 = y0 + off[nt][i];
                                     y1 = y1 + off[nt][2 + i];
                                 }
-                                const size_t p = sg.base + sg.sg0 + j;
+                                size_t p = sg.base + sg.sg0 + j;
+                                if (!GATE_UP && a.out_rows) p = a.out_rows[p];
                                 if (GATE_UP) {
                                     const int col = u * 8 + g;
                                     if (col < a.out_cols) {
@@ -836,6 +837,16 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled,
     (void)t;
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;  // quantized while staged: no separate pass over the SwiGLU rows
+    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
+}
+
+// The down projection with each output row written to out_rows[slot] (expert
+// parallelism: the row's place in the receive order).
+int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, Workspace& ws,
+                          const uint32_t* out_rows, int sms, cudaStream_t stream) {
+    ExpertArgs a = down_args(d, m, ws);
+    a.xf = ws.hidden_f;
+    a.out_rows = out_rows;
     return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
 }
 

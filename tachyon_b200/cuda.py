@@ -48,6 +48,10 @@ SYMBOLS = {
     "tc_moe_forward_host": (_i, [_vp, _vp, _i, _vp]),
     "tc_moe_last_routing": (_i, [_vp, _vp, _vp, _vp, _vp]),
     "tc_moe_last_dispatch": (_i, [_vp, _vp, _vp]),
+    "tc_ep_unique_id": (_i, [C.c_char_p]),
+    "tc_ep_init": (_i, [_vp, C.c_char_p, _i, _i]),
+    "tc_ep_expert_range": (_i, [_i, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "tc_moe_ep_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "tc_dispatch_static": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp]),
     "tc_capture_begin": (_i, [_vp]),

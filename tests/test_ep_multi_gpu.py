@@ -1,0 +1,87 @@
+"""Expert parallelism on real GPUs (needs at least two): every rank's shard of
+the expert-parallel block must equal, bit for bit, the same tokens through the
+single-GPU block on its own device."""
+import os
+import sys
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _device_count():
+    import ctypes
+
+    try:
+        rt = ctypes.CDLL("libcudart.so.12")
+    except OSError:
+        try:
+            import torch
+
+            return torch.cuda.device_count()
+        except Exception:
+            return 0
+    n = ctypes.c_int(0)
+    return n.value if rt.cudaGetDeviceCount(ctypes.byref(n)) == 0 else 0
+
+
+def _rank_main(rank, size, tmp, fmt, tokens):
+    sys.path.insert(0, ROOT)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    from tachyon_b200 import cuda, ep, workloads
+
+    ctx = cuda.Context(rank)
+    uid_path = os.path.join(tmp, "uid")
+    if rank == 0:
+        uid = ep.unique_id(ctx)
+        with open(uid_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.rename(uid_path + ".tmp", uid_path)
+    else:
+        for _ in range(600):
+            if os.path.exists(uid_path):
+                break
+            time.sleep(0.05)
+        uid = open(uid_path, "rb").read()
+    ep.init(ctx, uid, rank, size)
+    shape = workloads.MoeShape("ep", 512, 10, 4, 128, fmt=fmt)
+    lw = workloads.layer_weights(shape, seed=6)
+    x_all = workloads.hidden_states(shape, tokens, seed=7)
+    y0_all = workloads.hidden_states(shape, tokens, seed=8)
+    # single GPU, all tokens
+    full = cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, tokens)
+    xd, yd = ctx.to_device(x_all), ctx.to_device(y0_all)
+    full.forward(xd, yd)
+    ctx.sync()
+    want = yd.get()
+    # expert parallel, this rank's tokens
+    gu, dn = ep.local_experts(lw.gate_up, lw.down, shape.experts, rank, size)
+    t0, tn = ep.shard_range(tokens, rank, size)
+    layer = ep.EpMoeLayer(ctx, lw.router, gu, dn, shape.experts, shape.topk, max(tn, 1))
+    for _ in range(2):  # twice: buffers are reused
+        xs, ys = ctx.to_device(x_all[t0:t0 + tn]), ctx.to_device(y0_all[t0:t0 + tn])
+        layer.forward(xs, ys)
+        ctx.sync()
+        got = ys.get()
+        assert np.array_equal(got, want[t0:t0 + tn]), (rank, np.abs(got - want[t0:t0 + tn]).max())
+    layer.free()
+    full.free()
+    ctx.close()
+
+
+@pytest.mark.parametrize("fmt,tokens", [("q8", 64), ("q4", 37), ("q8", 600)])
+def test_expert_parallel_block_equals_single_gpu(tmp_path, fmt, tokens):
+    n = _device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    from tachyon_b200 import build
+
+    build.build()
+    size = 4 if n >= 4 else 2
+    mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens), nprocs=size, join=True,
+                       start_method="spawn")
