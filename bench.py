@@ -159,7 +159,9 @@ def config_dict(args, shape, world):
         "global_batch": args.batch * world,
         "layers": args.layers,
         "weights": "q8 (int8 + f16 scale per 32), router bf16",
-        "parallelism": "1 GPU" if world == 1 else f"{world} independent replicas (expert-parallel path: see DESIGN.md)",
+        "parallelism": "1 GPU" if world == 1 else
+                       f"ep{world}: experts sharded over {world} GPUs (contiguous ranges), tokens data-parallel, "
+                       f"NCCL all-to-all-v dispatch and combine per block",
         "l2": "each step streams every layer's expert weights (1.28 GB at 24 layers), more than the 126 MB L2",
     }
 
@@ -204,8 +206,23 @@ def main():
         dist.barrier()
     ctx = cuda.Context(local_rank)
 
-    weights_host, gen_s = build_weights(shape, args.layers, args.seed, host_threads)
-    layers = [cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, args.batch) for lw in weights_host]
+    if world == 1:
+        weights_host, gen_s = build_weights(shape, args.layers, args.seed, host_threads)
+        layers = [cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, args.batch) for lw in weights_host]
+    else:
+        from tachyon_b200 import ep
+
+        box = [ep.unique_id(ctx) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ep.init(ctx, box[0], rank, world)
+        first, count = ep.shard_range(shape.experts, rank, world)
+        t0 = time.time()
+        layers = []
+        for l in range(args.layers):
+            lw = workloads.layer_weights_local(shape, first, count, seed=args.seed, layer=l, threads=host_threads)
+            layers.append(ep.EpMoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.experts, shape.topk, args.batch))
+        gen_s = time.time() - t0
+        weights_host = None
     ones = ctx.to_device(np.ones(shape.hidden, np.float32))
     x_host = ctx.pinned((args.batch, shape.hidden))
     x_host[:] = workloads.hidden_states(shape, args.batch, seed=args.seed + rank)
@@ -221,23 +238,31 @@ def main():
     # ---- eager pass with per-kernel events: which kernel dominates, and its bandwidth
     enqueue_stack()
     ctx.sync()
-    ctx.profile_enable(True)
-    distinct = []
-    prof_steps = 3
-    for s in range(prof_steps):
-        ctx.copy(x, x_in)
-        for layer in layers:
-            layer.block(ones, EPS, x)
-            if s == 0:
-                _, _, counts, _ = layer.last_routing(args.batch)
-                distinct.append(int(np.count_nonzero(counts)))
-    prof = ctx.profile_read()
-    ctx.profile_enable(False)
+    distinct, prof = [], {}
+    if world == 1:
+        ctx.profile_enable(True)
+        for s in range(3):
+            ctx.copy(x, x_in)
+            for layer in layers:
+                layer.block(ones, EPS, x)
+                if s == 0:
+                    _, _, counts, _ = layer.last_routing(args.batch)
+                    distinct.append(int(np.count_nonzero(counts)))
+        prof = ctx.profile_read()
+        ctx.profile_enable(False)
 
-    # ---- captured stack, device-resident inputs
-    ctx.capture_begin()
-    enqueue_stack()
-    graph = ctx.capture_end()
+    # ---- the timed stack, device-resident inputs: one CUDA graph per step on one GPU;
+    # the expert-parallel block reads exchange sizes on the host, so it is enqueued directly.
+    class Eager:
+        def launch(self):
+            enqueue_stack()
+
+    if world == 1:
+        ctx.capture_begin()
+        enqueue_stack()
+        graph = ctx.capture_end()
+    else:
+        graph = Eager()
     for _ in range(max(args.warmup, 3)):
         graph.launch()
     ctx.sync()
@@ -284,6 +309,27 @@ def main():
     assert np.all(np.isfinite(y_host))
 
     if rank != 0:
+        return
+    if world > 1:
+        peak, peak_kind = measured_peaks()
+        # Bytes every rank's HBM must deliver per step: its share of the selected experts' weights
+        # (all experts are hit at these batch sizes), routers, activations.
+        step_bytes = args.layers * workloads.decode_algorithmic_bytes(shape, args.batch * world, shape.experts)
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 x int8 -> i32, f32 scales", "data": "synthetic",
+            "config": config_dict(args, shape, world),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
+                    "d2h_bytes_per_step": int(y_host.nbytes), "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+            "roofline": {"bound": "hbm", "kernel": "whole step, all ranks", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9,
+                         "peak": peak * world, "unit": "GB/s", "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / (peak * world),
+                         "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs x {world} GPUs)", "traffic": None},
+            "setup_s": {"weights_host": gen_s},
+        }
+        print(json.dumps(line))
         return
 
     # ---- roofline of the dominant kernel (gate_up expert products)

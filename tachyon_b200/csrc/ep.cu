@@ -86,6 +86,27 @@ __global__ void gather_rows_kernel(const int8_t* __restrict__ xq, const float* _
     }
 }
 
+// scale * sum of the 32 quants, per (row, block): what the 4-bit offsets multiply
+// (src/weights.rs:491-507). Recomputed from the received rows rather than sent.
+__global__ void block_sums_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs, size_t rows,
+                                  int hidden, int nbp, float* __restrict__ xsum) {
+    const int nb = hidden / QK, lane = threadIdx.x & 31;
+    const size_t warp = size_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const size_t nwarps = size_t(gridDim.x) * (blockDim.x >> 5);
+    for (size_t w = warp; w < rows * nbp; w += nwarps) {
+        const size_t row = w / nbp;
+        const int b = int(w - row * nbp);
+        if (b >= nb) {
+            if (lane == 0) xsum[w] = 0.0f;
+            continue;
+        }
+        int q = xq[row * hidden + b * QK + lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+        if (lane == 0) xsum[w] = xs[row * nbp + b] * float(q);
+    }
+}
+
 // From every rank's histogram over all experts: this rank's per-local-expert
 // counts, offsets and active list, and for each expert-contiguous slot its row
 // in the receive buffer (rows arrive grouped by source rank, and within a
@@ -183,6 +204,7 @@ bool ep_layer_alloc(EpLayerBuffers& b, const EpState& st, const MoeDims& d, int 
     };
     return get(b.send_xq, slots * d.hidden) && get(b.send_xs, slots * nbp_h) &&
            get(b.recv_xq, b.capacity * d.hidden) && get(b.recv_xs, b.capacity * nbp_h) &&
+           get(b.recv_xsum, b.capacity * nbp_h) &&
            get(b.hist_all, size_t(st.size) * d.experts) && get(b.counts, size_t(b.local) + 1) &&
            get(b.offsets, size_t(b.local) + 2) && get(b.active, size_t(b.local) + 2) &&
            get(b.slot_row, b.capacity) && get(b.hidden_f, b.capacity * d.inter) &&
@@ -264,6 +286,14 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
         lw.slot_token = b.slot_row;
         lw.xq = b.recv_xq;
         lw.xs = b.recv_xs;
+        if (gate_up.kind == 2) {
+            const size_t warps = received * nbp;
+            const size_t want_blocks = (warps + 7) / 8;
+            block_sums_kernel<<<unsigned(want_blocks < 148 * 16 ? want_blocks : 148 * 16), 256, 0, stream>>>(
+                b.recv_xq, b.recv_xs, received, d.hidden, nbp, b.recv_xsum);
+            *launches += 1;
+            lw.xsum = b.recv_xsum;
+        }
         lw.hidden_f = b.hidden_f;
         lw.out = b.out_recv;
         *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, t, lw, sms, stream);

@@ -20,7 +20,7 @@ struct EpLayerBuffers {
     int first = 0, local = 0;        // this rank's expert range
     size_t capacity = 0;             // rows the receive side can hold
     int8_t *send_xq = nullptr, *recv_xq = nullptr;
-    float *send_xs = nullptr, *recv_xs = nullptr;
+    float *send_xs = nullptr, *recv_xs = nullptr, *recv_xsum = nullptr;
     uint32_t* hist_all = nullptr;    // [size, experts]
     uint32_t *counts = nullptr, *offsets = nullptr, *slot_row = nullptr;
     int* active = nullptr;

@@ -87,6 +87,36 @@ def layer_weights(shape: MoeShape, seed: int = 0, layer: int = 0, fmt: str | Non
     )
 
 
+def layer_weights_local(shape: MoeShape, first: int, count: int, seed: int = 0, layer: int = 0,
+                        fmt: str | None = None, threads: int = 1) -> LayerWeights:
+    """The full router and experts [first, first+count) of a layer: the same values
+    ``layer_weights`` gives for those rows (the generator is counter-based)."""
+    fmt = fmt or shape.fmt
+    h, e, i = shape.hidden, shape.experts, shape.inter
+
+    def rows(stream, rows_per_expert, cols):
+        n = count * rows_per_expert * cols
+        start = first * rows_per_expert * cols
+        data = np.empty(n, np.float32)
+        step = max(1 << 20, -(-n // max(1, threads)))
+        step = -(-step // 4096) * 4096
+
+        def part(lo):
+            hi = min(n, lo + step)
+            data[lo:hi] = synth.normal(seed, stream, hi - lo, layer, scale=0.02, start=start + lo)
+
+        if threads > 1:
+            with ThreadPoolExecutor(threads) as ex:
+                list(ex.map(part, range(0, n, step)))
+        else:
+            for lo in range(0, n, step):
+                part(lo)
+        return Matrix.from_f32(data, count * rows_per_expert, cols, fmt)
+
+    return LayerWeights(router=_normal_matrix(seed, synth.STREAM_ROUTER, layer, e, h, "bf16"),
+                        gate_up=rows(synth.STREAM_GATE_UP, 2 * i, h), down=rows(synth.STREAM_DOWN, h, i))
+
+
 def hidden_states(shape: MoeShape, tokens: int, seed: int = 0, layer: int = 0) -> np.ndarray:
     return synth.normal(seed, synth.STREAM_HIDDEN, tokens * shape.hidden, layer).reshape(tokens, shape.hidden)
 
