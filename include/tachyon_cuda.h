@@ -148,6 +148,13 @@ tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int e
                                      const tc_matrix *router, const tc_matrix *gate_up_local,
                                      const tc_matrix *down_local, int max_tokens);
 
+/* Self-check of the tcgen05 path's encodings (no counterpart in the reference):
+ * one 128 x n x 32 int8 MMA (n = 64 or 128) through tensor memory.
+ * a_rows_host: i8[128*32], b_rows_host: i8[n*32], row-major; d_out_host:
+ * i32[128*n] = a_rows x b_rows^T. Allocates and frees its own scratch. */
+int tc_umma_selftest(tc_ctx *ctx, const int8_t *a_rows_host, const int8_t *b_rows_host, int n,
+                     int32_t *d_out_host);
+
 /* ---- the pre-MoE norm: kernels::rmsnorm (src/kernels.rs:522-528) per row,
  * as src/model.rs:662-667 applies it. out may alias x. */
 int tc_rmsnorm(tc_ctx *ctx, const float *x_dev, const float *weight_dev, float eps, int t, int n,

@@ -620,6 +620,43 @@ int tc_dispatch_static(tc_ctx* ctx, const uint32_t* ids, int t, int experts, int
     return 0;
 }
 
+int tc_umma_selftest(tc_ctx* ctx, const int8_t* a_rows, const int8_t* b_rows, int n, int32_t* d_out) {
+    // a_rows: 128 x 32 and b_rows: n x 32 int8, row-major on the host; d_out: 128 x n int32.
+    if (n != 64 && n != 128) return fail(ctx, "tc_umma_selftest: n must be 64 or 128");
+    std::vector<int8_t> ta(128 * 32), tb(size_t(n) * 32);
+    auto off = [](uint32_t rows, uint32_t r, uint32_t k) {
+        return (k / 16) * (rows / 8) * 128 + (r / 8) * 128 + (r % 8) * 16 + k % 16;
+    };
+    for (int r = 0; r < 128; r++)
+        for (int k = 0; k < 32; k++) ta[off(128, r, k)] = a_rows[r * 32 + k];
+    for (int r = 0; r < n; r++)
+        for (int k = 0; k < 32; k++) tb[off(n, r, k)] = b_rows[r * 32 + k];
+    void *da = nullptr, *db = nullptr, *dd = nullptr, *ds = nullptr;
+    bool ok = cuda_ok(ctx, cudaMalloc(&da, ta.size()), "cudaMalloc") && cuda_ok(ctx, cudaMalloc(&db, tb.size()), "cudaMalloc") &&
+              cuda_ok(ctx, cudaMalloc(&dd, size_t(128) * n * 4), "cudaMalloc") && cuda_ok(ctx, cudaMalloc(&ds, 4), "cudaMalloc");
+    int status = 0;
+    if (ok) {
+        cudaMemcpy(da, ta.data(), ta.size(), cudaMemcpyHostToDevice);
+        cudaMemcpy(db, tb.data(), tb.size(), cudaMemcpyHostToDevice);
+        cudaMemset(dd, 0xFF, size_t(128) * n * 4);
+        cudaMemset(ds, 0, 4);
+        ctx->launches += tc::launch_umma_probe(static_cast<int8_t*>(da), static_cast<int8_t*>(db), n,
+                                              static_cast<int*>(dd), static_cast<int*>(ds), ctx->stream);
+        ok = cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "tcgen05 self-test");
+        if (ok) {
+            cudaMemcpy(d_out, dd, size_t(128) * n * 4, cudaMemcpyDeviceToHost);
+            cudaMemcpy(&status, ds, 4, cudaMemcpyDeviceToHost);
+        }
+    }
+    cudaFree(da);
+    cudaFree(db);
+    cudaFree(dd);
+    cudaFree(ds);
+    if (!ok) return -1;
+    if (status) return fail(ctx, "tc_umma_selftest: the MMA did not complete within the wait limit");
+    return 0;
+}
+
 int tc_rmsnorm(tc_ctx* ctx, const float* x, const float* w, float eps, int t, int n, float* out) {
     if (t <= 0 || n <= 0) return fail(ctx, "rmsnorm over nothing");
     ctx->launches += staged(ctx, 6, [&] { return tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream); });

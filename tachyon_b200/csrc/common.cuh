@@ -122,6 +122,10 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
                           const uint32_t* out_rows, int sms, cudaStream_t stream);
 
+// One 128 x n x 32 int8 tcgen05 MMA (n = 64 or 128) through TMEM: a self-check of the encodings.
+int launch_umma_probe(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
+                      cudaStream_t stream);
+
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);
 
 int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, float* out,

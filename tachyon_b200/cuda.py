@@ -52,6 +52,7 @@ SYMBOLS = {
     "tc_ep_init": (_i, [_vp, C.c_char_p, _i, _i]),
     "tc_ep_expert_range": (_i, [_i, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "tc_moe_ep_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
+    "tc_umma_selftest": (_i, [_vp, _vp, _vp, _i, _vp]),
     "tc_dispatch_static": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp]),
     "tc_capture_begin": (_i, [_vp]),
@@ -212,6 +213,16 @@ class Context:
         self._check(self.lib.tc_dispatch_static(self.handle, ids.ptr, t, experts, topk, counts.ptr, offsets.ptr,
                                                 perm.ptr, pos.ptr, slot_token.ptr, active.ptr),
                     "tc_dispatch_static")
+
+    def umma_selftest(self, a_rows: np.ndarray, b_rows: np.ndarray) -> np.ndarray:
+        """a_rows i8[128, 32] x b_rows i8[n, 32]^T through one tcgen05 MMA; returns i32[128, n]."""
+        a_rows = np.ascontiguousarray(a_rows, np.int8)
+        b_rows = np.ascontiguousarray(b_rows, np.int8)
+        n = b_rows.shape[0]
+        out = np.empty((128, n), np.int32)
+        self._check(self.lib.tc_umma_selftest(self.handle, _ptr(a_rows), _ptr(b_rows), n, _ptr(out)),
+                    "tc_umma_selftest")
+        return out
 
     def capture_begin(self):
         self._check(self.lib.tc_capture_begin(self.handle), "tc_capture_begin")
