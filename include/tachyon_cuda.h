@@ -51,6 +51,12 @@ void *tc_stream(tc_ctx *ctx);
 enum { TC_ARITH_FAST = 0, TC_ARITH_CPU_LANES = 1 };
 int tc_set_arithmetic(tc_ctx *ctx, int mode);
 
+/* From how many tokens per expert (batch tokens x experts per token / experts,
+ * on average) a block's expert products run on the tcgen05 tensor-core kernels
+ * instead of the bandwidth-oriented ones. Default 32; 0 = always; a huge value
+ * = never. Both give the same values (same fma chain per output). */
+int tc_set_prefill_threshold(tc_ctx *ctx, int avg_tokens_per_expert);
+
 /* ---- device buffers: replace tm_buffer / tm_buffer_contents / tm_buffer_free
  *      (src/gpu/mod.rs:125-127). HBM is not host-visible, hence the copies. */
 void *tc_malloc(tc_ctx *ctx, size_t bytes);

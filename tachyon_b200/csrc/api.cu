@@ -31,6 +31,9 @@ struct tc_ctx {
     struct Span { int stage; size_t a, b; int launches; };
     std::vector<Span> spans;
     tc::EpState ep;           // expert parallelism (size 1 until tc_ep_init)
+    tc::PrefillScratch pre;   // token tiles of the tcgen05 path
+    std::vector<void*> pre_allocs;
+    int prefill_min_avg = 32; // tokens per expert (on average) from which the tcgen05 kernels take over
     float* host_x = nullptr;  // device staging for the host-buffer entry point
     float* host_y = nullptr;
     size_t host_elems = 0;
@@ -52,6 +55,8 @@ struct tc_moe_layer {
     int last_t = 0;
     uint8_t* gate_up_tiled = nullptr;  // the fast kernels' record layout of the two expert matrices
     uint8_t* down_tiled = nullptr;
+    tc::PrefillWeights pw;             // the tcgen05 kernels' tiles of the two expert matrices
+    std::vector<void*> pw_allocs;
     bool ep = false;                   // expert-parallel layer: gate_up/down hold this rank's experts only
     tc::EpLayerBuffers epb;
 };
@@ -132,6 +137,35 @@ void ws_release(tc_ctx* ctx) {
     ctx->ws = tc::Workspace{};
 }
 
+// Scratch of the tcgen05 path: token tiles for up to max_tokens * topk slots.
+bool prefill_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
+    const int tiles = tc::prefill_max_token_tiles(max_tokens * d.topk, d.experts);
+    const int nb = std::max(d.hidden, d.inter) / 32;
+    const size_t xt_bytes = size_t(tiles) * nb * 64 * 32, xst_elems = size_t(tiles) * nb * 64;
+    tc::PrefillScratch& p = ctx->pre;
+    if (p.max_tiles >= tiles && p.xt_bytes >= xt_bytes) return true;
+    cudaStreamSynchronize(ctx->stream);
+    for (void* q : ctx->pre_allocs) cudaFree(q);
+    ctx->pre_allocs.clear();
+    p = tc::PrefillScratch{};
+    auto get = [&](auto*& dst, size_t bytes) {
+        void* raw = nullptr;
+        if (!cuda_ok(ctx, cudaMalloc(&raw, bytes + 256), "cudaMalloc(prefill scratch)")) return false;
+        ctx->pre_allocs.push_back(raw);
+        dst = static_cast<std::remove_reference_t<decltype(dst)>>(raw);
+        return true;
+    };
+    const int T = std::max(tiles, p.max_tiles);
+    if (!(get(p.tile_expert, size_t(T) * 4) && get(p.tile_n, size_t(T) * 4) && get(p.tile_count, 4) &&
+          get(p.tile_p0, size_t(T) * 4) && get(p.xt, xt_bytes) && get(p.xst, xst_elems * 4) &&
+          get(p.xsumt, xst_elems * 4)))
+        return false;
+    p.max_tiles = T;
+    p.xt_bytes = xt_bytes;
+    p.xst_elems = xst_elems;
+    return true;
+}
+
 // Grows the context's scratch so a layer of these dimensions fits.
 bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
     tc::Workspace& w = ctx->ws;
@@ -199,6 +233,7 @@ tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
     tc::init_kernels_exact();
     tc::init_kernels_fast();
     tc::init_kernels_route();
+    tc::init_kernels_prefill();
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_stop) != cudaSuccess) {
@@ -213,6 +248,7 @@ void tc_destroy(tc_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     ws_release(ctx);
+    for (void* q : ctx->pre_allocs) cudaFree(q);
     if (ctx->host_x) cudaFree(ctx->host_x);
     if (ctx->host_y) cudaFree(ctx->host_y);
     tc::ep_destroy(ctx->ep);
@@ -295,6 +331,12 @@ void tc_host_free(tc_ctx* ctx, void* host) {
 int tc_set_arithmetic(tc_ctx* ctx, int mode) {
     if (mode != TC_ARITH_FAST && mode != TC_ARITH_CPU_LANES) return fail(ctx, "unknown arithmetic mode %d", mode);
     ctx->arith = mode;
+    return 0;
+}
+
+int tc_set_prefill_threshold(tc_ctx* ctx, int avg_tokens_per_expert) {
+    if (avg_tokens_per_expert < 0) return fail(ctx, "the threshold cannot be negative");
+    ctx->prefill_min_avg = avg_tokens_per_expert;
     return 0;
 }
 
@@ -466,6 +508,28 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
     l->down_tiled = static_cast<uint8_t*>(dn);
     tc::tile_weights(dl, gate_up->dev, true, l->gate_up_tiled, ctx->stream);
     tc::tile_weights(dl, down->dev, false, l->down_tiled, ctx->stream);
+    if (!ep && tc::prefill_fits(d) && prefill_reserve(ctx, d, max_tokens)) {
+        // Third copy of the experts, for prefill-size groups: int8 tiles in the tensor core's
+        // canonical order and f32 block scales.
+        auto get = [&](auto*& dst, size_t bytes) {
+            void* raw = nullptr;
+            if (!cuda_ok(ctx, cudaMalloc(&raw, bytes + 256), "cudaMalloc(prefill weights)")) return false;
+            l->pw_allocs.push_back(raw);
+            dst = static_cast<std::remove_reference_t<decltype(dst)>>(raw);
+            return true;
+        };
+        const bool q4g = gate_up->dev.kind == TC_Q4, q4d = down->dev.kind == TC_Q4;
+        bool okp = get(l->pw.gu_t, tc::prefill_weight_bytes(d, true)) && get(l->pw.gu_d, tc::prefill_scale_elems(d, true) * 4) &&
+                   get(l->pw.dn_t, tc::prefill_weight_bytes(d, false)) && get(l->pw.dn_d, tc::prefill_scale_elems(d, false) * 4);
+        if (okp && q4g) okp = get(l->pw.gu_c, tc::prefill_scale_elems(d, true) * 4);
+        if (okp && q4d) okp = get(l->pw.dn_c, tc::prefill_scale_elems(d, false) * 4);
+        if (!okp) {
+            tc_moe_layer_free(l);
+            return nullptr;
+        }
+        tc::tile_prefill_weights(d, gate_up->dev, true, l->pw.gu_t, l->pw.gu_d, l->pw.gu_c, ctx->stream);
+        tc::tile_prefill_weights(d, down->dev, false, l->pw.dn_t, l->pw.dn_d, l->pw.dn_c, ctx->stream);
+    }
     if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "weight tiling")) {
         tc_moe_layer_free(l);
         return nullptr;
@@ -479,6 +543,7 @@ extern "C" {
 void tc_moe_layer_free(tc_moe_layer* layer) {
     if (!layer) return;
     if (layer->bias) cudaFree(layer->bias);
+    for (void* q : layer->pw_allocs) cudaFree(q);
     if (layer->ep) tc::ep_layer_free(layer->epb);
     if (layer->gate_up_tiled) cudaFree(layer->gate_up_tiled);
     if (layer->down_tiled) cudaFree(layer->down_tiled);
@@ -528,6 +593,24 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
                                 x, norm_w, eps, t, ws, s);
     });
     const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
+    const bool prefill = !lanes && layer->pw.gu_t &&
+                         (long long)t * d.topk >= (long long)ctx->prefill_min_avg * d.experts;
+    if (prefill) {
+        const int slots = t * d.topk;
+        n += staged(ctx, 2, [&] {
+            return tc::launch_prefill(d, true, layer->gate_up->dev.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
+                                      ws.hidden_f, nullptr, s);
+        });
+        n += staged(ctx, 4, [&] {
+            return tc::launch_prefill(d, false, layer->down->dev.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
+                                      ws.out, nullptr, s);
+        });
+        n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
+        ctx->launches += n;
+        layer->last_t = t;
+        if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+        return 0;
+    }
     n += staged(ctx, 2, [&] {
         return lanes ? tc::launch_gate_up_exact(d, layer->gate_up->dev, t, ws, ctx->sms, s)
                      : tc::launch_gate_up_fast(d, layer->gate_up->dev, layer->gate_up_tiled, t, ws, ctx->sms, s);

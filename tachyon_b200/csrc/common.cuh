@@ -122,6 +122,29 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
                           const uint32_t* out_rows, int sms, cudaStream_t stream);
 
+// ---- prefill-size groups on tcgen05 (experts_prefill.cu)
+struct PrefillWeights {  // per layer: int8 tiles + f32 block scales (and 4-bit offsets)
+    int8_t *gu_t = nullptr, *dn_t = nullptr;
+    float *gu_d = nullptr, *gu_c = nullptr, *dn_d = nullptr, *dn_c = nullptr;
+};
+struct PrefillScratch {  // per context
+    int *tile_expert = nullptr, *tile_n = nullptr, *tile_count = nullptr;
+    uint32_t* tile_p0 = nullptr;
+    int8_t* xt = nullptr;
+    float *xst = nullptr, *xsumt = nullptr;
+    size_t xt_bytes = 0, xst_elems = 0;
+    int max_tiles = 0;
+};
+void init_kernels_prefill();
+bool prefill_fits(const MoeDims& d);
+size_t prefill_weight_bytes(const MoeDims& d, bool gate_up);
+size_t prefill_scale_elems(const MoeDims& d, bool gate_up);
+int prefill_max_token_tiles(int slots, int experts);
+void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, int8_t* wt, float* wd, float* wc,
+                          cudaStream_t stream);
+int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights& w, const PrefillScratch& s,
+                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream);
+
 // One 128 x n x 32 int8 tcgen05 MMA (n = 64 or 128) through TMEM: a self-check of the encodings.
 int launch_umma_probe(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
                       cudaStream_t stream);

@@ -130,39 +130,6 @@ __device__ __forceinline__ float2 lds_f2(uint32_t addr, uint32_t token) {
     return v;
 }
 
-// Two IEEE f32 operations per instruction (the results are those of the
-// scalar forms): a - m, a * b, fma(a, b, c) on register pairs.
-__device__ __forceinline__ float2 sub2(float2 a, float2 m) {
-    float2 r;
-    asm("{\n\t.reg .b64 ra, rm, rr;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rm, {%4, %5};\n\t"
-        "sub.rn.f32x2 rr, ra, rm;\n\t"
-        "mov.b64 {%0, %1}, rr;\n\t}"
-        : "=f"(r.x), "=f"(r.y)
-        : "f"(a.x), "f"(a.y), "f"(m.x), "f"(m.y));
-    return r;
-}
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-    float2 r;
-    asm("{\n\t.reg .b64 ra, rb, rr;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
-        "mul.rn.f32x2 rr, ra, rb;\n\t"
-        "mov.b64 {%0, %1}, rr;\n\t}"
-        : "=f"(r.x), "=f"(r.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-    return r;
-}
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-    float2 r;
-    asm("{\n\t.reg .b64 ra, rb, rc, rr;\n\t"
-        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
-        "fma.rn.f32x2 rr, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rr;\n\t}"
-        : "=f"(r.x), "=f"(r.y)
-        : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-    return r;
-}
-
 // f16 bits of a weight scale (finite, as every scale Tachyon stores is) to f32
 // on the full-rate pipes: the bits shifted into place, times 2^112
 // (src/kernels.rs:127-130). Exact for normals and subnormals of either sign.

@@ -1,0 +1,508 @@
+// Grouped expert products for prefill-size groups on the 5th-generation tensor
+// cores (tcgen05): int8 x int8 -> int32 MMAs issued by one thread per CTA,
+// operands staged in shared memory by bulk async copies, accumulators in tensor
+// memory (TMEM), read back with tcgen05.ld for the float work.
+//
+// Arithmetic: the same single fma chain per output as the decode-size kernel
+// (experts_fast.cu), so a token's value does not depend on which kernel ran:
+//     acc = fma(float(sum_b), ws[row,b] * xs[token,b], acc)      b = 0, 1, ...
+// One MMA has K = 32 = one quantization block, and is issued WITHOUT
+// accumulation into its own TMEM buffer: the per-block integer tile must leave
+// the tensor core to be scaled by (weight scale x activation scale) before it
+// can be added. That float work (about 2.5 instructions per output per block on
+// the CUDA cores) bounds this kernel, not the tensor pipe.
+//
+// Work decomposition: a CTA computes one output tile: 128 weight rows (for
+// gate_up: 64 gate rows interleaved with the 64 matching up rows, so SwiGLU
+// pairs sit in adjacent lanes) x 64 tokens of one expert, over all of K.
+// Roles: warp 8 streams operand chunks (8 blocks: 32 KB of weights + 16 KB of
+// activations) through a 3-stage ring; one thread of warp 9 issues the MMAs
+// into a ring of 8 TMEM buffers (64 columns each); warps 0-7 drain the buffers
+// (each TMEM lane quadrant is served by two warps, 32 columns each) and keep
+// the float chains in registers. Every wait is bounded and watches a CTA-wide
+// abort flag; TMEM is freed on every path.
+#include "experts_common.cuh"
+#include "umma.cuh"
+
+namespace tc {
+
+namespace {
+
+constexpr int P_ROWS = 128;           // MMA M
+constexpr int P_TOK = 64;             // MMA N
+constexpr int P_CHUNK = 8;            // blocks per smem stage
+constexpr int P_STAGES = 3;
+constexpr int P_TBUF = 8;             // TMEM buffers of P_TOK columns
+constexpr int P_A_BLOCK = P_ROWS * 32;  // bytes of one block of weights
+constexpr int P_B_BLOCK = P_TOK * 32;
+constexpr int P_STAGE_BYTES = P_CHUNK * (P_A_BLOCK + P_B_BLOCK);
+constexpr int P_THREADS = 320;        // 8 epilogue warps + producer + MMA
+constexpr uint32_t P_SPIN = 1u << 16;
+constexpr int P_SMEM_LIMIT = 226 * 1024;
+
+struct PrefillArgs {
+    const int8_t* wt;        // weight tiles [expert][row tile][block][128 x 32 canonical]
+    const float* wd;         // weight block scales [expert][row tile][128][nb]
+    const float* wc;         // 4-bit block offsets, same shape (null for 8-bit)
+    const int8_t* xt;        // activation tiles [token tile][block][64 x 32 canonical]
+    const float* xst;        // activation scales [token tile][nb][64]
+    const float* xsumt;      // scale * sum of quants, same shape (4-bit only)
+    const int* tile_expert;  // per token tile
+    const uint32_t* tile_p0; // first sorted slot of the tile
+    const int* tile_n;       // tokens in the tile (1..64)
+    const int* tile_count;
+    int nb, row_tiles, rows_per_expert, out_cols;
+    float* out;
+    const uint32_t* out_rows;
+    int* status;
+};
+
+// Bounded wait that also gives up when another warp of the CTA has.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < P_SPIN; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+template <bool Q4, bool GATE_UP>
+__global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const PrefillArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem;                                                  // P_STAGES x P_STAGE_BYTES
+    float* s_xs = reinterpret_cast<float*>(smem + P_STAGES * P_STAGE_BYTES);  // [nb][64]
+    float* s_xsum = s_xs + a.nb * P_TOK;                                     // [nb][64] (4-bit)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_xsum + (Q4 ? a.nb * P_TOK : 0));
+    uint64_t* full = bars;                    // [P_STAGES] operands landed
+    uint64_t* empty = bars + P_STAGES;        // [P_STAGES] MMAs that read the stage are done
+    uint64_t* tfull = bars + 2 * P_STAGES;    // [P_TBUF] a block's integer tile is in TMEM
+    uint64_t* tempty = tfull + P_TBUF;        // [P_TBUF] drained by all 8 epilogue warps
+    uint64_t* xbar = tempty + P_TBUF;         // activation scales landed
+    uint64_t* drain = xbar + 1;               // abort path only: the MMAs issued so far are done
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tt = blockIdx.y, rt = blockIdx.x;
+    if (tt >= *a.tile_count) return;  // uniform: the whole CTA leaves before touching TMEM
+    const int e = a.tile_expert[tt];
+    const int tile_n = a.tile_n[tt];
+    const uint32_t p0 = a.tile_p0[tt];
+    const int nb = a.nb;
+    const int nchunks = (nb + P_CHUNK - 1) / P_CHUNK;
+
+    if (tid == 0) {
+        for (int s = 0; s < P_STAGES; s++) {
+            mbar_init(full + s, 1);
+            mbar_init(empty + s, 1);
+        }
+        for (int b = 0; b < P_TBUF; b++) {
+            mbar_init(tfull + b, 1);
+            mbar_init(tempty + b, 8);
+        }
+        mbar_init(xbar, 1);
+        mbar_init(drain, 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 9) {
+        umma::tmem_alloc(&s_tmem, P_TBUF * P_TOK);
+        umma::tmem_relinquish();
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    volatile int* abort_flag = &s_abort;
+
+    const size_t tile_index = size_t(e) * a.row_tiles + rt;
+    if (warp == 8) {
+        // ---- producer: activation scales once, then the operand chunks
+        if (lane == 0) {
+            const uint32_t xs_bytes = uint32_t(nb) * P_TOK * 4;
+            mbar_expect_tx(xbar, Q4 ? 2 * xs_bytes : xs_bytes);
+            bulk_copy(s_xs, a.xst + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+            if (Q4) bulk_copy(s_xsum, a.xsumt + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+            const int8_t* wsrc = a.wt + tile_index * size_t(nb) * P_A_BLOCK;
+            const int8_t* xsrc = a.xt + size_t(tt) * nb * P_B_BLOCK;
+            int c = 0;
+            for (; c < nchunks; c++) {
+                const int s = c % P_STAGES;
+                if (!wait_or_abort(empty + s, ((c / P_STAGES) & 1) ^ 1, abort_flag)) break;
+                const int nblk = min(P_CHUNK, nb - c * P_CHUNK);
+                uint8_t* st = stages + s * P_STAGE_BYTES;
+                mbar_expect_tx(full + s, uint32_t(nblk) * (P_A_BLOCK + P_B_BLOCK));
+                bulk_copy(st, wsrc + size_t(c) * P_CHUNK * P_A_BLOCK, uint32_t(nblk) * P_A_BLOCK, full + s);
+                bulk_copy(st + P_CHUNK * P_A_BLOCK, xsrc + size_t(c) * P_CHUNK * P_B_BLOCK,
+                          uint32_t(nblk) * P_B_BLOCK, full + s);
+            }
+            if (*abort_flag) {
+                // Giving up: let the copies already issued land before the CTA's shared memory is released.
+                mbar_wait_bounded(xbar, 0);
+                for (int i = max(0, c - P_STAGES); i < c; i++) mbar_wait_bounded(full + i % P_STAGES, (i / P_STAGES) & 1);
+            }
+        }
+    } else if (warp == 9) {
+        // ---- MMA issuer: one block = one MMA into its own TMEM buffer
+        if (lane == 0) {
+            const uint32_t idesc = umma::idesc_s8(P_ROWS, P_TOK);
+            for (int b = 0; b < nb; b++) {
+                const int c = b / P_CHUNK, k = b % P_CHUNK, s = c % P_STAGES, buf = b % P_TBUF;
+                if (k == 0 && !wait_or_abort(full + s, (c / P_STAGES) & 1, abort_flag)) break;
+                if (!wait_or_abort(tempty + buf, ((b / P_TBUF) & 1) ^ 1, abort_flag)) break;
+                umma::fence_after_sync();
+                const uint32_t sa = smem_addr(stages + s * P_STAGE_BYTES + k * P_A_BLOCK);
+                const uint32_t sb = smem_addr(stages + s * P_STAGE_BYTES + P_CHUNK * P_A_BLOCK + k * P_B_BLOCK);
+                umma::mma_s8(tmem + buf * P_TOK, umma::smem_desc(sa, P_ROWS * 16, 128),
+                             umma::smem_desc(sb, P_TOK * 16, 128), idesc, 0u);
+                umma::commit(tfull + buf);
+                if (k == P_CHUNK - 1 || b == nb - 1) umma::commit(empty + s);
+            }
+            if (*abort_flag) {
+                // Giving up: the MMAs in flight must finish before TMEM is freed.
+                umma::commit(drain);
+                mbar_wait_bounded(drain, 0);
+            }
+        }
+    } else {
+        // ---- epilogue: warp w drains lanes 32*(w%4).. and columns 32*(w/4)..
+        const int quad = warp & 3, half = warp >> 2;
+        const int row = quad * 32 + lane;  // row of the tile = TMEM lane
+        const float* wd = a.wd + (tile_index * P_ROWS + row) * size_t(nb);
+        const float* wc = Q4 ? a.wc + (tile_index * P_ROWS + row) * size_t(nb) : nullptr;
+        float acc[32], off[Q4 ? 32 : 1];
+#pragma unroll
+        for (int j = 0; j < 32; j++) acc[j] = 0.0f;
+        if (Q4) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) off[j] = 0.0f;
+        }
+        bool ok = wait_or_abort(xbar, 0, abort_flag);
+        const float2 magic = make_float2(MAGIC_F, MAGIC_F);
+        for (int b = 0; ok && b < nb; b++) {
+            const int buf = b % P_TBUF;
+            const float wdb = wd[b];
+            const float wcb = Q4 ? wc[b] : 0.0f;
+            if (!wait_or_abort(tfull + buf, (b / P_TBUF) & 1, abort_flag)) {
+                ok = false;
+                break;
+            }
+            umma::fence_after_sync();
+            int v[32];
+            umma::ld_32x32(tmem + (uint32_t(quad * 32) << 16) + buf * P_TOK + half * 32, v);
+            umma::wait_ld();
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty + buf);
+            const float2* xs2 = reinterpret_cast<const float2*>(s_xs + b * P_TOK + half * 32);
+            const float2* su2 = reinterpret_cast<const float2*>(s_xsum + b * P_TOK + half * 32);
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const float2 sum = sub2(make_float2(__int_as_float(v[2 * j] + MAGIC_I),
+                                                    __int_as_float(v[2 * j + 1] + MAGIC_I)), magic);
+                const float2 d = mul2(make_float2(wdb, wdb), xs2[j]);
+                const float2 r = fma2(sum, d, make_float2(acc[2 * j], acc[2 * j + 1]));
+                acc[2 * j] = r.x;
+                acc[2 * j + 1] = r.y;
+                if (Q4) {
+                    const float2 o = fma2(make_float2(wcb, wcb), su2[j], make_float2(off[2 * j], off[2 * j + 1]));
+                    off[2 * j] = o.x;
+                    off[2 * j + 1] = o.y;
+                }
+            }
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                float y = acc[j];
+                if (Q4) y = y + off[j];
+                const int n = half * 32 + j;  // token of the tile
+                if (GATE_UP) {
+                    // Lanes 2i / 2i+1 hold the gate / up row of hidden column 64*rt + i.
+                    const float up = __shfl_xor_sync(0xffffffffu, y, 1);
+                    const int col = rt * 64 + (row >> 1);
+                    if (!(lane & 1) && n < tile_n && col < a.out_cols) {
+                        const float ex = exp_poly(-y);
+                        a.out[size_t(p0 + n) * a.out_cols + col] = __fdiv_rn(y, 1.0f + ex) * up;
+                    }
+                } else {
+                    const int r = rt * P_ROWS + row;
+                    if (n < tile_n && r < a.out_cols) {
+                        size_t p = p0 + n;
+                        if (a.out_rows) p = a.out_rows[p];
+                        a.out[p * a.out_cols + r] = y;
+                    }
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 9) umma::tmem_dealloc(tmem, P_TBUF * P_TOK);
+    if (tid == 0 && s_abort) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
+}
+
+// ---------------------------------------------------------------- tiling kernels
+
+// Weights of one (expert, row tile) into canonical 128 x 32 tiles per block,
+// with their block scales (and 4-bit offsets) as f32 per (row, block). 4-bit
+// values are expanded to int8 (q - 8). One CTA per (expert, row tile).
+template <bool Q4, bool GATE_UP>
+__global__ void tile_prefill_weights_kernel(const uint8_t* __restrict__ wdata, const void* __restrict__ wscales,
+                                            int cols, int rows_per_expert, int row_tiles,
+                                            int8_t* __restrict__ wt, float* __restrict__ wd,
+                                            float* __restrict__ wc) {
+    const int rt = blockIdx.x % row_tiles, e = blockIdx.x / row_tiles;
+    const int nb = cols / QK;
+    const size_t tile_index = size_t(e) * row_tiles + rt;
+    int8_t* dst = wt + tile_index * size_t(nb) * P_A_BLOCK;
+    for (int r = 0; r < P_ROWS; r++) {
+        int row;
+        if (GATE_UP) {
+            const int inter = rows_per_expert / 2, col = rt * 64 + (r >> 1);
+            row = col < inter ? e * rows_per_expert + (r & 1 ? inter : 0) + col : -1;
+        } else {
+            const int rr = rt * P_ROWS + r;
+            row = rr < rows_per_expert ? e * rows_per_expert + rr : -1;
+        }
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const int b = i / QK, k = i % QK;
+            int8_t v = 0;
+            if (row >= 0) {
+                if (!Q4) {
+                    v = int8_t(wdata[size_t(row) * cols + i]);
+                } else {
+                    const uint8_t byte = wdata[(size_t(row) * cols) / 2 + b * 16 + (k & 15)];
+                    v = int8_t(int(k < 16 ? (byte & 0xF) : (byte >> 4)) - 8);
+                }
+            }
+            dst[size_t(b) * P_A_BLOCK + umma::tile_offset(P_ROWS, r, k)] = v;
+        }
+        for (int b = threadIdx.x; b < nb; b += blockDim.x) {
+            float d = 0.0f, c = 0.0f;
+            if (row >= 0) {
+                if (!Q4) {
+                    d = f16_bits_to_f32(reinterpret_cast<const uint16_t*>(wscales)[size_t(row) * nb + b]);
+                } else {
+                    const int words = (nb + SUPER - 1) / SUPER * SUPER_WORDS;
+                    const uint32_t* w = reinterpret_cast<const uint32_t*>(wscales) + size_t(row) * words +
+                                        (b / SUPER) * SUPER_WORDS;
+                    const int j = b % SUPER;
+                    d = f16_bits_to_f32(uint16_t(w[0])) * float((w[1 + j / 4] >> (8 * (j % 4))) & 0xFFu);
+                    c = f16_bits_to_f32(uint16_t(w[0] >> 16)) *
+                        float(int(int8_t(uint8_t(w[3 + j / 4] >> (8 * (j % 4))))));
+                }
+            }
+            wd[(tile_index * P_ROWS + r) * size_t(nb) + b] = d;
+            if (Q4) wc[(tile_index * P_ROWS + r) * size_t(nb) + b] = c;
+        }
+    }
+}
+
+// The token tiles of the experts: expert e with m tokens gets ceil(m / 64) tiles. One CTA.
+__global__ void build_token_tiles_kernel(const uint32_t* __restrict__ counts, const uint32_t* __restrict__ offsets,
+                                         int experts, int* __restrict__ tile_expert,
+                                         uint32_t* __restrict__ tile_p0, int* __restrict__ tile_n,
+                                         int* __restrict__ tile_count) {
+    __shared__ int s_base[MAX_EXPERTS + 1];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; e++) {
+            s_base[e] = run;
+            run += (int(counts[e]) + P_TOK - 1) / P_TOK;
+        }
+        s_base[experts] = run;
+        *tile_count = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const int m = int(counts[e]);
+        for (int i = 0; i * P_TOK < m; i++) {
+            const int tt = s_base[e] + i;
+            tile_expert[tt] = e;
+            tile_p0[tt] = offsets[e] + i * P_TOK;
+            tile_n[tt] = min(P_TOK, m - i * P_TOK);
+        }
+    }
+}
+
+// Activations into canonical 64 x 32 tiles per (token tile, block), scales (and
+// block sums) transposed to [block][token]. Source rows are already 8-bit
+// (xq/xs/xsum through row_of_slot) or f32 rows to quantize here (xf), as
+// quantize_q8 does (src/kernels.rs:84-98). A thread per (token, block).
+template <bool Q4>
+__global__ void tile_activations_kernel(const int8_t* __restrict__ xq, const float* __restrict__ xs,
+                                        const float* __restrict__ xsum, const float* __restrict__ xf,
+                                        const uint32_t* __restrict__ row_of_slot, int cols, int nbp,
+                                        const uint32_t* __restrict__ tile_p0, const int* __restrict__ tile_n,
+                                        const int* __restrict__ tile_count, int8_t* __restrict__ xt,
+                                        float* __restrict__ xst, float* __restrict__ xsumt) {
+    const int nb = cols / QK;
+    const int tt = blockIdx.x;
+    if (tt >= *tile_count) return;
+    const int n_valid = tile_n[tt];
+    const uint32_t p0 = tile_p0[tt];
+    for (int task = threadIdx.x; task < P_TOK * nb; task += blockDim.x) {
+        const int n = task % P_TOK, b = task / P_TOK;
+        uint32_t q[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        float d = 0.0f, su = 0.0f;
+        if (n < n_valid) {
+            const size_t p = p0 + n;
+            const size_t row = row_of_slot ? row_of_slot[p] : p;
+            if (xf) {
+                const float4* src = reinterpret_cast<const float4*>(xf + row * cols + b * QK);
+                float4 v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = src[i];
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; i++)
+                    amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
+                                 fabsf(v[i].w));
+                d = __fdiv_rn(amax, 127.0f);
+                const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                auto q8 = [&](float x) {
+                    const float rr = roundf(x * id);
+                    return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                };
+                int qsum = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+                    qsum += q0 + q1 + q2 + q3;
+                    q[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) | (uint32_t(q2 & 0xFF) << 16) |
+                           (uint32_t(q3 & 0xFF) << 24);
+                }
+                su = d * float(qsum);
+            } else {
+                const uint4* src = reinterpret_cast<const uint4*>(xq + row * cols + b * QK);
+                const uint4 lo = src[0], hi = src[1];
+                q[0] = lo.x, q[1] = lo.y, q[2] = lo.z, q[3] = lo.w;
+                q[4] = hi.x, q[5] = hi.y, q[6] = hi.z, q[7] = hi.w;
+                d = xs[row * nbp + b];
+                if (Q4) su = xsum[row * nbp + b];
+            }
+        }
+        // Bytes 0-15 and 16-31 of the token's block are the two K halves of its core-matrix row.
+        int8_t* dst = xt + (size_t(tt) * nb + b) * P_B_BLOCK;
+        *reinterpret_cast<uint4*>(dst + umma::tile_offset(P_TOK, n, 0)) = make_uint4(q[0], q[1], q[2], q[3]);
+        *reinterpret_cast<uint4*>(dst + umma::tile_offset(P_TOK, n, 16)) = make_uint4(q[4], q[5], q[6], q[7]);
+        xst[(size_t(tt) * nb + b) * P_TOK + n] = d;
+        if (Q4) xsumt[(size_t(tt) * nb + b) * P_TOK + n] = su;
+    }
+}
+
+size_t prefill_smem(int nb, bool q4) {
+    return size_t(P_STAGES) * P_STAGE_BYTES + size_t(nb) * P_TOK * 4 * (q4 ? 2 : 1) +
+           (2 * P_STAGES + 2 * P_TBUF + 2) * 8 + 64;
+}
+
+}  // namespace
+
+void init_kernels_prefill() {
+    const int lim = P_SMEM_LIMIT;  // the kernel also has a few static words
+    cudaFuncSetAttribute(expert_prefill_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_prefill_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_prefill_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(expert_prefill_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+}
+
+int prefill_row_tiles(const MoeDims& d, bool gate_up) {
+    return gate_up ? (d.inter + 63) / 64 : (d.hidden + P_ROWS - 1) / P_ROWS;
+}
+
+bool prefill_fits(const MoeDims& d) {
+    return prefill_smem(d.hidden / QK, true) <= size_t(P_SMEM_LIMIT) && prefill_smem(d.inter / QK, true) <= size_t(P_SMEM_LIMIT);
+}
+
+size_t prefill_weight_bytes(const MoeDims& d, bool gate_up) {
+    const int cols = gate_up ? d.hidden : d.inter;
+    return size_t(d.experts) * prefill_row_tiles(d, gate_up) * (cols / QK) * P_A_BLOCK;
+}
+
+size_t prefill_scale_elems(const MoeDims& d, bool gate_up) {
+    const int cols = gate_up ? d.hidden : d.inter;
+    return size_t(d.experts) * prefill_row_tiles(d, gate_up) * P_ROWS * (cols / QK);
+}
+
+int prefill_max_token_tiles(int slots, int experts) { return (slots + P_TOK - 1) / P_TOK + experts; }
+
+void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, int8_t* wt, float* wd, float* wc,
+                          cudaStream_t stream) {
+    const int cols = gate_up ? d.hidden : d.inter;
+    const int rpe = gate_up ? 2 * d.inter : d.hidden;
+    const int rts = prefill_row_tiles(d, gate_up);
+    const unsigned grid = unsigned(d.experts * rts);
+    const uint8_t* data = static_cast<const uint8_t*>(m.data);
+    if (m.kind == 1) {
+        if (gate_up) tile_prefill_weights_kernel<false, true><<<grid, 256, 0, stream>>>(data, m.scales, cols, rpe, rts, wt, wd, wc);
+        else tile_prefill_weights_kernel<false, false><<<grid, 256, 0, stream>>>(data, m.scales, cols, rpe, rts, wt, wd, wc);
+    } else {
+        if (gate_up) tile_prefill_weights_kernel<true, true><<<grid, 256, 0, stream>>>(data, m.scales, cols, rpe, rts, wt, wd, wc);
+        else tile_prefill_weights_kernel<true, false><<<grid, 256, 0, stream>>>(data, m.scales, cols, rpe, rts, wt, wd, wc);
+    }
+}
+
+// One of the two grouped products on the tensor cores. `src` describes where the
+// activations come from: 8-bit rows through row_of_slot (gate_up), or f32 rows
+// in slot order to quantize (down).
+int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights& w, const PrefillScratch& s,
+                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream) {
+    const int cols = gate_up ? d.hidden : d.inter;
+    const int nb = cols / QK, nbp = (nb + 7) / 8 * 8;
+    const int max_tiles = prefill_max_token_tiles(slots, d.experts);
+    int launched = 0;
+    if (gate_up) {
+        build_token_tiles_kernel<<<1, 256, 0, stream>>>(ws.counts, ws.offsets, d.experts, s.tile_expert, s.tile_p0,
+                                                        s.tile_n, s.tile_count);
+        launched++;
+    }
+    if (q4)
+        tile_activations_kernel<true><<<max_tiles, 256, 0, stream>>>(
+            gate_up ? ws.xq : nullptr, gate_up ? ws.xs : nullptr, gate_up ? ws.xsum : nullptr,
+            gate_up ? nullptr : ws.hidden_f, gate_up ? ws.slot_token : nullptr, cols, nbp, s.tile_p0, s.tile_n,
+            s.tile_count, s.xt, s.xst, s.xsumt);
+    else
+        tile_activations_kernel<false><<<max_tiles, 256, 0, stream>>>(
+            gate_up ? ws.xq : nullptr, gate_up ? ws.xs : nullptr, nullptr, gate_up ? nullptr : ws.hidden_f,
+            gate_up ? ws.slot_token : nullptr, cols, nbp, s.tile_p0, s.tile_n, s.tile_count, s.xt, s.xst, s.xsumt);
+    launched++;
+    PrefillArgs a{};
+    a.wt = gate_up ? w.gu_t : w.dn_t;
+    a.wd = gate_up ? w.gu_d : w.dn_d;
+    a.wc = gate_up ? w.gu_c : w.dn_c;
+    a.xt = s.xt;
+    a.xst = s.xst;
+    a.xsumt = s.xsumt;
+    a.tile_expert = s.tile_expert;
+    a.tile_p0 = s.tile_p0;
+    a.tile_n = s.tile_n;
+    a.tile_count = s.tile_count;
+    a.nb = nb;
+    a.row_tiles = prefill_row_tiles(d, gate_up);
+    a.rows_per_expert = gate_up ? 2 * d.inter : d.hidden;
+    a.out_cols = gate_up ? d.inter : d.hidden;
+    a.out = out;
+    a.out_rows = out_rows;
+    a.status = ws.status;
+    const dim3 grid(a.row_tiles, max_tiles);
+    const size_t smem = prefill_smem(nb, q4);
+    if (q4) {
+        if (gate_up) expert_prefill_kernel<true, true><<<grid, P_THREADS, smem, stream>>>(a);
+        else expert_prefill_kernel<true, false><<<grid, P_THREADS, smem, stream>>>(a);
+    } else {
+        if (gate_up) expert_prefill_kernel<false, true><<<grid, P_THREADS, smem, stream>>>(a);
+        else expert_prefill_kernel<false, false><<<grid, P_THREADS, smem, stream>>>(a);
+    }
+    return launched + 1;
+}
+
+}  // namespace tc

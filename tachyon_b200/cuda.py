@@ -28,6 +28,7 @@ SYMBOLS = {
     "tc_sync": (_i, [_vp]),
     "tc_stream": (_vp, [_vp]),
     "tc_set_arithmetic": (_i, [_vp, _i]),
+    "tc_set_prefill_threshold": (_i, [_vp, _i]),
     "tc_malloc": (_vp, [_vp, _sz]),
     "tc_free": (None, [_vp, _vp]),
     "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
@@ -141,6 +142,11 @@ class Context:
     def set_arithmetic(self, mode: int):
         """ARITH_FAST (default) or ARITH_CPU_LANES (bit-identical to the CPU path)."""
         self._check(self.lib.tc_set_arithmetic(self.handle, mode), "tc_set_arithmetic")
+
+    def set_prefill_threshold(self, avg_tokens_per_expert: int):
+        """Average tokens per expert from which the tcgen05 kernels take over (default 32; 0 = always)."""
+        self._check(self.lib.tc_set_prefill_threshold(self.handle, avg_tokens_per_expert),
+                    "tc_set_prefill_threshold")
 
     def sync(self):
         self._check(self.lib.tc_sync(self.handle), "tc_sync")
