@@ -15,10 +15,10 @@
 // Work decomposition: a CTA computes one output tile: 128 weight rows (for
 // gate_up: 64 gate rows interleaved with the 64 matching up rows, so SwiGLU
 // pairs sit in adjacent lanes) x 64 tokens of one expert, over all of K.
-// Roles: warp 8 streams operand chunks (8 blocks: 32 KB of weights + 16 KB of
-// activations) through a 3-stage ring; one thread of warp 9 issues the MMAs
-// into a ring of 8 TMEM buffers (64 columns each); warps 0-7 drain the buffers
-// (each TMEM lane quadrant is served by two warps, 32 columns each) and keep
+// Roles: warp 16 streams operand chunks (8 blocks: 32 KB of weights + 16 KB of
+// activations) through a 3-stage ring; one thread each of warps 17-20 issues the MMAs
+// into a ring of 8 TMEM buffers (64 columns each); warps 0-15 drain the buffers
+// (each TMEM lane quadrant is served by four warps, 16 columns each) and keep
 // the float chains in registers. Every wait is bounded and watches a CTA-wide
 // abort flag; TMEM is freed on every path.
 #include "experts_common.cuh"
@@ -36,13 +36,16 @@ constexpr int P_TBUF = 8;             // TMEM buffers of P_TOK columns
 constexpr int P_A_BLOCK = P_ROWS * 32;  // bytes of one block of weights
 constexpr int P_B_BLOCK = P_TOK * 32;
 constexpr int P_STAGE_BYTES = P_CHUNK * (P_A_BLOCK + P_B_BLOCK);
-constexpr int P_THREADS = 320;        // 8 epilogue warps + producer + MMA
+constexpr int P_EW = 16;               // epilogue warps: 4 TMEM lane quadrants x 4 column slices
+constexpr int P_COLS = P_TOK * 4 / P_EW;  // columns (tokens) per epilogue warp
+constexpr int P_MW = 4;                // MMA-issuing warps: block b belongs to warp b % P_MW
+constexpr int P_THREADS = (P_EW + 1 + P_MW) * 32;  // + producer + MMA issuers
 constexpr uint32_t P_SPIN = 1u << 16;
 constexpr int P_SMEM_LIMIT = 226 * 1024;
 
 struct PrefillArgs {
     const int8_t* wt;        // weight tiles [expert][row tile][block][128 x 32 canonical]
-    const float* wd;         // weight block scales [expert][row tile][128][nb]
+    const float* wd;         // weight block scales [expert][row tile][nb][128]
     const float* wc;         // 4-bit block offsets, same shape (null for 8-bit)
     const int8_t* xt;        // activation tiles [token tile][block][64 x 32 canonical]
     const float* xst;        // activation scales [token tile][nb][64]
@@ -58,7 +61,20 @@ struct PrefillArgs {
 };
 
 // Bounded wait that also gives up when another warp of the CTA has.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test(bar, parity)) return true;  // the common case in steady state: no suspension machinery
     for (uint32_t i = 0; i < P_SPIN; i++) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
@@ -71,24 +87,41 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
+#ifdef TC_TIMELINE
+// Diagnostic build only: cycle stamps of the first 148 CTAs, per role.
+__device__ long long g_ptl[148][10][40];
+#define PTL(role, k)                                                                          \
+    do {                                                                                      \
+        const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                 \
+        if (GATE_UP && cta_ < 148 && (k) < 40) g_ptl[cta_][role][k] = clock64();              \
+    } while (0)
+#else
+#define PTL(role, k) \
+    do {             \
+    } while (0)
+#endif
+
 template <bool Q4, bool GATE_UP>
 __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const PrefillArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stages = smem;                                                  // P_STAGES x P_STAGE_BYTES
     float* s_xs = reinterpret_cast<float*>(smem + P_STAGES * P_STAGE_BYTES);  // [nb][64]
     float* s_xsum = s_xs + a.nb * P_TOK;                                     // [nb][64] (4-bit)
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_xsum + (Q4 ? a.nb * P_TOK : 0));
+    float* s_wd = s_xsum + (Q4 ? a.nb * P_TOK : 0);                          // [nb][128]
+    float* s_wc = s_wd + a.nb * P_ROWS;                                      // [nb][128] (4-bit)
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_wc + (Q4 ? a.nb * P_ROWS : 0));
     uint64_t* full = bars;                    // [P_STAGES] operands landed
     uint64_t* empty = bars + P_STAGES;        // [P_STAGES] MMAs that read the stage are done
     uint64_t* tfull = bars + 2 * P_STAGES;    // [P_TBUF] a block's integer tile is in TMEM
-    uint64_t* tempty = tfull + P_TBUF;        // [P_TBUF] drained by all 8 epilogue warps
+    uint64_t* tempty = tfull + P_TBUF;        // [P_TBUF] drained by all epilogue warps
     uint64_t* xbar = tempty + P_TBUF;         // activation scales landed
-    uint64_t* drain = xbar + 1;               // abort path only: the MMAs issued so far are done
+    uint64_t* drain = xbar + 1;               // [P_MW] abort path only: an issuer's MMAs so far are done
     __shared__ uint32_t s_tmem;
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tt = blockIdx.y, rt = blockIdx.x;
+    if (tid == 0) PTL(3, 0);
     if (tt >= *a.tile_count) return;  // uniform: the whole CTA leaves before touching TMEM
     const int e = a.tile_expert[tt];
     const int tile_n = a.tile_n[tt];
@@ -99,20 +132,20 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
     if (tid == 0) {
         for (int s = 0; s < P_STAGES; s++) {
             mbar_init(full + s, 1);
-            mbar_init(empty + s, 1);
+            mbar_init(empty + s, P_MW);
         }
         for (int b = 0; b < P_TBUF; b++) {
             mbar_init(tfull + b, 1);
-            mbar_init(tempty + b, 8);
+            mbar_init(tempty + b, P_EW);
         }
         mbar_init(xbar, 1);
-        mbar_init(drain, 1);
+        for (int i = 0; i < P_MW; i++) mbar_init(drain + i, 1);
         s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    if (warp == 9) {
+    if (warp == P_EW + 1) {
         umma::tmem_alloc(&s_tmem, P_TBUF * P_TOK);
         umma::tmem_relinquish();
     }
@@ -120,16 +153,22 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = s_tmem;
+    if (tid == 0) PTL(3, 1);
     volatile int* abort_flag = &s_abort;
 
     const size_t tile_index = size_t(e) * a.row_tiles + rt;
-    if (warp == 8) {
+    if (warp == P_EW) {
         // ---- producer: activation scales once, then the operand chunks
         if (lane == 0) {
             const uint32_t xs_bytes = uint32_t(nb) * P_TOK * 4;
-            mbar_expect_tx(xbar, Q4 ? 2 * xs_bytes : xs_bytes);
+            const uint32_t ws_bytes = uint32_t(nb) * P_ROWS * 4;
+            mbar_expect_tx(xbar, (Q4 ? 2 : 1) * (xs_bytes + ws_bytes));
             bulk_copy(s_xs, a.xst + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
-            if (Q4) bulk_copy(s_xsum, a.xsumt + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+            bulk_copy(s_wd, a.wd + tile_index * nb * P_ROWS, ws_bytes, xbar);
+            if (Q4) {
+                bulk_copy(s_xsum, a.xsumt + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+                bulk_copy(s_wc, a.wc + tile_index * nb * P_ROWS, ws_bytes, xbar);
+            }
             const int8_t* wsrc = a.wt + tile_index * size_t(nb) * P_A_BLOCK;
             const int8_t* xsrc = a.xt + size_t(tt) * nb * P_B_BLOCK;
             int c = 0;
@@ -138,6 +177,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                 if (!wait_or_abort(empty + s, ((c / P_STAGES) & 1) ^ 1, abort_flag)) break;
                 const int nblk = min(P_CHUNK, nb - c * P_CHUNK);
                 uint8_t* st = stages + s * P_STAGE_BYTES;
+                PTL(0, c);
                 mbar_expect_tx(full + s, uint32_t(nblk) * (P_A_BLOCK + P_B_BLOCK));
                 bulk_copy(st, wsrc + size_t(c) * P_CHUNK * P_A_BLOCK, uint32_t(nblk) * P_A_BLOCK, full + s);
                 bulk_copy(st + P_CHUNK * P_A_BLOCK, xsrc + size_t(c) * P_CHUNK * P_B_BLOCK,
@@ -149,92 +189,150 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                 for (int i = max(0, c - P_STAGES); i < c; i++) mbar_wait_bounded(full + i % P_STAGES, (i / P_STAGES) & 1);
             }
         }
-    } else if (warp == 9) {
-        // ---- MMA issuer: one block = one MMA into its own TMEM buffer
+    } else if (warp > P_EW) {
+        // ---- MMA issuers: one block = one MMA into its own TMEM buffer. A single thread
+        // spends several hundred cycles per block on its waits, fence and commit, far more
+        // than the MMA takes, so P_MW threads (one per warp) take the blocks in turn; the
+        // blocks are independent (different TMEM buffers), so no order among them is needed.
         if (lane == 0) {
             const uint32_t idesc = umma::idesc_s8(P_ROWS, P_TOK);
-            for (int b = 0; b < nb; b++) {
+            const int mw = warp - P_EW - 1;
+            for (int b = mw; b < nb; b += P_MW) {
                 const int c = b / P_CHUNK, k = b % P_CHUNK, s = c % P_STAGES, buf = b % P_TBUF;
-                if (k == 0 && !wait_or_abort(full + s, (c / P_STAGES) & 1, abort_flag)) break;
+                if (k < P_MW && !wait_or_abort(full + s, (c / P_STAGES) & 1, abort_flag)) break;
                 if (!wait_or_abort(tempty + buf, ((b / P_TBUF) & 1) ^ 1, abort_flag)) break;
                 umma::fence_after_sync();
+                PTL(1, b);
                 const uint32_t sa = smem_addr(stages + s * P_STAGE_BYTES + k * P_A_BLOCK);
                 const uint32_t sb = smem_addr(stages + s * P_STAGE_BYTES + P_CHUNK * P_A_BLOCK + k * P_B_BLOCK);
                 umma::mma_s8(tmem + buf * P_TOK, umma::smem_desc(sa, P_ROWS * 16, 128),
                              umma::smem_desc(sb, P_TOK * 16, 128), idesc, 0u);
+                PTL(4, b);
                 umma::commit(tfull + buf);
-                if (k == P_CHUNK - 1 || b == nb - 1) umma::commit(empty + s);
+                PTL(5, b);
+                // This thread's last block of the chunk. (A ragged last chunk may leave
+                // `empty` short of arrivals: nothing waits for it.)
+                if (k + P_MW >= P_CHUNK || b + P_MW >= nb) umma::commit(empty + s);
             }
             if (*abort_flag) {
                 // Giving up: the MMAs in flight must finish before TMEM is freed.
-                umma::commit(drain);
-                mbar_wait_bounded(drain, 0);
+                umma::commit(drain + mw);
+                mbar_wait_bounded(drain + mw, 0);
             }
         }
     } else {
-        // ---- epilogue: warp w drains lanes 32*(w%4).. and columns 32*(w/4)..
-        const int quad = warp & 3, half = warp >> 2;
+        // ---- epilogue: warp w drains lanes 32*(w%4).. and columns P_COLS*(w/4)..
+        const int quad = warp & 3, slice = warp >> 2;
         const int row = quad * 32 + lane;  // row of the tile = TMEM lane
-        const float* wd = a.wd + (tile_index * P_ROWS + row) * size_t(nb);
-        const float* wc = Q4 ? a.wc + (tile_index * P_ROWS + row) * size_t(nb) : nullptr;
-        float acc[32], off[Q4 ? 32 : 1];
+        float acc[P_COLS], off[Q4 ? P_COLS : 1];
 #pragma unroll
-        for (int j = 0; j < 32; j++) acc[j] = 0.0f;
+        for (int j = 0; j < P_COLS; j++) acc[j] = 0.0f;
         if (Q4) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) off[j] = 0.0f;
+            for (int j = 0; j < P_COLS; j++) off[j] = 0.0f;
         }
         bool ok = wait_or_abort(xbar, 0, abort_flag);
-        const float2 magic = make_float2(MAGIC_F, MAGIC_F);
-        for (int b = 0; ok && b < nb; b++) {
-            const int buf = b % P_TBUF;
-            const float wdb = wd[b];
-            const float wcb = Q4 ? wc[b] : 0.0f;
-            if (!wait_or_abort(tfull + buf, (b / P_TBUF) & 1, abort_flag)) {
+        const uint32_t tbase = tmem + (uint32_t(quad * 32) << 16) + slice * P_COLS;
+        // One block's float work on the integer tile in v.
+        auto consume = [&](int b, const int (&v)[P_COLS]) {
+            const float wdb = s_wd[b * P_ROWS + row];
+            const float wcb = Q4 ? s_wc[b * P_ROWS + row] : 0.0f;
+            const float4* xs4 = reinterpret_cast<const float4*>(s_xs + b * P_TOK + slice * P_COLS);
+            const float4* su4 = reinterpret_cast<const float4*>(s_xsum + b * P_TOK + slice * P_COLS);
+#pragma unroll
+            for (int j = 0; j < P_COLS / 4; j++) {
+                const float4 x = xs4[j];
+                const float2 xlo = make_float2(x.x, x.y), xhi = make_float2(x.z, x.w);
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int i = 4 * j + 2 * h;
+                    // The conversion unit works beside the FP32 pipe, which the two packed
+                    // operations below keep busy; the add-a-magic-number conversion used
+                    // where issue slots are short would add a third FP32 operation here.
+                    const float2 sum = make_float2(__int2float_rn(v[i]), __int2float_rn(v[i + 1]));
+                    const float2 d = mul2(make_float2(wdb, wdb), h ? xhi : xlo);
+                    const float2 r = fma2(sum, d, make_float2(acc[i], acc[i + 1]));
+                    acc[i] = r.x;
+                    acc[i + 1] = r.y;
+                }
+                if (Q4) {
+                    const float4 u = su4[j];
+                    const float2 o0 = fma2(make_float2(wcb, wcb), make_float2(u.x, u.y),
+                                           make_float2(off[4 * j], off[4 * j + 1]));
+                    const float2 o1 = fma2(make_float2(wcb, wcb), make_float2(u.z, u.w),
+                                           make_float2(off[4 * j + 2], off[4 * j + 3]));
+                    off[4 * j] = o0.x, off[4 * j + 1] = o0.y, off[4 * j + 2] = o1.x, off[4 * j + 3] = o1.y;
+                }
+            }
+        };
+        // Block b's tile is read from TMEM while block b-1's float work runs: the load is
+        // asynchronous until wait_ld, and the two register tiles alternate.
+        auto fetch = [&](int b, int (&v)[P_COLS]) -> bool {
+            if (!wait_or_abort(tfull + b % P_TBUF, (b / P_TBUF) & 1, abort_flag)) return false;
+            if (tid == 0) PTL(9, b);
+            umma::fence_after_sync();
+            if (tid == 0) PTL(0, 8 + b);
+            umma::ld_32x16(tbase + (b % P_TBUF) * P_TOK, v);
+            return true;
+        };
+        auto release = [&](int b) {  // after wait_ld: the buffer may be overwritten
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty + b % P_TBUF);
+        };
+        int va[P_COLS], vb[P_COLS];
+        if (ok) ok = fetch(0, va);
+        for (int b = 0; ok && b < nb; b += 2) {
+            umma::wait_ld(va);
+            if (tid == 0) PTL(2, b);
+            release(b);
+            if (tid == 0) PTL(6, b);
+            if (b + 1 < nb && !fetch(b + 1, vb)) {
                 ok = false;
                 break;
             }
-            umma::fence_after_sync();
-            int v[32];
-            umma::ld_32x32(tmem + (uint32_t(quad * 32) << 16) + buf * P_TOK + half * 32, v);
-            umma::wait_ld();
-            umma::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty + buf);
-            const float2* xs2 = reinterpret_cast<const float2*>(s_xs + b * P_TOK + half * 32);
-            const float2* su2 = reinterpret_cast<const float2*>(s_xsum + b * P_TOK + half * 32);
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const float2 sum = sub2(make_float2(__int_as_float(v[2 * j] + MAGIC_I),
-                                                    __int_as_float(v[2 * j + 1] + MAGIC_I)), magic);
-                const float2 d = mul2(make_float2(wdb, wdb), xs2[j]);
-                const float2 r = fma2(sum, d, make_float2(acc[2 * j], acc[2 * j + 1]));
-                acc[2 * j] = r.x;
-                acc[2 * j + 1] = r.y;
-                if (Q4) {
-                    const float2 o = fma2(make_float2(wcb, wcb), su2[j], make_float2(off[2 * j], off[2 * j + 1]));
-                    off[2 * j] = o.x;
-                    off[2 * j + 1] = o.y;
+            if (tid == 0) PTL(7, b);
+            consume(b, va);
+            if (tid == 0) PTL(8, b);
+            if (b + 1 < nb) {
+                umma::wait_ld(vb);
+                if (tid == 0) PTL(2, b + 1);
+                release(b + 1);
+                if (b + 2 < nb && !fetch(b + 2, va)) {
+                    ok = false;
+                    break;
                 }
+                consume(b + 1, vb);
             }
         }
+        if (tid == 0) PTL(3, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
+            if (GATE_UP) {
+                // Lanes 2i / 2i+1 hold the gate / up row of hidden column 64*rt + i. The pair
+                // trades halves so that each lane finishes one token of every two: the even
+                // lane token j (its gate, the partner's up), the odd lane token j+1.
+                const bool odd = lane & 1;
+                const int col = rt * 64 + (row >> 1);
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-                float y = acc[j];
-                if (Q4) y = y + off[j];
-                const int n = half * 32 + j;  // token of the tile
-                if (GATE_UP) {
-                    // Lanes 2i / 2i+1 hold the gate / up row of hidden column 64*rt + i.
-                    const float up = __shfl_xor_sync(0xffffffffu, y, 1);
-                    const int col = rt * 64 + (row >> 1);
-                    if (!(lane & 1) && n < tile_n && col < a.out_cols) {
-                        const float ex = exp_poly(-y);
-                        a.out[size_t(p0 + n) * a.out_cols + col] = __fdiv_rn(y, 1.0f + ex) * up;
+                for (int j = 0; j < P_COLS; j += 2) {
+                    float y0 = acc[j], y1 = acc[j + 1];
+                    if (Q4) y0 = y0 + off[j], y1 = y1 + off[j + 1];
+                    const float got = __shfl_xor_sync(0xffffffffu, odd ? y0 : y1, 1);
+                    const float g = odd ? got : y0, up = odd ? y1 : got;
+                    const int n = slice * P_COLS + j + (odd ? 1 : 0);  // token of the tile
+                    if (n < tile_n && col < a.out_cols) {
+                        const float ex = exp_poly(-g);
+                        a.out[size_t(p0 + n) * a.out_cols + col] = __fdiv_rn(g, 1.0f + ex) * up;
                     }
-                } else {
-                    const int r = rt * P_ROWS + row;
+                }
+            } else {
+                const int r = rt * P_ROWS + row;
+#pragma unroll
+                for (int j = 0; j < P_COLS; j++) {
+                    float y = acc[j];
+                    if (Q4) y = y + off[j];
+                    const int n = slice * P_COLS + j;
                     if (n < tile_n && r < a.out_cols) {
                         size_t p = p0 + n;
                         if (a.out_rows) p = a.out_rows[p];
@@ -244,16 +342,18 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
             }
         }
     }
+    if (tid == 0) PTL(3, 3);
     umma::fence_before_sync();
     __syncthreads();
-    if (warp == 9) umma::tmem_dealloc(tmem, P_TBUF * P_TOK);
+    if (tid == 0) PTL(3, 4);
+    if (warp == P_EW + 1) umma::tmem_dealloc(tmem, P_TBUF * P_TOK);
     if (tid == 0 && s_abort) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
 }
 
 // ---------------------------------------------------------------- tiling kernels
 
 // Weights of one (expert, row tile) into canonical 128 x 32 tiles per block,
-// with their block scales (and 4-bit offsets) as f32 per (row, block). 4-bit
+// with their block scales (and 4-bit offsets) as f32 per (block, row). 4-bit
 // values are expanded to int8 (q - 8). One CTA per (expert, row tile).
 template <bool Q4, bool GATE_UP>
 __global__ void tile_prefill_weights_kernel(const uint8_t* __restrict__ wdata, const void* __restrict__ wscales,
@@ -301,8 +401,8 @@ __global__ void tile_prefill_weights_kernel(const uint8_t* __restrict__ wdata, c
                         float(int(int8_t(uint8_t(w[3 + j / 4] >> (8 * (j % 4))))));
                 }
             }
-            wd[(tile_index * P_ROWS + r) * size_t(nb) + b] = d;
-            if (Q4) wc[(tile_index * P_ROWS + r) * size_t(nb) + b] = c;
+            wd[(tile_index * nb + b) * P_ROWS + r] = d;
+            if (Q4) wc[(tile_index * nb + b) * P_ROWS + r] = c;
         }
     }
 }
@@ -401,8 +501,8 @@ __global__ void tile_activations_kernel(const int8_t* __restrict__ xq, const flo
 }
 
 size_t prefill_smem(int nb, bool q4) {
-    return size_t(P_STAGES) * P_STAGE_BYTES + size_t(nb) * P_TOK * 4 * (q4 ? 2 : 1) +
-           (2 * P_STAGES + 2 * P_TBUF + 2) * 8 + 64;
+    return size_t(P_STAGES) * P_STAGE_BYTES + size_t(nb) * (P_TOK + P_ROWS) * 4 * (q4 ? 2 : 1) +
+           (2 * P_STAGES + 2 * P_TBUF + 1 + P_MW) * 8 + 64;
 }
 
 }  // namespace
@@ -506,3 +606,9 @@ int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights
 }
 
 }  // namespace tc
+
+#ifdef TC_TIMELINE
+extern "C" int tc_debug_prefill_timeline(long long* out) {
+    return int(cudaMemcpyFromSymbol(out, tc::g_ptl, sizeof(tc::g_ptl)));
+}
+#endif

@@ -82,6 +82,28 @@ __device__ __forceinline__ void ld_32x32(uint32_t taddr, int (&v)[32]) {
         : "memory");
 }
 
+// The same for 16 columns.
+__device__ __forceinline__ void ld_32x16(uint32_t taddr, int (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Waits for this thread's TMEM loads. The values pass through the statement so
+// that no use of them can be scheduled above the wait.
+__device__ __forceinline__ void wait_ld(int (&v)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                   "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]),
+                   "+r"(v[15])
+                 :
+                 : "memory");
+}
+
 // Byte offset of (row, kbyte) inside a tile of `rows` rows x 32 K-bytes.
 __host__ __device__ constexpr uint32_t tile_offset(uint32_t rows, uint32_t row, uint32_t kbyte) {
     return (kbyte / 16) * (rows / 8) * 128 + (row / 8) * 128 + (row % 8) * 16 + kbyte % 16;
