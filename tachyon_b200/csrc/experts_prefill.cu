@@ -17,7 +17,8 @@
 // pairs sit in adjacent lanes) x 64 tokens of one expert, over all of K.
 // Roles: warp 16 streams operand chunks (8 blocks: 32 KB of weights + 16 KB of
 // activations) through a 3-stage ring; one thread each of warps 17-20 issues the MMAs
-// into a ring of 8 TMEM buffers (64 columns each); warps 0-15 drain the buffers
+// into a ring of 8 TMEM buffers (64 columns each, handed over four at a time);
+// warps 0-15 drain the buffers
 // (each TMEM lane quadrant is served by four warps, 16 columns each) and keep
 // the float chains in registers. Every wait is bounded and watches a CTA-wide
 // abort flag; TMEM is freed on every path.
@@ -33,6 +34,9 @@ constexpr int P_TOK = 64;             // MMA N
 constexpr int P_CHUNK = 8;            // blocks per smem stage
 constexpr int P_STAGES = 3;
 constexpr int P_TBUF = 8;             // TMEM buffers of P_TOK columns
+constexpr int P_GROUP = 4;            // buffers per barrier: the ring is handed over in halves
+constexpr int P_NGRP = P_TBUF / P_GROUP;
+static_assert(P_GROUP == 4 && P_CHUNK % P_GROUP == 0, "block b of a group belongs to issuer b % P_MW");
 constexpr int P_A_BLOCK = P_ROWS * 32;  // bytes of one block of weights
 constexpr int P_B_BLOCK = P_TOK * 32;
 constexpr int P_STAGE_BYTES = P_CHUNK * (P_A_BLOCK + P_B_BLOCK);
@@ -134,9 +138,9 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
             mbar_init(full + s, 1);
             mbar_init(empty + s, P_MW);
         }
-        for (int b = 0; b < P_TBUF; b++) {
-            mbar_init(tfull + b, 1);
-            mbar_init(tempty + b, P_EW);
+        for (int g = 0; g < P_NGRP; g++) {
+            mbar_init(tfull + g, P_MW);
+            mbar_init(tempty + g, P_EW);
         }
         mbar_init(xbar, 1);
         for (int i = 0; i < P_MW; i++) mbar_init(drain + i, 1);
@@ -197,10 +201,18 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
         if (lane == 0) {
             const uint32_t idesc = umma::idesc_s8(P_ROWS, P_TOK);
             const int mw = warp - P_EW - 1;
-            for (int b = mw; b < nb; b += P_MW) {
+            const int ngroups = (nb + P_GROUP - 1) / P_GROUP;
+            for (int g = 0; g < ngroups; g++) {
+                // Block mw of every group of P_GROUP (= P_MW) blocks; the group's TMEM half is
+                // free once the epilogue warps have read group g - P_NGRP out of it.
+                const int b = g * P_GROUP + mw, gi = g % P_NGRP;
+                if (!wait_or_abort(tempty + gi, ((g / P_NGRP) & 1) ^ 1, abort_flag)) break;
+                if (b >= nb) {  // ragged last group: keep the arrival count whole
+                    mbar_arrive(tfull + gi);
+                    continue;
+                }
                 const int c = b / P_CHUNK, k = b % P_CHUNK, s = c % P_STAGES, buf = b % P_TBUF;
                 if (k < P_MW && !wait_or_abort(full + s, (c / P_STAGES) & 1, abort_flag)) break;
-                if (!wait_or_abort(tempty + buf, ((b / P_TBUF) & 1) ^ 1, abort_flag)) break;
                 umma::fence_after_sync();
                 PTL(1, b);
                 const uint32_t sa = smem_addr(stages + s * P_STAGE_BYTES + k * P_A_BLOCK);
@@ -208,7 +220,7 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                 umma::mma_s8(tmem + buf * P_TOK, umma::smem_desc(sa, P_ROWS * 16, 128),
                              umma::smem_desc(sb, P_TOK * 16, 128), idesc, 0u);
                 PTL(4, b);
-                umma::commit(tfull + buf);
+                umma::commit(tfull + gi);
                 PTL(5, b);
                 // This thread's last block of the chunk. (A ragged last chunk may leave
                 // `empty` short of arrivals: nothing waits for it.)
@@ -268,17 +280,19 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
         // Block b's tile is read from TMEM while block b-1's float work runs: the load is
         // asynchronous until wait_ld, and the two register tiles alternate.
         auto fetch = [&](int b, int (&v)[P_COLS]) -> bool {
-            if (!wait_or_abort(tfull + b % P_TBUF, (b / P_TBUF) & 1, abort_flag)) return false;
-            if (tid == 0) PTL(9, b);
-            umma::fence_after_sync();
-            if (tid == 0) PTL(0, 8 + b);
+            if (b % P_GROUP == 0) {  // first block of a group: its MMAs are all done
+                if (!wait_or_abort(tfull + (b / P_GROUP) % P_NGRP, (b / P_TBUF) & 1, abort_flag)) return false;
+                umma::fence_after_sync();
+            }
             umma::ld_32x16(tbase + (b % P_TBUF) * P_TOK, v);
             return true;
         };
-        auto release = [&](int b) {  // after wait_ld: the buffer may be overwritten
-            umma::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tempty + b % P_TBUF);
+        auto release = [&](int b) {  // after wait_ld of a group's last block: its half may be overwritten
+            if (b % P_GROUP == P_GROUP - 1 || b == nb - 1) {
+                umma::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty + (b / P_GROUP) % P_NGRP);
+            }
         };
         int va[P_COLS], vb[P_COLS];
         if (ok) ok = fetch(0, va);
