@@ -34,6 +34,12 @@ sys.path.insert(0, ROOT)
 from tachyon_b200 import synth, workloads  # noqa: E402
 
 METRIC = "granite_moe_decode_tokens_per_s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gate_up expert kernel,
+# from the ncu capture summarised in profiles/expert_fast_kernel_granite1b_q8_batch32.md
+# (read 35,761,408 B, written 0 B: the 0.5 MB of output stays in L2). Keyed by workload; other
+# workloads have no capture and report null.
+NCU_DRAM_BYTES_PER_LAUNCH = {("granite-1b-a400m", "q8", 32): 35761408}
 UNIT = "tokens/s"
 EPS = 1e-6
 
@@ -350,7 +356,7 @@ def main():
         "frac_of_8TBs_nominal": achieved / 8000.0,
         "algorithmic_bytes_per_launch": gu_bytes, "avg_launch_us": gu_ms * 1e3,
         "distinct_experts_per_layer": mean_u,
-        "traffic": None,
+        "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((shape.name, shape.fmt, args.batch)),
         "kernel_share_of_step": {k: v[0] / total_prof for k, v in prof.items() if v[1]},
         "down_kernel": {"achieved": (mean_u * eb_dn + args.batch * shape.topk * (shape.inter + 4 * 8)
                                      + args.batch * shape.topk * shape.hidden * 4) / (stage_ms["down"] * 1e-3) / 1e9,
