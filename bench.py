@@ -54,6 +54,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="plain stream order between the kernels of a block (no programmatic dependent launch)")
     return ap.parse_args()
 
 
@@ -211,6 +213,8 @@ def main():
         dist.init_process_group("gloo")
         dist.barrier()
     ctx = cuda.Context(local_rank)
+    if args.no_overlap:
+        ctx.set_launch_overlap(False)
 
     if world == 1:
         weights_host, gen_s = build_weights(shape, args.layers, args.seed, host_threads)

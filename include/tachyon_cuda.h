@@ -51,6 +51,11 @@ void *tc_stream(tc_ctx *ctx);
 enum { TC_ARITH_FAST = 0, TC_ARITH_CPU_LANES = 1 };
 int tc_set_arithmetic(tc_ctx *ctx, int mode);
 
+/* Overlap of consecutive kernels of a block (programmatic dependent launch:
+ * a kernel's weight prefetch runs under the previous kernel's tail). Process-wide,
+ * on by default; results do not depend on it. */
+int tc_set_launch_overlap(tc_ctx *ctx, int on);
+
 /* From how many tokens per expert (batch tokens x experts per token / experts,
  * on average) a block's expert products run on the tcgen05 tensor-core kernels
  * instead of the bandwidth-oriented ones. Default 32; 0 = always; a huge value

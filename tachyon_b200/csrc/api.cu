@@ -208,6 +208,10 @@ bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
 
 }  // namespace
 
+namespace tc {
+bool g_launch_overlap = true;
+}
+
 extern "C" {
 
 tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
@@ -331,6 +335,12 @@ void tc_host_free(tc_ctx* ctx, void* host) {
 int tc_set_arithmetic(tc_ctx* ctx, int mode) {
     if (mode != TC_ARITH_FAST && mode != TC_ARITH_CPU_LANES) return fail(ctx, "unknown arithmetic mode %d", mode);
     ctx->arith = mode;
+    return 0;
+}
+
+int tc_set_launch_overlap(tc_ctx* ctx, int on) {
+    (void)ctx;
+    tc::g_launch_overlap = on != 0;
     return 0;
 }
 

@@ -22,6 +22,10 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
     __shared__ uint32_t s_pos[MAX_TOPK];
     __shared__ float s_gate[MAX_TOPK];
     const int token = blockIdx.x, tid = threadIdx.x;
+    KTL_BEGIN(3)
+    grid_launch_dependents();
+    grid_dependency_wait();
+    KTL_MARK(2)
     if (tid < topk) {
         const uint32_t mine = ids[size_t(token) * topk + tid];
         int rank = 0;
@@ -49,14 +53,18 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
         r.w = r.w + proj.w;
         *reinterpret_cast<float4*>(yr + c) = r;
     }
+    KTL_MARK(3)
 }
 
 }  // namespace
 
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream) {
-    combine_kernel<<<t, COMBINE_THREADS, 0, stream>>>(ws.ids, ws.gates, ws.pos, ws.out, d.hidden,
-                                                      d.topk, y);
+    launch_overlapped(combine_kernel, dim3(t), dim3(COMBINE_THREADS), size_t(0), stream,
+                      static_cast<const uint32_t*>(ws.ids), static_cast<const float*>(ws.gates),
+                      static_cast<const uint32_t*>(ws.pos), static_cast<const float*>(ws.out), d.hidden, d.topk, y);
     return 1;
 }
 
 }  // namespace tc
+
+KTL_DUMP(tc_debug_ktl_combine)

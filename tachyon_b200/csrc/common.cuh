@@ -122,6 +122,73 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
                           const uint32_t* out_rows, int sms, cudaStream_t stream);
 
+// ---- overlapping consecutive kernels of a block (programmatic dependent launch)
+//
+// The four kernels of a block are launched with the programmatic-stream-
+// serialization attribute: each may start while the one in front of it still
+// runs, does the part of its prologue that reads nothing an earlier kernel
+// writes (barrier setup, weight prefetch), and then waits for the earlier grid
+// to complete. Every such kernel executes grid_dependency_wait() on every path,
+// before its first read or write of shared state, so completion stays
+// transitive along the chain. Off: plain stream order.
+extern bool g_launch_overlap;
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_launch_overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
+#if defined(TC_TIMELINE) && defined(__CUDACC__)
+// Diagnostic build only: wall-clock stamps (ns) of CTA 0 of each launch in this
+// translation unit: kind, entry, after the dependency wait, exit.
+static __device__ unsigned long long g_ktl[2048][4];
+static __device__ unsigned g_ktl_n;
+__device__ __forceinline__ unsigned long long ktl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define KTL_BEGIN(kind)                                                  \
+    unsigned ktl_slot = 0xffffffffu;                                     \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {        \
+        ktl_slot = atomicAdd(&g_ktl_n, 1u) % 2048u;                      \
+        g_ktl[ktl_slot][0] = (kind);                                     \
+        g_ktl[ktl_slot][1] = ktl_now();                                  \
+    }
+#define KTL_MARK(i) \
+    if (ktl_slot != 0xffffffffu) g_ktl[ktl_slot][i] = ktl_now();
+#define KTL_DUMP(name)                                                               \
+    extern "C" int name(unsigned long long* out, unsigned* n) {                      \
+        cudaMemcpyFromSymbol(n, tc::g_ktl_n, sizeof(unsigned));                      \
+        return int(cudaMemcpyFromSymbol(out, tc::g_ktl, sizeof(tc::g_ktl)));         \
+    }
+#else
+#define KTL_BEGIN(kind)
+#define KTL_MARK(i)
+#define KTL_DUMP(name)
+#endif
+
+// Batches that reach (nearly) every expert walk all experts with a partition that
+// does not depend on the routing; smaller ones walk the list of experts that have
+// tokens. At 4 picks per expert on average an expert is left out with p < 2 %.
+inline bool dense_walk(const MoeDims& d, int t) { return (long long)t * d.topk >= 4LL * d.experts; }
+
 // ---- prefill-size groups on tcgen05 (experts_prefill.cu)
 struct PrefillWeights {  // per layer: int8 tiles + f32 block scales (and 4-bit offsets)
     int8_t *gu_t = nullptr, *dn_t = nullptr;

@@ -62,6 +62,7 @@ struct FastArgs {
     int stages;            // ring depth per warp
     int x_stride;          // bytes per staged activation row (cols + 16)
     int nbp;               // pad8(cols / 32)
+    int dense;             // walk every expert (static partition) instead of the active list
 };
 
 // Shared memory carve-up (offsets in bytes).
@@ -169,8 +170,9 @@ struct FWalker {
                 cur.valid = false;
                 return;
             }
-            cur.e = f.e.active[cur.ai];
+            cur.e = f.dense ? cur.ai : int(f.e.active[cur.ai]);
             cur.m = f.e.counts[cur.e];
+            if (f.dense && cur.m == 0) cur.m = 1;  // an expert nobody picked is walked once, with no tokens
             const int seg_lo = max(lo, cur.ai * upe);
             cur.seg_hi = min(hi, (cur.ai + 1) * upe);
             if (uint32_t(cur.sg0) < cur.m) {
@@ -340,7 +342,7 @@ __device__ long long g_timeline[148][F_MAX_WARPS][16];
 // One segment of the CTA's walk: an expert and up to F_TOK of its tokens.
 struct Segment {
     int ai, e, sg0, ntok, G;
-    uint32_t m, base;
+    uint32_t m, mw, base;  // tokens of the expert; the same, at least 1 in a dense walk
     bool valid;
 };
 
@@ -353,6 +355,8 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
     const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
     const Layout<KIND> L(nwarps, f.stages, a.cols, f.nbp);
     const int STAGES = f.stages;
+    KTL_BEGIN(GATE_UP ? 1 : 2)
+    grid_launch_dependents();
     TL(0);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
@@ -364,7 +368,31 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
     __syncthreads();
     TL(1);
     const int upe = a.units_per_expert;
-    const int total = a.active[a.experts] * upe;
+    const int nchunks = (a.cols + F_KC - 1) / F_KC;
+    // Dense walk (batches that reach nearly every expert): the partition of units over
+    // CTAs and warps does not depend on the routing, so each warp's first records are
+    // requested before this grid waits for the one in front of it in the stream: the
+    // weights stream in while the router (or the gate_up kernel's tail) still runs.
+    int npre = 0;
+    if (f.dense) {
+        const int total_d = a.experts * upe;
+        const int lo_d = int((long long)blockIdx.x * total_d / gridDim.x);
+        const int hi_d = int((long long)(blockIdx.x + 1) * total_d / gridDim.x);
+        const int a0 = lo_d + warp;  // the first expert of the range starts the rotation at warp 0
+        if (a0 < min(hi_d, (lo_d / upe + 1) * upe)) {
+            npre = min(STAGES - 1, nchunks);
+            if (lane == 0) {
+                for (int s = 0; s < npre; s++) {
+                    mbar_expect_tx(bars + s, R::BYTES);
+                    bulk_copy(ring + s * R::BYTES, f.tiled + (size_t(a0) * nchunks + s) * R::BYTES, R::BYTES,
+                              bars + s);
+                }
+            }
+        }
+    }
+    grid_dependency_wait();  // everything below reads what earlier kernels wrote
+    KTL_MARK(2)
+    const int total = (f.dense ? a.experts : int(a.active[a.experts])) * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
 
@@ -386,7 +414,11 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         fills++;
         wk.advance(prod);
     };
-    for (int s = 0; s < STAGES - 1; s++) fill_next();
+    for (int s = 0; s < npre; s++) {  // already on their way
+        fills++;
+        wk.advance(prod);
+    }
+    for (int s = npre; s < STAGES - 1; s++) fill_next();
     TL(2);
 
     const int g = lane >> 2, t = lane & 3;
@@ -403,23 +435,26 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
     Segment next;
     next.ai = lo / upe;
     next.sg0 = -F_TOK;
-    next.m = 0;
+    next.m = next.mw = 0;
     next.valid = lo < hi;
+    bool walking = false;
     auto step_segment = [&](Segment& sgm) {
         if (!sgm.valid) return;
         sgm.sg0 += F_TOK;
-        while (uint32_t(sgm.sg0) >= sgm.m) {  // first call, or past this expert's tokens
-            if (sgm.m != 0) sgm.ai++;
+        while (!walking || uint32_t(sgm.sg0) >= sgm.mw) {  // first call, or past this expert's tokens
+            if (walking) sgm.ai++;
+            walking = true;
             if (sgm.ai * upe >= hi) {
                 sgm.valid = false;
                 return;
             }
-            sgm.e = a.active[sgm.ai];
+            sgm.e = f.dense ? sgm.ai : int(a.active[sgm.ai]);
             sgm.m = a.counts[sgm.e];
+            sgm.mw = f.dense && sgm.m == 0 ? 1u : sgm.m;
             sgm.base = a.offsets[sgm.e];
             sgm.sg0 = 0;
         }
-        sgm.ntok = min(F_TOK, int(sgm.m) - sgm.sg0);
+        sgm.ntok = max(0, min(F_TOK, int(sgm.m) - sgm.sg0));
         sgm.G = (sgm.ntok + 7) >> 3;
     };
     step_segment(next);
@@ -575,7 +610,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                 const int blk0 = cons.c * F_NBC;
                 if (sg.G == 1)
                     fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
-                else
+                else if (sg.G == 2)  // (0: an expert without tokens in a dense walk; its records are only drained)
                     fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 __syncwarp();
 #ifdef TC_TIMELINE
@@ -633,6 +668,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
 #endif
     }
     TL(15);
+    KTL_MARK(3)
 #ifdef TC_TIMELINE
     if (GATE_UP && lane == 0 && blockIdx.x < 148) {
         g_timeline[blockIdx.x][warp][12] = tl_wait;
@@ -724,9 +760,10 @@ bool pick_config(int cols, int nbp, int& nwarps, int& stages) {
 }
 
 template <int KIND, bool GATE_UP>
-int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, cudaStream_t stream) {
+int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, bool dense, cudaStream_t stream) {
     FastArgs f;
     f.e = e;
+    f.dense = dense ? 1 : 0;
     f.tiled = tiled;
     f.nbp = (e.cols / QK + SUPER - 1) / SUPER * SUPER;
     f.x_stride = e.cols + 16;
@@ -736,7 +773,7 @@ int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, cudaStream_t
     int grid = min(sms, total_units);
     if (grid < 1) grid = 1;
     const Layout<KIND> L(nwarps, f.stages, e.cols, f.nbp);
-    expert_fast_kernel<KIND, GATE_UP><<<grid, nwarps * 32, L.total, stream>>>(f);
+    launch_overlapped(expert_fast_kernel<KIND, GATE_UP>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, f);
     return 1;
 }
 
@@ -796,15 +833,18 @@ int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* til
                         int sms, cudaStream_t stream) {
     (void)t;
     const ExpertArgs a = gate_up_args(d, m, ws);
-    return m.kind == 1 ? launch_fast<1, true>(a, tiled, sms, stream) : launch_fast<2, true>(a, tiled, sms, stream);
+    const bool dense = dense_walk(d, t);
+    return m.kind == 1 ? launch_fast<1, true>(a, tiled, sms, dense, stream)
+                       : launch_fast<2, true>(a, tiled, sms, dense, stream);
 }
 
 int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, int t, Workspace& ws,
                      int sms, cudaStream_t stream) {
-    (void)t;
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;  // quantized while staged: no separate pass over the SwiGLU rows
-    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
+    const bool dense = dense_walk(d, t);
+    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, dense, stream)
+                       : launch_fast<2, false>(a, tiled, sms, dense, stream);
 }
 
 // The down projection with each output row written to out_rows[slot] (expert
@@ -814,7 +854,10 @@ int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* t
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;
     a.out_rows = out_rows;
-    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, stream) : launch_fast<2, false>(a, tiled, sms, stream);
+    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, false, stream)
+                       : launch_fast<2, false>(a, tiled, sms, false, stream);
 }
 
 }  // namespace tc
+
+KTL_DUMP(tc_debug_ktl_experts)

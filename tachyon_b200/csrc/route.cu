@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     const int token = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hidden = a.hidden, experts = a.experts, topk = a.topk;
+    KTL_BEGIN(0)
+    grid_launch_dependents();
     // The router matrix, one bulk copy per row, into rows padded by 32 bytes (so the four-thread
     // groups of a half-warp read distinct banks). Issued first: it lands while the row is normed.
     const int wstride = 2 * hidden + 32;
@@ -134,6 +136,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
             for (int e = lane; e < experts; e += 32)
                 bulk_copy(wsm + size_t(e) * wstride, a.router + size_t(e) * hidden, 2 * hidden, &s_wbar);
     }
+    // The router matrix is a constant: it streams in while the kernel in front of this
+    // one (the previous block's combine) finishes. Everything below reads its output.
+    grid_dependency_wait();
+    KTL_MARK(2)
     const float* xin = a.x + size_t(token) * hidden;
     RTL(0);
     for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
@@ -325,6 +331,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
     RTL(6);
+    KTL_MARK(3)
 }
 
 
@@ -386,7 +393,7 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
     if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
-    route_kernel<<<t, ROUTE_THREADS, smem, stream>>>(a);
+    launch_overlapped(route_kernel, dim3(t), dim3(ROUTE_THREADS), smem, stream, a);
     int launched = 1;
     if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
     return launched;
@@ -400,3 +407,5 @@ int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, floa
 }
 
 }  // namespace tc
+
+KTL_DUMP(tc_debug_ktl_route)

@@ -29,6 +29,7 @@ SYMBOLS = {
     "tc_stream": (_vp, [_vp]),
     "tc_set_arithmetic": (_i, [_vp, _i]),
     "tc_set_prefill_threshold": (_i, [_vp, _i]),
+    "tc_set_launch_overlap": (_i, [_vp, _i]),
     "tc_malloc": (_vp, [_vp, _sz]),
     "tc_free": (None, [_vp, _vp]),
     "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
@@ -142,6 +143,10 @@ class Context:
     def set_arithmetic(self, mode: int):
         """ARITH_FAST (default) or ARITH_CPU_LANES (bit-identical to the CPU path)."""
         self._check(self.lib.tc_set_arithmetic(self.handle, mode), "tc_set_arithmetic")
+
+    def set_launch_overlap(self, on: bool):
+        """Programmatic dependent launch between the kernels of a block (default on)."""
+        self._check(self.lib.tc_set_launch_overlap(self.handle, int(on)), "tc_set_launch_overlap")
 
     def set_prefill_threshold(self, avg_tokens_per_expert: int):
         """Average tokens per expert from which the tcgen05 kernels take over (default 32; 0 = always)."""
