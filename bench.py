@@ -54,6 +54,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-exchange", default="fixed", choices=["fixed", "alltoallv"],
+                    help="N > 1: all-gather + reduce-scatter of fixed size inside a CUDA graph, or the "
+                         "variable-size all-to-all enqueued directly")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain stream order between the kernels of a block (no programmatic dependent launch)")
     return ap.parse_args()
@@ -169,7 +172,9 @@ def config_dict(args, shape, world):
         "weights": "q8 (int8 + f16 scale per 32), router bf16",
         "parallelism": "1 GPU" if world == 1 else
                        f"ep{world}: experts sharded over {world} GPUs (contiguous ranges), tokens data-parallel, "
-                       f"NCCL all-to-all-v dispatch and combine per block",
+                       + ("NCCL all-gather of the 8-bit rows and reduce-scatter of the expert outputs per block, "
+                          "one CUDA graph per step" if args.ep_exchange == "fixed"
+                          else "NCCL all-to-all-v dispatch and combine per block"),
         "l2": "each step streams every layer's expert weights (1.28 GB at 24 layers), more than the 126 MB L2",
     }
 
@@ -224,7 +229,7 @@ def main():
 
         box = [ep.unique_id(ctx) if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
-        ep.init(ctx, box[0], rank, world)
+        ep.init(ctx, box[0], rank, world, uniform_batch=args.ep_exchange == "fixed")
         first, count = ep.shard_range(shape.experts, rank, world)
         t0 = time.time()
         layers = []
@@ -261,13 +266,13 @@ def main():
         prof = ctx.profile_read()
         ctx.profile_enable(False)
 
-    # ---- the timed stack, device-resident inputs: one CUDA graph per step on one GPU;
-    # the expert-parallel block reads exchange sizes on the host, so it is enqueued directly.
+    # ---- the timed stack, device-resident inputs: one CUDA graph per step. (The variable-size
+    # expert-parallel exchange reads its sizes on the host, so that one is enqueued directly.)
     class Eager:
         def launch(self):
             enqueue_stack()
 
-    if world == 1:
+    if world == 1 or args.ep_exchange == "fixed":
         ctx.capture_begin()
         enqueue_stack()
         graph = ctx.capture_end()

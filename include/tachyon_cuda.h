@@ -155,6 +155,15 @@ int tc_dispatch_static(tc_ctx *ctx, const uint32_t *ids_dev, int t, int experts,
 int tc_ep_unique_id(char *out128);
 int tc_ep_init(tc_ctx *ctx, const char *id128, int rank, int size);
 int tc_ep_expert_range(int experts, int rank, int size, int *first, int *count);
+/* Promise that every rank calls each block with the SAME number of tokens. Layers
+ * created afterwards then run decode-size blocks (ranks x tokens x experts-per-
+ * token x hidden x 4 bytes <= 64 MiB) through a fixed-size exchange: one grouped
+ * all-gather of the 8-bit rows and expert ids, the dispatch over all ranks'
+ * tokens, this rank's experts, one reduce-scatter of the slot-ordered outputs.
+ * Nothing is read on the host, so such a block can be captured in a CUDA graph;
+ * same values as one GPU. Larger blocks keep the all-to-all-v exchange. Create
+ * every layer before capturing. */
+int tc_ep_set_uniform_batch(tc_ctx *ctx, int on);
 tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int experts_per_token, int inter,
                                      const tc_matrix *router, const tc_matrix *gate_up_local,
                                      const tc_matrix *down_local, int max_tokens);

@@ -460,6 +460,11 @@ int tc_ep_init(tc_ctx* ctx, const char* id128, int rank, int size) {
     return why ? fail(ctx, "tc_ep_init: %s", why) : 0;
 }
 
+int tc_ep_set_uniform_batch(tc_ctx* ctx, int on) {
+    ctx->ep.uni.on = on != 0;
+    return 0;
+}
+
 int tc_ep_expert_range(int experts, int rank, int size, int* first, int* count) {
     if (size < 1 || rank < 0 || rank >= size) return -1;
     tc::ep_expert_range(experts, rank, size, first, count);
@@ -502,6 +507,10 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
     l->ep = ep;
     tc::MoeDims dl = d;  // the shape of the matrices held here
     dl.experts = local;
+    if (ep && ctx->ep.uni.on && !tc::ep_uniform_reserve(ctx->ep, d, max_tokens)) {
+        delete l;
+        return bad("could not allocate the fixed-size exchange buffers");
+    }
     if (ep && !tc::ep_layer_alloc(l->epb, ctx->ep, d, max_tokens)) {
         tc::ep_layer_free(l->epb);
         delete l;
@@ -587,6 +596,17 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     tc::Workspace& ws = ctx->ws;
     cudaStream_t s = ctx->stream;
     int n = 0;
+    if (layer->ep && tc::ep_uniform_applies(ctx->ep, d, t)) {
+        const char* why = tc::ep_forward_uniform(ctx->ep, layer->epb, d,
+                                                 static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
+                                                 layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                                 layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
+        ctx->launches += n;
+        layer->last_t = t;
+        if (why) return fail(ctx, "expert-parallel block: %s", why);
+        if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+        return 0;
+    }
     if (layer->ep) {
         if (ctx->capturing) return fail(ctx, "the expert-parallel block reads exchange sizes on the host: it cannot be captured");
         const char* why = tc::ep_forward(ctx->ep, layer->epb, d, static_cast<const uint16_t*>(layer->router->dev.data),

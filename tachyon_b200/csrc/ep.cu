@@ -42,6 +42,8 @@ struct NcclApi {
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t,
+                                  cudaStream_t) = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
@@ -60,12 +62,13 @@ NcclApi& nccl() {
     api.CommInitRank = reinterpret_cast<decltype(api.CommInitRank)>(sym("ncclCommInitRank"));
     api.CommDestroy = reinterpret_cast<decltype(api.CommDestroy)>(sym("ncclCommDestroy"));
     api.AllGather = reinterpret_cast<decltype(api.AllGather)>(sym("ncclAllGather"));
+    api.ReduceScatter = reinterpret_cast<decltype(api.ReduceScatter)>(sym("ncclReduceScatter"));
     api.Send = reinterpret_cast<decltype(api.Send)>(sym("ncclSend"));
     api.Recv = reinterpret_cast<decltype(api.Recv)>(sym("ncclRecv"));
     api.GroupStart = reinterpret_cast<decltype(api.GroupStart)>(sym("ncclGroupStart"));
     api.GroupEnd = reinterpret_cast<decltype(api.GroupEnd)>(sym("ncclGroupEnd"));
     api.GetErrorString = reinterpret_cast<decltype(api.GetErrorString)>(sym("ncclGetErrorString"));
-    if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.Send && api.Recv &&
+    if (api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.ReduceScatter && api.Send && api.Recv &&
         api.GroupStart && api.GroupEnd)
         api.lib = h;
     return api;
@@ -184,6 +187,8 @@ const char* ep_init(EpState& st, const char* id128, int rank, int size) {
 }
 
 void ep_destroy(EpState& st) {
+    for (void* p : st.uni.allocs) cudaFree(p);
+    st.uni.allocs.clear();
     if (st.comm) nccl().CommDestroy(st.comm);
     st.comm = nullptr;
     if (st.hist_host) cudaFreeHost(st.hist_host);
@@ -214,6 +219,128 @@ bool ep_layer_alloc(EpLayerBuffers& b, const EpState& st, const MoeDims& d, int 
 void ep_layer_free(EpLayerBuffers& b) {
     for (void* p : b.allocs) cudaFree(p);
     b.allocs.clear();
+}
+
+// ---------------------------------------------------------------------------
+// The fixed-size exchange, for decode-size blocks where every rank brings the
+// same number of tokens t. Nothing is read on the host, so the block can be
+// captured in a CUDA graph:
+//   1. route (own tokens);
+//   2. one grouped all-gather of every rank's 8-bit rows, scales and expert ids;
+//   3. dispatch over all size * t tokens and all experts (the same kernels as on one
+//      GPU); this rank's experts are a contiguous run of the sorted slots;
+//   4. gate_up + SwiGLU and down on the local experts, each output row written at
+//      its (home rank, token, pick) place in a zeroed [size * t * k, H] buffer;
+//   5. reduce-scatter (sum): every row has one producer, so a home rank receives
+//      x + 0 + ... + 0 = x exactly, in (token, pick) order;
+//   6. the usual combine, reading the rows in place.
+// The return moves size * t * k * H * 4 bytes per rank whatever the routing, which
+// is why this path is limited to blocks where that is a few megabytes.
+constexpr size_t UNIFORM_MAX_BYTES = size_t(64) << 20;
+
+__global__ void iota_kernel(uint32_t* out, size_t n) {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x)
+        out[i] = uint32_t(i);
+}
+
+bool ep_uniform_reserve(EpState& st, const MoeDims& d, int max_tokens) {
+    EpUniform& u = st.uni;
+    const int G = max_tokens * st.size;
+    if (size_t(G) * d.topk * d.hidden * 4 > UNIFORM_MAX_BYTES || G > 16384) return true;  // not for this size
+    if (u.tokens >= G && u.hidden >= d.hidden && u.experts >= d.experts && u.topk >= d.topk && u.inter >= d.inter)
+        return true;
+    cudaDeviceSynchronize();
+    for (void* p : u.allocs) cudaFree(p);
+    u.allocs.clear();
+    const int T = G > u.tokens ? G : u.tokens, H = d.hidden > u.hidden ? d.hidden : u.hidden,
+              E = d.experts > u.experts ? d.experts : u.experts, K = d.topk > u.topk ? d.topk : u.topk,
+              I = d.inter > u.inter ? d.inter : u.inter;
+    const size_t nbp = (H / QK + 7) / 8 * 8, slots = size_t(T) * K;
+    auto get = [&](auto*& p, size_t elems) {
+        void* raw = nullptr;
+        if (cudaMalloc(&raw, elems * sizeof(*p) + 256) != cudaSuccess) return false;
+        u.allocs.push_back(raw);
+        p = static_cast<std::remove_reference_t<decltype(p)>>(raw);
+        return true;
+    };
+    const bool ok = get(u.xq, size_t(T) * H) && get(u.xs, size_t(T) * nbp) && get(u.xsum, size_t(T) * nbp) &&
+                    get(u.ids, slots) && get(u.counts, size_t(E) + 1) && get(u.offsets, size_t(E) + 2) &&
+                    get(u.perm, slots) && get(u.pos, slots) && get(u.slot_token, slots) &&
+                    get(u.active, size_t(E) + 2) && get(u.block_hist, size_t((T + 255) / 256) * E) &&
+                    get(u.hidden_f, slots * I) && get(u.big, slots * H) && get(u.identity, slots);
+    if (!ok) {
+        for (void* p : u.allocs) cudaFree(p);
+        u.allocs.clear();
+        u.tokens = 0;
+        return false;
+    }
+    iota_kernel<<<64, 256>>>(u.identity, slots);
+    cudaDeviceSynchronize();
+    u.tokens = T, u.hidden = H, u.experts = E, u.topk = K, u.inter = I;
+    return true;
+}
+
+bool ep_uniform_applies(const EpState& st, const MoeDims& d, int t) {
+    const EpUniform& u = st.uni;
+    return u.on && size_t(t) * st.size <= size_t(u.tokens) && d.hidden <= u.hidden && d.experts <= u.experts &&
+           d.topk <= u.topk && d.inter <= u.inter;
+}
+
+const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
+                               const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
+                               const MatrixDev& down, const uint8_t* down_tiled, const float* x,
+                               const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
+                               cudaStream_t stream, int* launches) {
+    NcclApi& n = nccl();
+    EpUniform& u = st.uni;
+    const int R = st.size, G = R * t;
+    const int nbp = (d.hidden / QK + 7) / 8 * 8;
+    *launches += launch_route(d, router, bias, x, norm_w, eps, t, ws, stream);
+    n.GroupStart();
+    n.AllGather(ws.xq, u.xq, size_t(t) * d.hidden, ncclInt8, st.comm, stream);
+    n.AllGather(ws.xs, u.xs, size_t(t) * nbp, ncclFloat32, st.comm, stream);
+    n.AllGather(ws.ids, u.ids, size_t(t) * d.topk, ncclUint32, st.comm, stream);
+    if (n.GroupEnd() != ncclSuccess) return "all-gather of the token rows failed";
+
+    Workspace gw = ws;  // the view over every rank's tokens
+    gw.ids = u.ids;
+    gw.xq = u.xq;
+    gw.xs = u.xs;
+    gw.xsum = u.xsum;
+    gw.counts = u.counts;
+    gw.offsets = u.offsets;
+    gw.perm = u.perm;
+    gw.pos = u.pos;
+    gw.slot_token = u.slot_token;
+    gw.active = u.active;
+    gw.block_hist = u.block_hist;
+    *launches += launch_dispatch(d, G, gw, stream);
+    if (gate_up.kind == 2) {
+        const size_t want_blocks = (size_t(G) * nbp + 7) / 8;
+        block_sums_kernel<<<unsigned(want_blocks < 148 * 16 ? want_blocks : 148 * 16), 256, 0, stream>>>(
+            u.xq, u.xs, size_t(G), d.hidden, nbp, u.xsum);
+        *launches += 1;
+    }
+    cudaMemsetAsync(u.big, 0, size_t(G) * d.topk * d.hidden * sizeof(float), stream);
+
+    MoeDims ld = d;
+    ld.experts = b.local;
+    Workspace lw = gw;  // this rank's experts: a contiguous run of the sorted slots
+    lw.counts = u.counts + b.first;
+    lw.offsets = u.offsets + b.first;
+    lw.active = nullptr;  // no list of this run's non-empty experts: the kernels walk them all
+    lw.hidden_f = u.hidden_f;
+    lw.out = u.big;
+    *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
+    *launches += launch_down_fast_rows(ld, down, down_tiled, lw, u.perm, sms, stream);
+
+    if (n.ReduceScatter(u.big, ws.out, size_t(t) * d.topk * d.hidden, ncclFloat32, ncclSum, st.comm, stream) !=
+        ncclSuccess)
+        return "reduce-scatter of the expert outputs failed";
+    Workspace cw = ws;
+    cw.pos = u.identity;  // rows arrive in (token, pick) order
+    *launches += launch_combine(d, t, cw, y, stream);
+    return nullptr;
 }
 
 // The block over expert-parallel ranks. `gate_up_tiled` / `down_tiled` hold this

@@ -9,11 +9,30 @@ struct ncclComm;
 
 namespace tc {
 
+// Buffers of the fixed-size exchange (every rank brings the same number of tokens):
+// all ranks' rows gathered here, their dispatch, and the slot-ordered output
+// buffer that the reduce-scatter returns to the tokens' home ranks. Shared by the
+// context's layers.
+struct EpUniform {
+    bool on = false;
+    int tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;  // sized for (tokens = size * per-rank)
+    int8_t* xq = nullptr;                  // [G, H]
+    float *xs = nullptr, *xsum = nullptr;  // [G, pad8(H/32)]
+    uint32_t* ids = nullptr;               // [G, k]
+    uint32_t *counts = nullptr, *offsets = nullptr, *perm = nullptr, *pos = nullptr, *slot_token = nullptr;
+    int* active = nullptr;
+    uint32_t* block_hist = nullptr;
+    float *hidden_f = nullptr, *big = nullptr;  // [G*k, I]; [G*k, H]
+    uint32_t* identity = nullptr;               // [T*k] = 0, 1, 2, ...
+    std::vector<void*> allocs;
+};
+
 struct EpState {
     ncclComm* comm = nullptr;
     int rank = 0, size = 1;
     uint32_t* hist_host = nullptr;  // pinned [size * experts]
     size_t hist_host_elems = 0;
+    EpUniform uni;
 };
 
 struct EpLayerBuffers {
@@ -35,6 +54,15 @@ const char* ep_init(EpState& st, const char* id128, int rank, int size);
 void ep_destroy(EpState& st);
 bool ep_layer_alloc(EpLayerBuffers& b, const EpState& st, const MoeDims& d, int max_tokens);
 void ep_layer_free(EpLayerBuffers& b);
+// Sizes the fixed-size exchange for blocks of up to max_tokens tokens per rank.
+bool ep_uniform_reserve(EpState& st, const MoeDims& d, int max_tokens);
+// True if a block of t tokens per rank goes through the fixed-size exchange.
+bool ep_uniform_applies(const EpState& st, const MoeDims& d, int t);
+const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
+                               const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
+                               const MatrixDev& down, const uint8_t* down_tiled, const float* x,
+                               const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
+                               cudaStream_t stream, int* launches);
 const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                        const MatrixDev& down, const uint8_t* down_tiled, const float* x,

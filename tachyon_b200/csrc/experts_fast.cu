@@ -833,7 +833,7 @@ int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* til
                         int sms, cudaStream_t stream) {
     (void)t;
     const ExpertArgs a = gate_up_args(d, m, ws);
-    const bool dense = dense_walk(d, t);
+    const bool dense = dense_walk(d, t) || !ws.active;
     return m.kind == 1 ? launch_fast<1, true>(a, tiled, sms, dense, stream)
                        : launch_fast<2, true>(a, tiled, sms, dense, stream);
 }
@@ -854,8 +854,9 @@ int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* t
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;
     a.out_rows = out_rows;
-    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, false, stream)
-                       : launch_fast<2, false>(a, tiled, sms, false, stream);
+    const bool dense = !ws.active;  // a caller without a list of non-empty experts
+    return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, dense, stream)
+                       : launch_fast<2, false>(a, tiled, sms, dense, stream);
 }
 
 }  // namespace tc

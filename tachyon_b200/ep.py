@@ -64,9 +64,14 @@ def unique_id(ctx: Context) -> bytes:
     return buf.raw
 
 
-def init(ctx: Context, uid: bytes, rank: int, size: int):
+def init(ctx: Context, uid: bytes, rank: int, size: int, uniform_batch: bool = False):
+    """Collective. uniform_batch=True promises that every rank calls each block with the
+    same number of tokens: decode-size blocks then use the fixed-size exchange (an
+    all-gather and a reduce-scatter, no host read, capturable in a CUDA graph)."""
     ctx._check(ctx.lib.tc_ep_init(ctx.handle, uid, rank, size), "tc_ep_init")
     ctx.ep_rank, ctx.ep_size = rank, size
+    if uniform_batch:
+        ctx._check(ctx.lib.tc_ep_set_uniform_batch(ctx.handle, 1), "tc_ep_set_uniform_batch")
 
 
 class EpMoeLayer(MoeLayer):

@@ -28,7 +28,7 @@ def _device_count():
     return n.value if rt.cudaGetDeviceCount(ctypes.byref(n)) == 0 else 0
 
 
-def _rank_main(rank, size, tmp, fmt, tokens):
+def _rank_main(rank, size, tmp, fmt, tokens, uniform=False):
     sys.path.insert(0, ROOT)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from tachyon_b200 import cuda, ep, workloads
@@ -46,7 +46,7 @@ def _rank_main(rank, size, tmp, fmt, tokens):
                 break
             time.sleep(0.05)
         uid = open(uid_path, "rb").read()
-    ep.init(ctx, uid, rank, size)
+    ep.init(ctx, uid, rank, size, uniform_batch=uniform)
     shape = workloads.MoeShape("ep", 512, 10, 4, 128, fmt=fmt)
     lw = workloads.layer_weights(shape, seed=6)
     x_all = workloads.hidden_states(shape, tokens, seed=7)
@@ -67,6 +67,18 @@ def _rank_main(rank, size, tmp, fmt, tokens):
         ctx.sync()
         got = ys.get()
         assert np.array_equal(got, want[t0:t0 + tn]), (rank, np.abs(got - want[t0:t0 + tn]).max())
+    if uniform:
+        # The fixed-size exchange reads nothing on the host: the block replays from a CUDA graph.
+        xs, ys = ctx.to_device(x_all[t0:t0 + tn]), ctx.to_device(y0_all[t0:t0 + tn])
+        ctx.capture_begin()
+        layer.forward(xs, ys)
+        graph = ctx.capture_end()
+        for _ in range(2):
+            ctx.upload(ys.ptr, y0_all[t0:t0 + tn])
+            graph.launch()
+            ctx.sync()
+            assert np.array_equal(ys.get(), want[t0:t0 + tn])
+        graph.free()
     layer.free()
     full.free()
     ctx.close()
@@ -84,4 +96,21 @@ def test_expert_parallel_block_equals_single_gpu(tmp_path, fmt, tokens):
     build.build()
     size = 4 if n >= 4 else 2
     mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens), nprocs=size, join=True,
+                       start_method="spawn")
+
+
+@pytest.mark.parametrize("fmt,tokens", [("q8", 64), ("q4", 36), ("q8", 1024)])
+def test_fixed_size_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_path, fmt, tokens):
+    """Every rank brings tokens / size tokens: all-gather, dispatch over all of them,
+    local experts, reduce-scatter; also captured and replayed."""
+    n = _device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    from tachyon_b200 import build
+
+    build.build()
+    size = 4 if n >= 4 else 2
+    mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens, True), nprocs=size, join=True,
                        start_method="spawn")
