@@ -54,8 +54,9 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ep-exchange", default="fixed", choices=["fixed", "alltoallv"],
-                    help="N > 1: all-gather + reduce-scatter of fixed size inside a CUDA graph, or the "
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "fixed", "alltoallv"],
+                    help="N > 1: NVLink stores into mapped peer windows with flag waits (no NCCL call in a block), "
+                         "all-gather + reduce-scatter of fixed size (both from a CUDA graph), or the "
                          "variable-size all-to-all enqueued directly")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain stream order between the kernels of a block (no programmatic dependent launch)")
@@ -172,7 +173,9 @@ def config_dict(args, shape, world):
         "weights": "q8 (int8 + f16 scale per 32), router bf16",
         "parallelism": "1 GPU" if world == 1 else
                        f"ep{world}: experts sharded over {world} GPUs (contiguous ranges), tokens data-parallel, "
-                       + ("NCCL all-gather of the 8-bit rows and reduce-scatter of the expert outputs per block, "
+                       + ("rows and expert outputs stored into mapped peer windows over NVLink with flag waits "
+                          "(no NCCL call inside a block), one CUDA graph per step" if args.ep_exchange == "peer"
+                          else "NCCL all-gather of the 8-bit rows and reduce-scatter of the expert outputs per block, "
                           "one CUDA graph per step" if args.ep_exchange == "fixed"
                           else "NCCL all-to-all-v dispatch and combine per block"),
         "l2": "each step streams every layer's expert weights (1.28 GB at 24 layers), more than the 126 MB L2",
@@ -229,7 +232,9 @@ def main():
 
         box = [ep.unique_id(ctx) if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
-        ep.init(ctx, box[0], rank, world, uniform_batch=args.ep_exchange == "fixed")
+        ep.init(ctx, box[0], rank, world, uniform_batch=args.ep_exchange != "alltoallv")
+        if args.ep_exchange == "peer":
+            ep.enable_peer_exchange(ctx, shape.hidden, shape.topk, args.batch)
         first, count = ep.shard_range(shape.experts, rank, world)
         t0 = time.time()
         layers = []
@@ -250,6 +255,8 @@ def main():
         for layer in layers:
             layer.block(ones, EPS, x)  # x += moe(rmsnorm(x)): src/model.rs:662-681
 
+    if dist:
+        dist.barrier()  # ranks enter their first block together: the peer exchange's waits are bounded
     # ---- eager pass with per-kernel events: which kernel dominates, and its bandwidth
     enqueue_stack()
     ctx.sync()
@@ -272,7 +279,7 @@ def main():
         def launch(self):
             enqueue_stack()
 
-    if world == 1 or args.ep_exchange == "fixed":
+    if world == 1 or args.ep_exchange != "alltoallv":
         ctx.capture_begin()
         enqueue_stack()
         graph = ctx.capture_end()

@@ -164,6 +164,17 @@ int tc_ep_expert_range(int experts, int rank, int size, int *first, int *count);
  * same values as one GPU. Larger blocks keep the all-to-all-v exchange. Create
  * every layer before capturing. */
 int tc_ep_set_uniform_batch(tc_ctx *ctx, int on);
+/* Collective, up to 8 ranks of one NVSwitch node, before the layers are created;
+ * implies tc_ep_set_uniform_batch(ctx, 1). Blocks of up to max_tokens tokens per
+ * rank with this hidden size and experts-per-token then exchange over peer memory:
+ * each rank allocates a window, the others map it (CUDA IPC), rows and expert
+ * outputs are stored straight into the destination rank's window over NVLink and
+ * announced with flags that the consuming kernels wait for (bounded: a rank that
+ * never signals leaves an error status for tc_sync, not a hang). No collective
+ * library call runs inside a block; same values as one GPU. */
+int tc_ep_enable_peer_exchange(tc_ctx *ctx, int hidden, int experts_per_token, int max_tokens);
+/* Collective: returns when every rank has reached it (host-side barrier). */
+int tc_ep_barrier(tc_ctx *ctx);
 tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int experts_per_token, int inter,
                                      const tc_matrix *router, const tc_matrix *gate_up_local,
                                      const tc_matrix *down_local, int max_tokens);

@@ -460,6 +460,18 @@ int tc_ep_init(tc_ctx* ctx, const char* id128, int rank, int size) {
     return why ? fail(ctx, "tc_ep_init: %s", why) : 0;
 }
 
+int tc_ep_enable_peer_exchange(tc_ctx* ctx, int hidden, int experts_per_token, int max_tokens) {
+    cudaSetDevice(ctx->device);
+    const char* why = tc::ep_peer_enable(ctx->ep, hidden, experts_per_token, max_tokens);
+    return why ? fail(ctx, "tc_ep_enable_peer_exchange: %s", why) : 0;
+}
+
+int tc_ep_barrier(tc_ctx* ctx) {
+    cudaSetDevice(ctx->device);
+    const char* why = tc::ep_barrier(ctx->ep, ctx->stream);
+    return why ? fail(ctx, "tc_ep_barrier: %s", why) : 0;
+}
+
 int tc_ep_set_uniform_batch(tc_ctx* ctx, int on) {
     ctx->ep.uni.on = on != 0;
     return 0;
@@ -596,6 +608,17 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     tc::Workspace& ws = ctx->ws;
     cudaStream_t s = ctx->stream;
     int n = 0;
+    if (layer->ep && tc::ep_peer_applies(ctx->ep, d, t)) {
+        const char* why = tc::ep_forward_peer(ctx->ep, layer->epb, d,
+                                              static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
+                                              layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                              layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
+        ctx->launches += n;
+        layer->last_t = t;
+        if (why) return fail(ctx, "expert-parallel block: %s", why);
+        if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+        return 0;
+    }
     if (layer->ep && tc::ep_uniform_applies(ctx->ep, d, t)) {
         const char* why = tc::ep_forward_uniform(ctx->ep, layer->epb, d,
                                                  static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,

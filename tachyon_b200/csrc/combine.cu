@@ -18,7 +18,7 @@ constexpr int COMBINE_THREADS = 256;
 __global__ void __launch_bounds__(COMBINE_THREADS)
 combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates,
                const uint32_t* __restrict__ pos, const float* __restrict__ out, int hidden, int topk,
-               float* y) {
+               float* y, const PeerWait pw) {
     __shared__ uint32_t s_pos[MAX_TOPK];
     __shared__ float s_gate[MAX_TOPK];
     const int token = blockIdx.x, tid = threadIdx.x;
@@ -26,6 +26,10 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
     grid_launch_dependents();
     grid_dependency_wait();
     KTL_MARK(2)
+    if (pw.flags) {  // expert outputs arrive from other ranks: all of them have signalled this block
+        if (tid < pw.ranks) peer_wait(pw, tid);
+        __syncthreads();
+    }
     if (tid < topk) {
         const uint32_t mine = ids[size_t(token) * topk + tid];
         int rank = 0;
@@ -61,7 +65,8 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream) {
     launch_overlapped(combine_kernel, dim3(t), dim3(COMBINE_THREADS), size_t(0), stream,
                       static_cast<const uint32_t*>(ws.ids), static_cast<const float*>(ws.gates),
-                      static_cast<const uint32_t*>(ws.pos), static_cast<const float*>(ws.out), d.hidden, d.topk, y);
+                      static_cast<const uint32_t*>(ws.pos), static_cast<const float*>(ws.out), d.hidden, d.topk, y,
+                      ws.combine_wait);
     return 1;
 }
 

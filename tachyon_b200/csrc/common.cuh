@@ -23,6 +23,7 @@ constexpr int MAX_TOPK = 32;
 enum : int {
     ERR_NONE = 0,
     ERR_COPY_WAIT_TIMEOUT = 1,  // a staged weight copy did not arrive within the spin limit
+    ERR_PEER_WAIT_TIMEOUT = 2,  // another rank's signal did not arrive within the spin limit
 };
 
 struct MatrixDev {
@@ -33,6 +34,15 @@ struct MatrixDev {
 };
 
 // Per-context scratch, sized at layer creation for max_tokens.
+// Waiting for other ranks' signals (expert parallelism over peer memory): flags[r] is
+// written by rank r with its block counter; *epoch is this rank's own counter.
+struct PeerWait {
+    const uint32_t* flags = nullptr;  // [ranks], in this rank's memory
+    const uint32_t* epoch = nullptr;
+    int ranks = 0;
+    int* status = nullptr;
+};
+
 struct Workspace {
     int max_tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;
     float* logits = nullptr;      // [T, E]
@@ -55,6 +65,7 @@ struct Workspace {
     float* out = nullptr;         // [T*k, H] expert outputs, sorted order
     int* status = nullptr;        // device status word
     int* ticket = nullptr;        // arrival counter of the router CTAs (zero between launches)
+    PeerWait combine_wait;        // set for the peer-memory exchange only
 };
 
 struct MoeDims {
@@ -119,8 +130,10 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
                      Workspace& ws, int sms, cudaStream_t stream);
 
 // y[i] += sum over the token's experts, ascending expert index, gate * out.
+// (peer_out: when given, `ranks` buffers; output row p goes to rank p / peer_rows.)
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
-                          const uint32_t* out_rows, int sms, cudaStream_t stream);
+                          const uint32_t* out_rows, int sms, cudaStream_t stream,
+                          float* const* peer_out = nullptr, int ranks = 0, uint32_t peer_rows = 0);
 
 // ---- overlapping consecutive kernels of a block (programmatic dependent launch)
 //
@@ -182,6 +195,22 @@ __device__ __forceinline__ unsigned long long ktl_now() {
 #define KTL_BEGIN(kind)
 #define KTL_MARK(i)
 #define KTL_DUMP(name)
+#endif
+
+#ifdef __CUDACC__
+// Bounded wait for rank r's signal: about ten seconds of polling (ranks of one job
+// can be seconds apart when they enqueue their first block), then an error status;
+// the caller goes on, so the context stays usable.
+__device__ __forceinline__ void peer_wait(const PeerWait& pw, int r) {
+    const uint32_t want = *pw.epoch;
+    for (uint32_t i = 0; i < (1u << 23); i++) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(pw.flags + r) : "memory");
+        if (int32_t(seen - want) >= 0) return;
+        __nanosleep(i < 64 ? 32 : 512);
+    }
+    atomicExch(pw.status, ERR_PEER_WAIT_TIMEOUT);
+}
 #endif
 
 // Batches that reach (nearly) every expert walk all experts with a partition that

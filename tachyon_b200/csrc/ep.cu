@@ -187,6 +187,13 @@ const char* ep_init(EpState& st, const char* id128, int rank, int size) {
 }
 
 void ep_destroy(EpState& st) {
+    if (st.peer.on) {
+        for (int r = 0; r < st.size; r++)
+            if (r != st.rank && st.peer.base[r]) cudaIpcCloseMemHandle(st.peer.base[r]);
+        cudaFree(st.peer.window);
+        cudaFree(st.peer.epoch);
+        st.peer = EpPeer{};
+    }
     for (void* p : st.uni.allocs) cudaFree(p);
     st.uni.allocs.clear();
     if (st.comm) nccl().CommDestroy(st.comm);
@@ -339,6 +346,209 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
         return "reduce-scatter of the expert outputs failed";
     Workspace cw = ws;
     cw.pos = u.identity;  // rows arrive in (token, pick) order
+    *launches += launch_combine(d, t, cw, y, stream);
+    return nullptr;
+}
+
+// ---------------------------------------------------------------------------
+// The exchange over peer memory. Same plan as the fixed-size exchange, with the
+// two collectives replaced by stores into the destination rank's window:
+//   1. route (own tokens);
+//   2. peer_scatter_signal_kernel: this rank's 8-bit rows, scales and expert ids into
+//      every rank's window (NVLink stores), then a release-store of this rank's block
+//      counter into every rank's flag word;
+//   3. peer_wait_kernel: all ranks' rows have arrived here;
+//   4. dispatch over all ranks' tokens, gate_up + SwiGLU, down on this rank's experts;
+//      the down kernel stores each output row into its home rank's window at
+//      (token, pick);
+//   5. peer_signal_kernel; the combine kernel waits for every rank's signal and reads
+//      the rows in place.
+// Every wait is bounded (peer_wait) and leaves an error status instead of hanging.
+// Ordering across blocks needs no second buffer: a rank can only reach step 2 of block
+// n+1 after its combine of block n, which waited for every rank's step 5 of block n,
+// i.e. for every reader of the rows of block n.
+struct PeerPlan {
+    uint8_t* base[8];
+    size_t off_xq, off_xs, off_ids, off_flags;
+    const int8_t* xq;
+    const float* xs;
+    const uint32_t* ids;
+    int t, hidden, nbp, topk, me, ranks, flag_set;
+    uint32_t* epoch;
+};
+
+__global__ void __launch_bounds__(1024) peer_scatter_signal_kernel(const PeerPlan a) {
+    const int tid = threadIdx.x, n = blockDim.x;
+    const size_t xq_vec = size_t(a.t) * a.hidden / 16, xs_vec = size_t(a.t) * a.nbp / 4;
+    const size_t ids_n = size_t(a.t) * a.topk;
+    for (int r = 0; r < a.ranks; r++) {
+        uint8_t* w = a.base[r];
+        uint4* dq = reinterpret_cast<uint4*>(w + a.off_xq + size_t(a.me) * a.t * a.hidden);
+        const uint4* sq = reinterpret_cast<const uint4*>(a.xq);
+        for (size_t i = tid; i < xq_vec; i += n) dq[i] = sq[i];
+        uint4* ds = reinterpret_cast<uint4*>(w + a.off_xs + size_t(a.me) * a.t * a.nbp * 4);
+        const uint4* ss = reinterpret_cast<const uint4*>(a.xs);
+        for (size_t i = tid; i < xs_vec; i += n) ds[i] = ss[i];
+        uint32_t* di = reinterpret_cast<uint32_t*>(w + a.off_ids) + size_t(a.me) * ids_n;
+        for (size_t i = tid; i < ids_n; i += n) di[i] = a.ids[i];
+    }
+    __threadfence_system();
+    __syncthreads();
+    __shared__ uint32_t s_epoch;
+    if (tid == 0) {
+        s_epoch = a.epoch[a.flag_set] + 1;
+        a.epoch[a.flag_set] = s_epoch;
+        __threadfence_system();
+    }
+    __syncthreads();
+    if (tid < a.ranks) {
+        uint32_t* flag = reinterpret_cast<uint32_t*>(a.base[tid] + a.off_flags) + a.flag_set * 8 + a.me;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(s_epoch) : "memory");
+    }
+}
+
+// The signal alone (t = 0 rows): after the down kernel, whose stores into the other
+// ranks' windows are complete when this kernel starts.
+__global__ void peer_wait_kernel(const PeerWait pw) {
+    if (int(threadIdx.x) < pw.ranks) peer_wait(pw, threadIdx.x);
+}
+
+const char* ep_barrier(EpState& st, cudaStream_t stream) {
+    NcclApi& n = nccl();
+    if (!st.comm) return "no communicator";
+    uint32_t* buf = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&buf), size_t(st.size + 1) * 4) != cudaSuccess) return "cudaMalloc failed";
+    const bool ok = n.AllGather(buf + st.size, buf, 1, ncclUint32, st.comm, stream) == ncclSuccess &&
+                    cudaStreamSynchronize(stream) == cudaSuccess;
+    cudaFree(buf);
+    return ok ? nullptr : "barrier all-gather failed";
+}
+
+const char* ep_peer_enable(EpState& st, int hidden, int topk, int max_tokens) {
+    NcclApi& n = nccl();
+    EpPeer& p = st.peer;
+    if (!st.comm) return "call tc_ep_init first";
+    if (st.size > 8) return "the peer-memory exchange is for up to 8 ranks";
+    if (p.on) return "already enabled";
+    const size_t G = size_t(max_tokens) * st.size, nbp = (hidden / QK + 7) / 8 * 8;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    size_t o = 0;
+    p.off_xq = o, o = up(o + G * hidden);
+    p.off_xs = o, o = up(o + G * nbp * 4);
+    p.off_ids = o, o = up(o + G * topk * 4);
+    p.off_out = o, o = up(o + size_t(max_tokens) * topk * hidden * 4);
+    p.off_flags = o, o = up(o + 2 * 8 * 4);
+    p.bytes = o;
+    if (cudaMalloc(reinterpret_cast<void**>(&p.window), p.bytes) != cudaSuccess) return "cudaMalloc(window) failed";
+    cudaMemset(p.window, 0, p.bytes);
+    if (cudaMalloc(reinterpret_cast<void**>(&p.epoch), 8) != cudaSuccess) return "cudaMalloc failed";
+    cudaMemset(p.epoch, 0, 8);
+    cudaIpcMemHandle_t mine;
+    if (cudaIpcGetMemHandle(&mine, p.window) != cudaSuccess) return "cudaIpcGetMemHandle failed";
+    // Every rank's handle, through the communicator that already exists.
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    uint8_t* dev = nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&dev), hb * (st.size + 1)) != cudaSuccess) return "cudaMalloc failed";
+    cudaMemcpy(dev + hb * st.size, &mine, hb, cudaMemcpyHostToDevice);
+    std::vector<cudaIpcMemHandle_t> all(st.size);
+    const bool ok = n.AllGather(dev + hb * st.size, dev, hb, ncclInt8, st.comm, nullptr) == ncclSuccess &&
+                    cudaStreamSynchronize(nullptr) == cudaSuccess &&
+                    cudaMemcpy(all.data(), dev, hb * st.size, cudaMemcpyDeviceToHost) == cudaSuccess;
+    cudaFree(dev);
+    if (!ok) return "exchange of the window handles failed";
+    for (int r = 0; r < st.size; r++) {
+        if (r == st.rank) {
+            p.base[r] = p.window;
+            continue;
+        }
+        void* ptr = nullptr;
+        if (cudaIpcOpenMemHandle(&ptr, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+            return "cudaIpcOpenMemHandle failed (are the ranks' GPUs peers?)";
+        p.base[r] = static_cast<uint8_t*>(ptr);
+    }
+    p.tokens = max_tokens, p.hidden = hidden, p.topk = topk;
+    p.on = true;
+    st.uni.on = true;  // the dispatch over all ranks' tokens uses the same buffers
+    // Nobody stores into a window before every rank has mapped and cleared its own.
+    return ep_barrier(st, nullptr);
+}
+
+bool ep_peer_applies(const EpState& st, const MoeDims& d, int t) {
+    const EpPeer& p = st.peer;
+    return p.on && t <= p.tokens && d.hidden == p.hidden && d.topk == p.topk && ep_uniform_applies(st, d, t);
+}
+
+const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
+                            const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
+                            const MatrixDev& down, const uint8_t* down_tiled, const float* x,
+                            const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
+                            cudaStream_t stream, int* launches) {
+    EpUniform& u = st.uni;
+    EpPeer& p = st.peer;
+    const int R = st.size, G = R * t;
+    const int nbp = (d.hidden / QK + 7) / 8 * 8;
+    *launches += launch_route(d, router, bias, x, norm_w, eps, t, ws, stream);
+
+    PeerPlan plan{};
+    for (int r = 0; r < R; r++) plan.base[r] = p.base[r];
+    plan.off_xq = p.off_xq, plan.off_xs = p.off_xs, plan.off_ids = p.off_ids, plan.off_flags = p.off_flags;
+    plan.xq = ws.xq, plan.xs = ws.xs, plan.ids = ws.ids;
+    plan.t = t, plan.hidden = d.hidden, plan.nbp = nbp, plan.topk = d.topk, plan.me = st.rank, plan.ranks = R;
+    plan.flag_set = 0;
+    plan.epoch = p.epoch;
+    peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
+    PeerWait w1;
+    w1.flags = reinterpret_cast<const uint32_t*>(p.window + p.off_flags);
+    w1.epoch = p.epoch;
+    w1.ranks = R;
+    w1.status = ws.status;
+    peer_wait_kernel<<<1, 32, 0, stream>>>(w1);
+    *launches += 2;
+
+    Workspace gw = ws;  // the view over every rank's tokens, gathered in this rank's window
+    gw.ids = reinterpret_cast<uint32_t*>(p.window + p.off_ids);
+    gw.xq = reinterpret_cast<int8_t*>(p.window + p.off_xq);
+    gw.xs = reinterpret_cast<float*>(p.window + p.off_xs);
+    gw.xsum = u.xsum;
+    gw.counts = u.counts;
+    gw.offsets = u.offsets;
+    gw.perm = u.perm;
+    gw.pos = u.pos;
+    gw.slot_token = u.slot_token;
+    gw.active = u.active;
+    gw.block_hist = u.block_hist;
+    *launches += launch_dispatch(d, G, gw, stream);
+    if (gate_up.kind == 2) {
+        const size_t want_blocks = (size_t(G) * nbp + 7) / 8;
+        block_sums_kernel<<<unsigned(want_blocks < 148 * 16 ? want_blocks : 148 * 16), 256, 0, stream>>>(
+            gw.xq, gw.xs, size_t(G), d.hidden, nbp, u.xsum);
+        *launches += 1;
+    }
+    MoeDims ld = d;
+    ld.experts = b.local;
+    Workspace lw = gw;
+    lw.counts = u.counts + b.first;
+    lw.offsets = u.offsets + b.first;
+    lw.active = nullptr;
+    lw.hidden_f = u.hidden_f;
+    lw.out = nullptr;
+    float* outs[8] = {};
+    for (int r = 0; r < R; r++) outs[r] = reinterpret_cast<float*>(p.base[r] + p.off_out);
+    *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
+    *launches += launch_down_fast_rows(ld, down, down_tiled, lw, u.perm, sms, stream, outs, R,
+                                       uint32_t(t) * d.topk);
+    plan.t = 0;  // nothing to copy: the signal that this rank's outputs are in place
+    plan.flag_set = 1;
+    peer_scatter_signal_kernel<<<1, 32, 0, stream>>>(plan);
+    *launches += 1;
+
+    Workspace cw = ws;
+    cw.out = reinterpret_cast<float*>(p.window + p.off_out);
+    cw.pos = u.identity;
+    cw.combine_wait.flags = reinterpret_cast<const uint32_t*>(p.window + p.off_flags) + 8;
+    cw.combine_wait.epoch = p.epoch + 1;
+    cw.combine_wait.ranks = R;
+    cw.combine_wait.status = ws.status;
     *launches += launch_combine(d, t, cw, y, stream);
     return nullptr;
 }

@@ -27,12 +27,26 @@ struct EpUniform {
     std::vector<void*> allocs;
 };
 
+// Expert parallelism over peer memory (one NVSwitch node, up to 8 ranks): each rank
+// owns a window that the others map through CUDA IPC. Rows and expert outputs
+// are stored straight into the destination rank's window over NVLink and
+// announced with flags; no collective library call is made inside a block.
+struct EpPeer {
+    bool on = false;
+    int tokens = 0, hidden = 0, topk = 0;      // per-rank token capacity and row shape
+    uint8_t* window = nullptr;                 // this rank's
+    uint8_t* base[8] = {};                     // every rank's window as mapped here (base[rank] == window)
+    size_t off_xq = 0, off_xs = 0, off_ids = 0, off_out = 0, off_flags = 0, bytes = 0;
+    uint32_t* epoch = nullptr;                 // [2] this rank's signal counters (rows sent, outputs sent)
+};
+
 struct EpState {
     ncclComm* comm = nullptr;
     int rank = 0, size = 1;
     uint32_t* hist_host = nullptr;  // pinned [size * experts]
     size_t hist_host_elems = 0;
     EpUniform uni;
+    EpPeer peer;
 };
 
 struct EpLayerBuffers {
@@ -63,6 +77,15 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
                                const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                                const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
                                cudaStream_t stream, int* launches);
+// Collective: allocates this rank's window and maps every other rank's.
+const char* ep_peer_enable(EpState& st, int hidden, int topk, int max_tokens);
+bool ep_peer_applies(const EpState& st, const MoeDims& d, int t);
+const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
+                            const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
+                            const MatrixDev& down, const uint8_t* down_tiled, const float* x,
+                            const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
+                            cudaStream_t stream, int* launches);
+const char* ep_barrier(EpState& st, cudaStream_t stream);
 const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                        const MatrixDev& down, const uint8_t* down_tiled, const float* x,

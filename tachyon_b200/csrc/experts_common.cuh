@@ -10,6 +10,7 @@
 namespace tc {
 
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
+constexpr int MAX_PEERS = 8;  // ranks of a peer-memory exchange (one NVSwitch node)
 constexpr int MAGIC_I = 0x4B400000;  // bits of 12582912.0f = 1.5 * 2^23
 constexpr float MAGIC_F = 12582912.0f;
 
@@ -31,6 +32,10 @@ struct ExpertArgs {
     float* out;               // gate_up: hidden_f [slots, inter]; down: out [slots, hidden]
     int out_cols;
     const uint32_t* out_rows;  // when set: output row of sorted slot p (expert parallel: its row in the receive order)
+    // Expert parallelism over peer memory: when peer_out[0] is set, output row p (after
+    // out_rows) belongs to rank p / peer_rows and is stored into that rank's buffer.
+    float* peer_out[MAX_PEERS];
+    uint32_t peer_rows;
     int* status;
 };
 

@@ -642,8 +642,14 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                                     }
                                 } else {
                                     const int r0 = u * F_ROWS + g;
-                                    if (r0 < a.out_cols) a.out[p * a.out_cols + r0] = y0;
-                                    if (r0 + 8 < a.out_cols) a.out[p * a.out_cols + r0 + 8] = y1;
+                                    float* dst = a.out;
+                                    if (a.peer_out[0]) {  // the row's home rank's buffer, over NVLink
+                                        const uint32_t home = uint32_t(p) / a.peer_rows;
+                                        dst = a.peer_out[home];
+                                        p -= size_t(home) * a.peer_rows;
+                                    }
+                                    if (r0 < a.out_cols) dst[p * a.out_cols + r0] = y0;
+                                    if (r0 + 8 < a.out_cols) dst[p * a.out_cols + r0 + 8] = y1;
                                 }
                             }
                         }
@@ -850,10 +856,13 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled,
 // The down projection with each output row written to out_rows[slot] (expert
 // parallelism: the row's place in the receive order).
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, Workspace& ws,
-                          const uint32_t* out_rows, int sms, cudaStream_t stream) {
+                          const uint32_t* out_rows, int sms, cudaStream_t stream, float* const* peer_out,
+                          int ranks, uint32_t peer_rows) {
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;
     a.out_rows = out_rows;
+    for (int r = 0; r < ranks && r < MAX_PEERS; r++) a.peer_out[r] = peer_out[r];
+    a.peer_rows = peer_rows;
     const bool dense = !ws.active;  // a caller without a list of non-empty experts
     return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, dense, stream)
                        : launch_fast<2, false>(a, tiled, sms, dense, stream);

@@ -74,6 +74,18 @@ def init(ctx: Context, uid: bytes, rank: int, size: int, uniform_batch: bool = F
         ctx._check(ctx.lib.tc_ep_set_uniform_batch(ctx.handle, 1), "tc_ep_set_uniform_batch")
 
 
+def enable_peer_exchange(ctx: Context, hidden: int, experts_per_token: int, max_tokens: int):
+    """Collective, before the layers are created: blocks of up to max_tokens tokens per
+    rank exchange rows and expert outputs by NVLink stores into mapped peer windows
+    (no NCCL call inside a block). Implies uniform batches."""
+    ctx._check(ctx.lib.tc_ep_enable_peer_exchange(ctx.handle, hidden, experts_per_token, max_tokens),
+               "tc_ep_enable_peer_exchange")
+
+
+def barrier(ctx: Context):
+    ctx._check(ctx.lib.tc_ep_barrier(ctx.handle), "tc_ep_barrier")
+
+
 class EpMoeLayer(MoeLayer):
     """One MoE block with this rank's experts; forward()/block() exchange rows over NCCL."""
 

@@ -28,7 +28,8 @@ def _device_count():
     return n.value if rt.cudaGetDeviceCount(ctypes.byref(n)) == 0 else 0
 
 
-def _rank_main(rank, size, tmp, fmt, tokens, uniform=False):
+def _rank_main(rank, size, tmp, fmt, tokens, mode="alltoallv"):
+    uniform = mode != "alltoallv"
     sys.path.insert(0, ROOT)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     from tachyon_b200 import cuda, ep, workloads
@@ -48,6 +49,8 @@ def _rank_main(rank, size, tmp, fmt, tokens, uniform=False):
         uid = open(uid_path, "rb").read()
     ep.init(ctx, uid, rank, size, uniform_batch=uniform)
     shape = workloads.MoeShape("ep", 512, 10, 4, 128, fmt=fmt)
+    if mode == "peer":
+        ep.enable_peer_exchange(ctx, shape.hidden, shape.topk, tokens // size)
     lw = workloads.layer_weights(shape, seed=6)
     x_all = workloads.hidden_states(shape, tokens, seed=7)
     y0_all = workloads.hidden_states(shape, tokens, seed=8)
@@ -61,6 +64,7 @@ def _rank_main(rank, size, tmp, fmt, tokens, uniform=False):
     gu, dn = ep.local_experts(lw.gate_up, lw.down, shape.experts, rank, size)
     t0, tn = ep.shard_range(tokens, rank, size)
     layer = ep.EpMoeLayer(ctx, lw.router, gu, dn, shape.experts, shape.topk, max(tn, 1))
+    ep.barrier(ctx)  # ranks reach their first block together (the peer exchange's waits are bounded)
     for _ in range(2):  # twice: buffers are reused
         xs, ys = ctx.to_device(x_all[t0:t0 + tn]), ctx.to_device(y0_all[t0:t0 + tn])
         layer.forward(xs, ys)
@@ -112,5 +116,22 @@ def test_fixed_size_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_path
 
     build.build()
     size = 4 if n >= 4 else 2
-    mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens, True), nprocs=size, join=True,
+    mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens, "fixed"), nprocs=size, join=True,
+                       start_method="spawn")
+
+
+@pytest.mark.parametrize("fmt,tokens", [("q8", 64), ("q4", 36), ("q8", 1024)])
+def test_peer_memory_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_path, fmt, tokens):
+    """Rows and expert outputs stored straight into the other ranks' windows over NVLink,
+    announced with flags; no collective call inside the block."""
+    n = _device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+
+    from tachyon_b200 import build
+
+    build.build()
+    size = 4 if n >= 4 else 2
+    mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens, "peer"), nprocs=size, join=True,
                        start_method="spawn")
