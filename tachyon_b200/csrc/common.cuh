@@ -43,6 +43,18 @@ struct PeerWait {
     int* status = nullptr;
 };
 
+// Sending this rank's rows to every rank's window, then announcing it (or, with t = 0,
+// the announcement alone).
+struct PeerPlan {
+    uint8_t* base[8] = {};  // every rank's window as mapped here
+    size_t off_xq = 0, off_xs = 0, off_ids = 0, off_flags = 0;
+    const int8_t* xq = nullptr;
+    const float* xs = nullptr;
+    const uint32_t* ids = nullptr;
+    int t = 0, hidden = 0, nbp = 0, topk = 0, me = 0, ranks = 0, flag_set = 0;
+    uint32_t* epoch = nullptr;  // this rank's counters, one per flag set
+};
+
 struct Workspace {
     int max_tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;
     float* logits = nullptr;      // [T, E]
@@ -66,6 +78,8 @@ struct Workspace {
     int* status = nullptr;        // device status word
     int* ticket = nullptr;        // arrival counter of the router CTAs (zero between launches)
     PeerWait combine_wait;        // set for the peer-memory exchange only
+    PeerWait dispatch_wait;       // the same, before the dispatch over every rank's tokens
+    PeerPlan route_scatter;       // the same: rows sent by the router kernel's last CTA (ranks > 0)
 };
 
 struct MoeDims {
@@ -133,7 +147,9 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& down, const uint8_t* til
 // (peer_out: when given, `ranks` buffers; output row p goes to rank p / peer_rows.)
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t* tiled, Workspace& ws,
                           const uint32_t* out_rows, int sms, cudaStream_t stream,
-                          float* const* peer_out = nullptr, int ranks = 0, uint32_t peer_rows = 0);
+                          float* const* peer_out = nullptr, int ranks = 0, uint32_t peer_rows = 0,
+                          uint32_t* const* peer_flag = nullptr, uint32_t* peer_epoch = nullptr,
+                          uint32_t* peer_ticket = nullptr);
 
 // ---- overlapping consecutive kernels of a block (programmatic dependent launch)
 //
@@ -210,6 +226,36 @@ __device__ __forceinline__ void peer_wait(const PeerWait& pw, int r) {
         __nanosleep(i < 64 ? 32 : 512);
     }
     atomicExch(pw.status, ERR_PEER_WAIT_TIMEOUT);
+}
+
+// One CTA: copies this rank's rows into every window and release-stores the next value
+// of this rank's counter into every rank's flag word. Writes of all the CTA's threads
+// are ordered before the flags: CTA barrier, then a cumulative system-scope release.
+__device__ __forceinline__ void peer_scatter_signal(const PeerPlan& a, uint32_t* s_epoch) {
+    const int tid = threadIdx.x, n = blockDim.x;
+    const size_t xq_vec = size_t(a.t) * a.hidden / 16, xs_vec = size_t(a.t) * a.nbp / 4;
+    const size_t ids_n = size_t(a.t) * a.topk;
+    for (int r = 0; r < a.ranks; r++) {
+        uint8_t* w = a.base[r];
+        uint4* dq = reinterpret_cast<uint4*>(w + a.off_xq + size_t(a.me) * a.t * a.hidden);
+        const uint4* sq = reinterpret_cast<const uint4*>(a.xq);
+        for (size_t i = tid; i < xq_vec; i += n) dq[i] = sq[i];
+        uint4* ds = reinterpret_cast<uint4*>(w + a.off_xs + size_t(a.me) * a.t * a.nbp * 4);
+        const uint4* ss = reinterpret_cast<const uint4*>(a.xs);
+        for (size_t i = tid; i < xs_vec; i += n) ds[i] = ss[i];
+        uint32_t* di = reinterpret_cast<uint32_t*>(w + a.off_ids) + size_t(a.me) * ids_n;
+        for (size_t i = tid; i < ids_n; i += n) di[i] = a.ids[i];
+    }
+    __syncthreads();
+    if (tid == 0) {
+        *s_epoch = a.epoch[a.flag_set] + 1;
+        a.epoch[a.flag_set] = *s_epoch;
+    }
+    __syncthreads();
+    if (tid < a.ranks) {
+        uint32_t* flag = reinterpret_cast<uint32_t*>(a.base[tid] + a.off_flags) + a.flag_set * 8 + a.me;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(*s_epoch) : "memory");
+    }
 }
 #endif
 

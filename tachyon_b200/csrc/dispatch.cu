@@ -26,17 +26,28 @@ __global__ void __launch_bounds__(DISPATCH_THREADS)
 dispatch_small_kernel(const uint32_t* __restrict__ ids, int t, int experts, int topk,
                       uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets,
                       uint32_t* __restrict__ perm, uint32_t* __restrict__ pos,
-                      uint32_t* __restrict__ slot_token, int* __restrict__ active) {
+                      uint32_t* __restrict__ slot_token, int* __restrict__ active, const PeerWait pw) {
     __shared__ DispatchSmem sm;
+    KTL_BEGIN(7)
+    if (pw.flags) {  // the ids come from other ranks: all of them have signalled this block
+        if (int(threadIdx.x) < pw.ranks) peer_wait(pw, threadIdx.x);
+        __syncthreads();
+    }
+    KTL_MARK(2)
     dispatch_small_body(sm, ids, t, experts, topk, counts, offsets, perm, pos, slot_token, active);
+    KTL_MARK(3)
 }
 
 // Large batches, pass 1: each CTA's histogram of its DISPATCH_THREADS tokens.
 __global__ void __launch_bounds__(DISPATCH_THREADS)
 dispatch_count_kernel(const uint32_t* __restrict__ ids, int t, int experts, int topk,
-                      uint32_t* __restrict__ block_hist) {
+                      uint32_t* __restrict__ block_hist, const PeerWait pw) {
     __shared__ uint32_t bits[MAX_EXPERTS][DISPATCH_WARPS];
     const int tid = threadIdx.x;
+    if (pw.flags) {
+        if (tid < pw.ranks) peer_wait(pw, tid);
+        __syncthreads();
+    }
     mark_picks(bits, ids, blockIdx.x * DISPATCH_THREADS + tid, t, experts, topk);
     for (int e = tid; e < experts; e += DISPATCH_THREADS)
         block_hist[size_t(blockIdx.x) * experts + e] = row_count(bits, e);
@@ -97,12 +108,13 @@ int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream)
     if (t <= DISPATCH_THREADS) {
         dispatch_small_kernel<<<1, DISPATCH_THREADS, 0, stream>>>(ws.ids, t, d.experts, d.topk,
                                                                   ws.counts, ws.offsets, ws.perm,
-                                                                  ws.pos, ws.slot_token, ws.active);
+                                                                  ws.pos, ws.slot_token, ws.active,
+                                                                  ws.dispatch_wait);
         return 1;
     }
     const int blocks = (t + DISPATCH_THREADS - 1) / DISPATCH_THREADS;
     dispatch_count_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ws.ids, t, d.experts, d.topk,
-                                                                   ws.block_hist);
+                                                                   ws.block_hist, ws.dispatch_wait);
     dispatch_scan_kernel<<<1, DISPATCH_THREADS, 0, stream>>>(ws.block_hist, blocks, d.experts,
                                                              ws.counts, ws.offsets, ws.active);
     dispatch_permute_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(
@@ -159,7 +171,7 @@ const char* dispatch_static(int device, const uint32_t* ids, int t, int experts,
     }
     uint32_t* block_hist = g_static_block_hist_dev[device];
     const int blocks = (t + DISPATCH_THREADS - 1) / DISPATCH_THREADS;
-    dispatch_count_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ids, t, experts, topk, block_hist);
+    dispatch_count_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ids, t, experts, topk, block_hist, PeerWait{});
     dispatch_scan_kernel<<<1, DISPATCH_THREADS, 0, stream>>>(block_hist, blocks, experts, counts, offsets, active);
     dispatch_permute_kernel<<<blocks, DISPATCH_THREADS, 0, stream>>>(ids, t, experts, topk, block_hist, offsets,
                                                                      perm, pos, slot_token);
@@ -167,3 +179,5 @@ const char* dispatch_static(int device, const uint32_t* ids, int t, int experts,
 }
 
 }  // namespace tc
+
+KTL_DUMP(tc_debug_ktl_dispatch)

@@ -367,50 +367,22 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
 // Ordering across blocks needs no second buffer: a rank can only reach step 2 of block
 // n+1 after its combine of block n, which waited for every rank's step 5 of block n,
 // i.e. for every reader of the rows of block n.
-struct PeerPlan {
-    uint8_t* base[8];
-    size_t off_xq, off_xs, off_ids, off_flags;
-    const int8_t* xq;
-    const float* xs;
-    const uint32_t* ids;
-    int t, hidden, nbp, topk, me, ranks, flag_set;
-    uint32_t* epoch;
-};
-
 __global__ void __launch_bounds__(1024) peer_scatter_signal_kernel(const PeerPlan a) {
-    const int tid = threadIdx.x, n = blockDim.x;
-    const size_t xq_vec = size_t(a.t) * a.hidden / 16, xs_vec = size_t(a.t) * a.nbp / 4;
-    const size_t ids_n = size_t(a.t) * a.topk;
-    for (int r = 0; r < a.ranks; r++) {
-        uint8_t* w = a.base[r];
-        uint4* dq = reinterpret_cast<uint4*>(w + a.off_xq + size_t(a.me) * a.t * a.hidden);
-        const uint4* sq = reinterpret_cast<const uint4*>(a.xq);
-        for (size_t i = tid; i < xq_vec; i += n) dq[i] = sq[i];
-        uint4* ds = reinterpret_cast<uint4*>(w + a.off_xs + size_t(a.me) * a.t * a.nbp * 4);
-        const uint4* ss = reinterpret_cast<const uint4*>(a.xs);
-        for (size_t i = tid; i < xs_vec; i += n) ds[i] = ss[i];
-        uint32_t* di = reinterpret_cast<uint32_t*>(w + a.off_ids) + size_t(a.me) * ids_n;
-        for (size_t i = tid; i < ids_n; i += n) di[i] = a.ids[i];
-    }
-    __threadfence_system();
-    __syncthreads();
+    KTL_BEGIN(4 + a.flag_set)
+    KTL_MARK(2)
     __shared__ uint32_t s_epoch;
-    if (tid == 0) {
-        s_epoch = a.epoch[a.flag_set] + 1;
-        a.epoch[a.flag_set] = s_epoch;
-        __threadfence_system();
-    }
-    __syncthreads();
-    if (tid < a.ranks) {
-        uint32_t* flag = reinterpret_cast<uint32_t*>(a.base[tid] + a.off_flags) + a.flag_set * 8 + a.me;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(s_epoch) : "memory");
-    }
+    peer_scatter_signal(a, &s_epoch);
+    KTL_MARK(3)
 }
 
 // The signal alone (t = 0 rows): after the down kernel, whose stores into the other
 // ranks' windows are complete when this kernel starts.
 __global__ void peer_wait_kernel(const PeerWait pw) {
+    KTL_BEGIN(6)
+    KTL_MARK(2)
     if (int(threadIdx.x) < pw.ranks) peer_wait(pw, threadIdx.x);
+    __syncwarp();
+    KTL_MARK(3)
 }
 
 const char* ep_barrier(EpState& st, cudaStream_t stream) {
@@ -441,8 +413,8 @@ const char* ep_peer_enable(EpState& st, int hidden, int topk, int max_tokens) {
     p.bytes = o;
     if (cudaMalloc(reinterpret_cast<void**>(&p.window), p.bytes) != cudaSuccess) return "cudaMalloc(window) failed";
     cudaMemset(p.window, 0, p.bytes);
-    if (cudaMalloc(reinterpret_cast<void**>(&p.epoch), 8) != cudaSuccess) return "cudaMalloc failed";
-    cudaMemset(p.epoch, 0, 8);
+    if (cudaMalloc(reinterpret_cast<void**>(&p.epoch), 16) != cudaSuccess) return "cudaMalloc failed";
+    cudaMemset(p.epoch, 0, 16);
     cudaIpcMemHandle_t mine;
     if (cudaIpcGetMemHandle(&mine, p.window) != cudaSuccess) return "cudaIpcGetMemHandle failed";
     // Every rank's handle, through the communicator that already exists.
@@ -487,8 +459,6 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     EpPeer& p = st.peer;
     const int R = st.size, G = R * t;
     const int nbp = (d.hidden / QK + 7) / 8 * 8;
-    *launches += launch_route(d, router, bias, x, norm_w, eps, t, ws, stream);
-
     PeerPlan plan{};
     for (int r = 0; r < R; r++) plan.base[r] = p.base[r];
     plan.off_xq = p.off_xq, plan.off_xs = p.off_xs, plan.off_ids = p.off_ids, plan.off_flags = p.off_flags;
@@ -496,14 +466,13 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     plan.t = t, plan.hidden = d.hidden, plan.nbp = nbp, plan.topk = d.topk, plan.me = st.rank, plan.ranks = R;
     plan.flag_set = 0;
     plan.epoch = p.epoch;
-    peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
-    PeerWait w1;
-    w1.flags = reinterpret_cast<const uint32_t*>(p.window + p.off_flags);
-    w1.epoch = p.epoch;
-    w1.ranks = R;
-    w1.status = ws.status;
-    peer_wait_kernel<<<1, 32, 0, stream>>>(w1);
-    *launches += 2;
+    Workspace rw = ws;
+    rw.route_scatter = plan;  // batches of up to one CTA's worth of tokens: sent by the router's last CTA
+    *launches += launch_route(d, router, bias, x, norm_w, eps, t, rw, stream);
+    if (t > 256) {  // larger ones: the router ran its own multi-CTA dispatch; send with a kernel
+        peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
+        *launches += 1;
+    }
 
     Workspace gw = ws;  // the view over every rank's tokens, gathered in this rank's window
     gw.ids = reinterpret_cast<uint32_t*>(p.window + p.off_ids);
@@ -517,6 +486,10 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     gw.slot_token = u.slot_token;
     gw.active = u.active;
     gw.block_hist = u.block_hist;
+    gw.dispatch_wait.flags = reinterpret_cast<const uint32_t*>(p.window + p.off_flags);
+    gw.dispatch_wait.epoch = p.epoch;
+    gw.dispatch_wait.ranks = R;
+    gw.dispatch_wait.status = ws.status;
     *launches += launch_dispatch(d, G, gw, stream);
     if (gate_up.kind == 2) {
         const size_t want_blocks = (size_t(G) * nbp + 7) / 8;
@@ -535,12 +508,10 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     float* outs[8] = {};
     for (int r = 0; r < R; r++) outs[r] = reinterpret_cast<float*>(p.base[r] + p.off_out);
     *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
+    uint32_t* flags2[8] = {};
+    for (int r = 0; r < R; r++) flags2[r] = reinterpret_cast<uint32_t*>(p.base[r] + p.off_flags) + 8 + st.rank;
     *launches += launch_down_fast_rows(ld, down, down_tiled, lw, u.perm, sms, stream, outs, R,
-                                       uint32_t(t) * d.topk);
-    plan.t = 0;  // nothing to copy: the signal that this rank's outputs are in place
-    plan.flag_set = 1;
-    peer_scatter_signal_kernel<<<1, 32, 0, stream>>>(plan);
-    *launches += 1;
+                                       uint32_t(t) * d.topk, flags2, p.epoch + 1, p.epoch + 2);
 
     Workspace cw = ws;
     cw.out = reinterpret_cast<float*>(p.window + p.off_out);
@@ -650,3 +621,5 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
 }
 
 }  // namespace tc
+
+KTL_DUMP(tc_debug_ktl_ep)

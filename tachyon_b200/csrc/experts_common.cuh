@@ -36,6 +36,12 @@ struct ExpertArgs {
     // out_rows) belongs to rank p / peer_rows and is stored into that rank's buffer.
     float* peer_out[MAX_PEERS];
     uint32_t peer_rows;
+    // ... and the last CTA to finish announces this rank's outputs: *peer_epoch + 1 into
+    // peer_flag[r] (this rank's flag word in rank r's window) for every rank.
+    uint32_t* peer_flag[MAX_PEERS];
+    uint32_t* peer_epoch;
+    uint32_t* peer_ticket;
+    int peer_ranks;
     int* status;
 };
 

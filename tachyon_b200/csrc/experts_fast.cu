@@ -684,6 +684,23 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         g_timeline[blockIdx.x][warp][11] = tl_epi;
     }
 #endif
+    if (!GATE_UP && a.peer_ranks) {
+        // Rows went into other ranks' windows. Order this CTA's stores before its ticket
+        // (CTA barrier, then a cumulative system-scope fence); the last CTA to arrive then
+        // release-stores the next value of this rank's counter into every rank's flag.
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence_system();
+            if (atomicAdd(a.peer_ticket, 1u) == gridDim.x - 1) {
+                *a.peer_ticket = 0;  // ready for the next launch
+                __threadfence_system();
+                const uint32_t e = *a.peer_epoch + 1;
+                *a.peer_epoch = e;
+                for (int r = 0; r < a.peer_ranks; r++)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.peer_flag[r]), "r"(e) : "memory");
+            }
+        }
+    }
     if (!ok) {
         if (threadIdx.x == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
         // Give copies already in flight a bounded chance to land before the
@@ -857,12 +874,19 @@ int launch_down_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled,
 // parallelism: the row's place in the receive order).
 int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, Workspace& ws,
                           const uint32_t* out_rows, int sms, cudaStream_t stream, float* const* peer_out,
-                          int ranks, uint32_t peer_rows) {
+                          int ranks, uint32_t peer_rows, uint32_t* const* peer_flag, uint32_t* peer_epoch,
+                          uint32_t* peer_ticket) {
     ExpertArgs a = down_args(d, m, ws);
     a.xf = ws.hidden_f;
     a.out_rows = out_rows;
     for (int r = 0; r < ranks && r < MAX_PEERS; r++) a.peer_out[r] = peer_out[r];
     a.peer_rows = peer_rows;
+    if (peer_flag) {
+        for (int r = 0; r < ranks && r < MAX_PEERS; r++) a.peer_flag[r] = peer_flag[r];
+        a.peer_epoch = peer_epoch;
+        a.peer_ticket = peer_ticket;
+        a.peer_ranks = ranks;
+    }
     const bool dense = !ws.active;  // a caller without a list of non-empty experts
     return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, dense, stream)
                        : launch_fast<2, false>(a, tiled, sms, dense, stream);

@@ -94,6 +94,7 @@ struct RouteArgs {
     int* status;
     uint32_t *counts, *offsets, *perm, *pos, *slot_token;
     int* active;
+    PeerPlan scatter;      // ranks > 0: the last CTA sends the rows to every rank instead of dispatching
 };
 
 #ifdef TC_TIMELINE
@@ -324,9 +325,16 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         RTL(5);
         if (s_last) {
             __threadfence();
-            DispatchSmem& sm = *reinterpret_cast<DispatchSmem*>(smem);
-            dispatch_small_body(sm, a.ids, a.t, experts, topk, a.counts, a.offsets, a.perm, a.pos,
-                                a.slot_token, a.active);
+            if (a.scatter.ranks) {
+                // Expert parallelism over peer memory: the dispatch runs over every rank's
+                // tokens, after this CTA has stored this rank's rows into every window.
+                __shared__ uint32_t s_epoch;
+                peer_scatter_signal(a.scatter, &s_epoch);
+            } else {
+                DispatchSmem& sm = *reinterpret_cast<DispatchSmem*>(smem);
+                dispatch_small_body(sm, a.ids, a.t, experts, topk, a.counts, a.offsets, a.perm, a.pos,
+                                    a.slot_token, a.active);
+            }
             if (tid == 0) *a.ticket = 0;  // ready for the next launch on this stream
         }
     }
@@ -388,6 +396,7 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.pos = ws.pos;
     a.slot_token = ws.slot_token;
     a.active = ws.active;
+    if (a.fuse_dispatch) a.scatter = ws.route_scatter;
     size_t smem = (size_t(d.hidden + d.experts) * sizeof(float) + 127) / 128 * 128;
     const size_t staged = smem + size_t(d.experts) * (2 * size_t(d.hidden) + 32);
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
