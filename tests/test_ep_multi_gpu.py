@@ -135,3 +135,20 @@ def test_peer_memory_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_pat
     size = 4 if n >= 4 else 2
     mp.start_processes(_rank_main, args=(size, str(tmp_path), fmt, tokens, "peer"), nprocs=size, join=True,
                        start_method="spawn")
+
+
+@pytest.mark.parametrize("mode", ["alltoallv", "fixed", "peer"])
+@pytest.mark.parametrize("fmt,tokens", [("q8", 40), ("q4", 37), ("q8", 300)])
+def test_one_rank_runs_every_exchange(tmp_path, fmt, tokens, mode):
+    """A communicator of one rank on one GPU: the same kernels and buffers as with
+    several ranks (the window is the rank's own), so the three exchanges are covered
+    where only one GPU is present."""
+    if _device_count() < 1:
+        pytest.skip("needs a GPU")
+    import torch.multiprocessing as mp
+
+    from tachyon_b200 import build
+
+    build.build()
+    mp.start_processes(_rank_main, args=(1, str(tmp_path), fmt, tokens, mode), nprocs=1, join=True,
+                       start_method="spawn")
