@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         const int hi_d = int((long long)(blockIdx.x + 1) * total_d / gridDim.x);
         const int a0 = lo_d + warp;  // the first expert of the range starts the rotation at warp 0
         if (a0 < min(hi_d, (lo_d / upe + 1) * upe)) {
-            npre = min(STAGES - 1, nchunks);
+            npre = min(STAGES, nchunks);  // the whole ring: the walk's first fill then waits for a free stage
             if (lane == 0) {
                 for (int s = 0; s < npre; s++) {
                     mbar_expect_tx(bars + s, R::BYTES);
@@ -575,7 +575,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
 #ifdef TC_TIMELINE
                 const long long tf0 = clock64();
 #endif
-                fill_next();
+                if (fills - takes < uint32_t(STAGES)) fill_next();
 #ifdef TC_TIMELINE
                 __syncwarp();
                 tl_fill += clock64() - tf0;

@@ -281,7 +281,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // ---- 8-bit quantization of the row, a warp per 32-block.
     const int nb = hidden / QK;
     const int padded = (nb + SUPER - 1) / SUPER * SUPER;
-    for (int b = warp; b < padded; b += ROUTE_THREADS / 32) {
+    // Warps 1.. take the blocks while warp 0 is still ranking the logits above (the two do
+    // not depend on each other); a single-warp launch would do both in turn.
+    constexpr int QWARPS = ROUTE_THREADS / 32 - 1;
+    for (int b = warp - 1; warp > 0 && b < padded; b += QWARPS) {
         if (b >= nb) {  // zero padding up to whole super-blocks
             if (lane == 0) {
                 a.xs[size_t(token) * padded + b] = 0.0f;
