@@ -55,6 +55,17 @@ struct PeerPlan {
     uint32_t* epoch = nullptr;  // this rank's counters, one per flag set
 };
 
+// The sorted slots cut into runs of at most 16 slots of one expert, for callers
+// whose experts see several 16-token segments each (expert parallelism): the
+// expert kernels then spread (run, unit) pairs evenly over CTAs and warps instead
+// of giving all segments of an expert's unit to one warp.
+struct RunList {
+    int* expert = nullptr;        // [runs] expert of the run (index into the matrices held)
+    uint32_t* count = nullptr;    // [runs] 1..16
+    uint32_t* offset = nullptr;   // [runs] first sorted slot
+    int* n = nullptr;             // number of runs
+};
+
 struct Workspace {
     int max_tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;
     float* logits = nullptr;      // [T, E]
@@ -77,6 +88,7 @@ struct Workspace {
     float* out = nullptr;         // [T*k, H] expert outputs, sorted order
     int* status = nullptr;        // device status word
     int* ticket = nullptr;        // arrival counter of the router CTAs (zero between launches)
+    RunList runs;                 // when set: the expert kernels walk these instead of counts/offsets/active
     PeerWait combine_wait;        // set for the peer-memory exchange only
     PeerWait dispatch_wait;       // the same, before the dispatch over every rank's tokens
     PeerPlan route_scatter;       // the same: rows sent by the router kernel's last CTA (ranks > 0)
@@ -150,6 +162,10 @@ int launch_down_fast_rows(const MoeDims& d, const MatrixDev& down, const uint8_t
                           float* const* peer_out = nullptr, int ranks = 0, uint32_t peer_rows = 0,
                           uint32_t* const* peer_flag = nullptr, uint32_t* peer_epoch = nullptr,
                           uint32_t* peer_ticket = nullptr);
+
+// Fills `runs` from counts/offsets of `experts` experts (one CTA).
+int launch_build_runs(const uint32_t* counts, const uint32_t* offsets, int experts, const RunList& runs,
+                      cudaStream_t stream);
 
 // ---- overlapping consecutive kernels of a block (programmatic dependent launch)
 //

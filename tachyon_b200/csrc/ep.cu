@@ -274,7 +274,9 @@ bool ep_uniform_reserve(EpState& st, const MoeDims& d, int max_tokens) {
                     get(u.ids, slots) && get(u.counts, size_t(E) + 1) && get(u.offsets, size_t(E) + 2) &&
                     get(u.perm, slots) && get(u.pos, slots) && get(u.slot_token, slots) &&
                     get(u.active, size_t(E) + 2) && get(u.block_hist, size_t((T + 255) / 256) * E) &&
-                    get(u.hidden_f, slots * I) && get(u.big, slots * H) && get(u.identity, slots);
+                    get(u.hidden_f, slots * I) && get(u.big, slots * H) && get(u.identity, slots) &&
+                    get(u.runs.expert, size_t(E) + slots / 16 + 2) && get(u.runs.count, size_t(E) + slots / 16 + 2) &&
+                    get(u.runs.offset, size_t(E) + slots / 16 + 2) && get(u.runs.n, size_t(2));
     if (!ok) {
         for (void* p : u.allocs) cudaFree(p);
         u.allocs.clear();
@@ -335,7 +337,9 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
     Workspace lw = gw;  // this rank's experts: a contiguous run of the sorted slots
     lw.counts = u.counts + b.first;
     lw.offsets = u.offsets + b.first;
-    lw.active = nullptr;  // no list of this run's non-empty experts: the kernels walk them all
+    lw.active = nullptr;
+    lw.runs = u.runs;  // experts here see several 16-token segments each: spread them over the CTAs
+    *launches += launch_build_runs(lw.counts, lw.offsets, b.local, u.runs, stream);
     lw.hidden_f = u.hidden_f;
     lw.out = u.big;
     *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
@@ -503,6 +507,8 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     lw.counts = u.counts + b.first;
     lw.offsets = u.offsets + b.first;
     lw.active = nullptr;
+    lw.runs = u.runs;  // experts here see several 16-token segments each: spread them over the CTAs
+    *launches += launch_build_runs(lw.counts, lw.offsets, b.local, u.runs, stream);
     lw.hidden_f = u.hidden_f;
     lw.out = nullptr;
     float* outs[8] = {};

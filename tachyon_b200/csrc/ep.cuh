@@ -24,6 +24,7 @@ struct EpUniform {
     uint32_t* block_hist = nullptr;
     float *hidden_f = nullptr, *big = nullptr;  // [G*k, I]; [G*k, H]
     uint32_t* identity = nullptr;               // [T*k] = 0, 1, 2, ...
+    RunList runs;                               // this rank's slots in runs of up to 16 per expert
     std::vector<void*> allocs;
 };
 

@@ -25,6 +25,7 @@ struct ExpertArgs {
     const uint32_t* offsets;
     const uint32_t* slot_token;  // gate_up: sorted slot -> token (null for down: rows are slots)
     const int* active;        // experts with tokens, ascending; active[experts] = their number
+    RunList runs;             // when runs.expert is set, walked instead of the three lists above
     const int8_t* xq;         // activations [rows, cols]
     const float* xs;          // scales [rows, pad8(cols/32)]
     const float* xsum;        // [rows, pad8(cols/32)] (4-bit offsets)
@@ -58,6 +59,7 @@ inline ExpertArgs gate_up_args(const MoeDims& d, const MatrixDev& m, const Works
     a.offsets = ws.offsets;
     a.slot_token = ws.slot_token;
     a.active = ws.active;
+    a.runs = ws.runs;
     a.xq = ws.xq;
     a.xs = ws.xs;
     a.xsum = ws.xsum;
@@ -80,6 +82,7 @@ inline ExpertArgs down_args(const MoeDims& d, const MatrixDev& m, const Workspac
     a.offsets = ws.offsets;
     a.slot_token = nullptr;
     a.active = ws.active;
+    a.runs = ws.runs;
     a.xq = ws.hq;
     a.xs = ws.hs;
     a.xsum = ws.hsum;

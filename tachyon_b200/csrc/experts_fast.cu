@@ -170,8 +170,13 @@ struct FWalker {
                 cur.valid = false;
                 return;
             }
-            cur.e = f.dense ? cur.ai : int(f.e.active[cur.ai]);
-            cur.m = f.e.counts[cur.e];
+            if (f.e.runs.expert) {  // ai counts runs of up to F_TOK slots
+                cur.e = f.e.runs.expert[cur.ai];
+                cur.m = f.e.runs.count[cur.ai];
+            } else {
+                cur.e = f.dense ? cur.ai : int(f.e.active[cur.ai]);
+                cur.m = f.e.counts[cur.e];
+            }
             if (f.dense && cur.m == 0) cur.m = 1;  // an expert nobody picked is walked once, with no tokens
             const int seg_lo = max(lo, cur.ai * upe);
             cur.seg_hi = min(hi, (cur.ai + 1) * upe);
@@ -392,7 +397,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
     }
     grid_dependency_wait();  // everything below reads what earlier kernels wrote
     KTL_MARK(2)
-    const int total = (f.dense ? a.experts : int(a.active[a.experts])) * upe;
+    const int total = (a.runs.expert ? *a.runs.n : f.dense ? a.experts : int(a.active[a.experts])) * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
 
@@ -448,10 +453,16 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                 sgm.valid = false;
                 return;
             }
-            sgm.e = f.dense ? sgm.ai : int(a.active[sgm.ai]);
-            sgm.m = a.counts[sgm.e];
+            if (a.runs.expert) {
+                sgm.e = a.runs.expert[sgm.ai];
+                sgm.m = a.runs.count[sgm.ai];
+                sgm.base = a.runs.offset[sgm.ai];
+            } else {
+                sgm.e = f.dense ? sgm.ai : int(a.active[sgm.ai]);
+                sgm.m = a.counts[sgm.e];
+                sgm.base = a.offsets[sgm.e];
+            }
             sgm.mw = f.dense && sgm.m == 0 ? 1u : sgm.m;
-            sgm.base = a.offsets[sgm.e];
             sgm.sg0 = 0;
         }
         sgm.ntok = max(0, min(F_TOK, int(sgm.m) - sgm.sg0));
@@ -793,7 +804,7 @@ int launch_fast(const ExpertArgs& e, const uint8_t* tiled, int sms, bool dense, 
     int nwarps = 0;
     if (!pick_config<KIND>(e.cols, f.nbp, nwarps, f.stages)) return -1;
     const int total_units = e.experts * e.units_per_expert;
-    int grid = min(sms, total_units);
+    int grid = e.runs.expert ? sms : min(sms, total_units);  // (runs: at least as many tasks as units)
     if (grid < 1) grid = 1;
     const Layout<KIND> L(nwarps, f.stages, e.cols, f.nbp);
     launch_overlapped(expert_fast_kernel<KIND, GATE_UP>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, f);
@@ -852,11 +863,44 @@ void tile_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, uint8_t* t
     }
 }
 
+namespace {
+// One CTA: expert e with m slots becomes ceil(m / F_TOK) runs.
+__global__ void build_runs_kernel(const uint32_t* __restrict__ counts, const uint32_t* __restrict__ offsets,
+                                  int experts, RunList runs) {
+    __shared__ int s_first[MAX_EXPERTS + 1];
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < experts; e++) {
+            s_first[e] = run;
+            run += (int(counts[e]) + F_TOK - 1) / F_TOK;
+        }
+        s_first[experts] = run;
+        *runs.n = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+        const uint32_t m = counts[e], base = offsets[e];
+        for (uint32_t i = 0; i * F_TOK < m; i++) {
+            const int r = s_first[e] + int(i);
+            runs.expert[r] = e;
+            runs.count[r] = min(uint32_t(F_TOK), m - i * F_TOK);
+            runs.offset[r] = base + i * F_TOK;
+        }
+    }
+}
+}  // namespace
+
+int launch_build_runs(const uint32_t* counts, const uint32_t* offsets, int experts, const RunList& runs,
+                      cudaStream_t stream) {
+    build_runs_kernel<<<1, 256, 0, stream>>>(counts, offsets, experts, runs);
+    return 1;
+}
+
 int launch_gate_up_fast(const MoeDims& d, const MatrixDev& m, const uint8_t* tiled, int t, Workspace& ws,
                         int sms, cudaStream_t stream) {
     (void)t;
     const ExpertArgs a = gate_up_args(d, m, ws);
-    const bool dense = dense_walk(d, t) || !ws.active;
+    const bool dense = !ws.runs.expert && (dense_walk(d, t) || !ws.active);
     return m.kind == 1 ? launch_fast<1, true>(a, tiled, sms, dense, stream)
                        : launch_fast<2, true>(a, tiled, sms, dense, stream);
 }
@@ -887,7 +931,7 @@ int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* t
         a.peer_ticket = peer_ticket;
         a.peer_ranks = ranks;
     }
-    const bool dense = !ws.active;  // a caller without a list of non-empty experts
+    const bool dense = !ws.runs.expert && !ws.active;  // a caller without a list of non-empty experts
     return m.kind == 1 ? launch_fast<1, false>(a, tiled, sms, dense, stream)
                        : launch_fast<2, false>(a, tiled, sms, dense, stream);
 }
