@@ -116,7 +116,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     __shared__ float s_inv;
     __shared__ int s_last;
     __shared__ __align__(8) uint64_t s_wbar;
-    const int token = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hidden = a.hidden, experts = a.experts, topk = a.topk;
     KTL_BEGIN(0)
@@ -141,6 +140,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // one (the previous block's combine) finishes. Everything below reads its output.
     grid_dependency_wait();
     KTL_MARK(2)
+    // One token per CTA for decode-size batches; larger batches launch fewer CTAs than
+    // tokens and each walks several, so the router matrix is staged once per CTA.
+    bool w_landed = true;
+    for (int token = blockIdx.x; token < a.t; token += gridDim.x) {
+    if (token != int(blockIdx.x)) __syncthreads();  // the previous token's row and logits are no longer read
     const float* xin = a.x + size_t(token) * hidden;
     RTL(0);
     for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
@@ -165,8 +169,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // a whole batch of steps are requested before the chains run, so the loads
     // overlap instead of each waiting for the previous fma.
     constexpr int BATCH = 16;
-    bool w_landed = true;
-    if (a.stage_router) w_landed = mbar_wait_bounded(&s_wbar, 0);
+    if (a.stage_router && token == int(blockIdx.x)) w_landed = mbar_wait_bounded(&s_wbar, 0);
     for (int e0 = 0; e0 < experts; e0 += ROUTE_THREADS / 4) {
         const int e = e0 + (tid >> 2), q = tid & 3;
         const bool valid = e < experts;
@@ -311,6 +314,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
 
+    }  // tokens of this CTA
+
     // ---- the dispatch, by the last CTA to get here (batches of up to one CTA's worth of tokens).
     RTL(4);
     if (a.stage_router && !w_landed) {
@@ -405,7 +410,9 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
     if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
-    launch_overlapped(route_kernel, dim3(t), dim3(ROUTE_THREADS), smem, stream, a);
+    // Up to a few CTAs' worth of tokens per SM at a time; beyond that a CTA walks several tokens.
+    const int grid = a.fuse_dispatch ? t : (t < 148 * 4 ? t : 148 * 4);
+    launch_overlapped(route_kernel, dim3(grid), dim3(ROUTE_THREADS), smem, stream, a);
     int launched = 1;
     if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
     return launched;

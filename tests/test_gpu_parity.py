@@ -309,3 +309,29 @@ def test_bad_arguments_are_refused(ctx):
     with pytest.raises(cuda.TachyonCudaError):  # empty batch (src/model.rs:565)
         layer.forward(x, x, t=0)
     layer.free()
+
+
+def test_launch_overlap_does_not_change_results(oracle, ctx):
+    """Programmatic dependent launch only moves work earlier in time."""
+    shape = MoeShape("1b-small", 512, 16, 4, 128, fmt="q8")
+    lw = layer_weights(oracle, shape, 2)
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    outs = []
+    for on in [True, False, True]:
+        ctx.set_launch_overlap(on)
+        for t in [3, 64]:  # sparse walk, dense walk with weight prefetch before the dependency wait
+            x = workloads.hidden_states(shape, t, seed=4)
+            layer = make_layer(ctx, lw, shape.topk, t)
+            yd = ctx.to_device(x.copy())
+            ones = ctx.to_device(np.ones(shape.hidden, np.float32))
+            for _ in range(3):  # back-to-back blocks: each kernel starts under the previous one's tail
+                layer.block(ones, 1e-6, yd)
+            ctx.sync()
+            outs.append(yd.get())
+            for d in (yd, ones):
+                d.free()
+            layer.free()
+    ctx.set_launch_overlap(True)
+    assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[0], outs[4])
+    assert np.array_equal(outs[1], outs[3]) and np.array_equal(outs[1], outs[5])
+    assert np.all(np.isfinite(outs[1]))
