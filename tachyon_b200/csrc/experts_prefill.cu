@@ -149,9 +149,35 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    const size_t tile_index = size_t(e) * a.row_tiles + rt;
+    const int8_t* wsrc = a.wt + tile_index * size_t(nb) * P_A_BLOCK;
+    const int8_t* xsrc = a.xt + size_t(tt) * nb * P_B_BLOCK;
+    auto issue_chunk = [&](int c) {
+        const int s = c % P_STAGES;
+        const int nblk = min(P_CHUNK, nb - c * P_CHUNK);
+        uint8_t* st = stages + s * P_STAGE_BYTES;
+        mbar_expect_tx(full + s, uint32_t(nblk) * (P_A_BLOCK + P_B_BLOCK));
+        bulk_copy(st, wsrc + size_t(c) * P_CHUNK * P_A_BLOCK, uint32_t(nblk) * P_A_BLOCK, full + s);
+        bulk_copy(st + P_CHUNK * P_A_BLOCK, xsrc + size_t(c) * P_CHUNK * P_B_BLOCK, uint32_t(nblk) * P_B_BLOCK,
+                  full + s);
+    };
+    const int first_chunks = min(P_STAGES, nchunks);
     if (warp == P_EW + 1) {
         umma::tmem_alloc(&s_tmem, P_TBUF * P_TOK);
         umma::tmem_relinquish();
+    } else if (warp == P_EW && lane == 0) {
+        // The ring starts empty: the scales and the first stages' operands are requested
+        // while TMEM is being allocated.
+        const uint32_t xs_bytes = uint32_t(nb) * P_TOK * 4;
+        const uint32_t ws_bytes = uint32_t(nb) * P_ROWS * 4;
+        mbar_expect_tx(xbar, (Q4 ? 2 : 1) * (xs_bytes + ws_bytes));
+        bulk_copy(s_xs, a.xst + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+        bulk_copy(s_wd, a.wd + tile_index * nb * P_ROWS, ws_bytes, xbar);
+        if (Q4) {
+            bulk_copy(s_xsum, a.xsumt + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
+            bulk_copy(s_wc, a.wc + tile_index * nb * P_ROWS, ws_bytes, xbar);
+        }
+        for (int c = 0; c < first_chunks; c++) issue_chunk(c);
     }
     umma::fence_before_sync();
     __syncthreads();
@@ -160,32 +186,15 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
     if (tid == 0) PTL(3, 1);
     volatile int* abort_flag = &s_abort;
 
-    const size_t tile_index = size_t(e) * a.row_tiles + rt;
     if (warp == P_EW) {
-        // ---- producer: activation scales once, then the operand chunks
+        // ---- producer: the rest of the operand chunks, each once its stage is free again
         if (lane == 0) {
-            const uint32_t xs_bytes = uint32_t(nb) * P_TOK * 4;
-            const uint32_t ws_bytes = uint32_t(nb) * P_ROWS * 4;
-            mbar_expect_tx(xbar, (Q4 ? 2 : 1) * (xs_bytes + ws_bytes));
-            bulk_copy(s_xs, a.xst + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
-            bulk_copy(s_wd, a.wd + tile_index * nb * P_ROWS, ws_bytes, xbar);
-            if (Q4) {
-                bulk_copy(s_xsum, a.xsumt + size_t(tt) * nb * P_TOK, xs_bytes, xbar);
-                bulk_copy(s_wc, a.wc + tile_index * nb * P_ROWS, ws_bytes, xbar);
-            }
-            const int8_t* wsrc = a.wt + tile_index * size_t(nb) * P_A_BLOCK;
-            const int8_t* xsrc = a.xt + size_t(tt) * nb * P_B_BLOCK;
-            int c = 0;
+            int c = first_chunks;
             for (; c < nchunks; c++) {
                 const int s = c % P_STAGES;
                 if (!wait_or_abort(empty + s, ((c / P_STAGES) & 1) ^ 1, abort_flag)) break;
-                const int nblk = min(P_CHUNK, nb - c * P_CHUNK);
-                uint8_t* st = stages + s * P_STAGE_BYTES;
                 PTL(0, c);
-                mbar_expect_tx(full + s, uint32_t(nblk) * (P_A_BLOCK + P_B_BLOCK));
-                bulk_copy(st, wsrc + size_t(c) * P_CHUNK * P_A_BLOCK, uint32_t(nblk) * P_A_BLOCK, full + s);
-                bulk_copy(st + P_CHUNK * P_A_BLOCK, xsrc + size_t(c) * P_CHUNK * P_B_BLOCK,
-                          uint32_t(nblk) * P_B_BLOCK, full + s);
+                issue_chunk(c);
             }
             if (*abort_flag) {
                 // Giving up: let the copies already issued land before the CTA's shared memory is released.

@@ -140,8 +140,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // one (the previous block's combine) finishes. Everything below reads its output.
     grid_dependency_wait();
     KTL_MARK(2)
-    // One token per CTA for decode-size batches; larger batches launch fewer CTAs than
-    // tokens and each walks several, so the router matrix is staged once per CTA.
+    // A CTA walks tokens blockIdx.x, blockIdx.x + gridDim.x, ...: one each as launched today.
     bool w_landed = true;
     for (int token = blockIdx.x; token < a.t; token += gridDim.x) {
     if (token != int(blockIdx.x)) __syncthreads();  // the previous token's row and logits are no longer read
@@ -410,9 +409,9 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
     if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
-    // Up to a few CTAs' worth of tokens per SM at a time; beyond that a CTA walks several tokens.
-    const int grid = a.fuse_dispatch ? t : (t < 148 * 4 ? t : 148 * 4);
-    launch_overlapped(route_kernel, dim3(grid), dim3(ROUTE_THREADS), smem, stream, a);
+    // One CTA per token at every batch size: measured faster than fewer CTAs that walk several
+    // tokens each (which the kernel's token loop would allow), since short CTAs overlap better.
+    launch_overlapped(route_kernel, dim3(t), dim3(ROUTE_THREADS), smem, stream, a);
     int launched = 1;
     if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
     return launched;
