@@ -41,6 +41,7 @@ METRIC = "granite_moe_decode_tokens_per_s"
 # workloads have no capture and report null.
 NCU_DRAM_BYTES_PER_LAUNCH = {("granite-1b-a400m", "q8", 32): 35761408}
 UNIT = "tokens/s"
+CLOCK_WINDOW_STEPS = 300  # untimed steps after the timed ones, for the clock sampler
 EPS = 1e-6
 
 
@@ -296,8 +297,13 @@ def main():
         for _ in range(args.steps):
             graph.launch()
         ms = ctx.timer_stop_ms()
+        launches = ctx.launch_count() - launches0
+        # The timed region lasts tens of milliseconds and nvidia-smi samples every 100 ms: keep the
+        # same load running (untimed; the same count on every rank) until a few samples are in.
+        for _ in range(CLOCK_WINDOW_STEPS if args.batch * args.layers <= 256 * 24 else 20):
+            graph.launch()
+        ctx.sync()
     ctx.sync()
-    launches = ctx.launch_count() - launches0
     if dist:
         import torch
 
