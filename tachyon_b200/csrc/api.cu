@@ -539,7 +539,9 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
     l->down_tiled = static_cast<uint8_t*>(dn);
     tc::tile_weights(dl, gate_up->dev, true, l->gate_up_tiled, ctx->stream);
     tc::tile_weights(dl, down->dev, false, l->down_tiled, ctx->stream);
-    if (!ep && tc::prefill_fits(d) && prefill_reserve(ctx, d, max_tokens)) {
+    // (Expert-parallel layers: tiles of this rank's experts; scratch for every rank's tokens.)
+    const tc::MoeDims& dp = ep ? dl : d;
+    if (tc::prefill_fits(dp) && prefill_reserve(ctx, d, ep ? max_tokens * ctx->ep.size : max_tokens)) {
         // Third copy of the experts, for prefill-size groups: int8 tiles in the tensor core's
         // canonical order and f32 block scales.
         auto get = [&](auto*& dst, size_t bytes) {
@@ -550,16 +552,16 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
             return true;
         };
         const bool q4g = gate_up->dev.kind == TC_Q4, q4d = down->dev.kind == TC_Q4;
-        bool okp = get(l->pw.gu_t, tc::prefill_weight_bytes(d, true)) && get(l->pw.gu_d, tc::prefill_scale_elems(d, true) * 4) &&
-                   get(l->pw.dn_t, tc::prefill_weight_bytes(d, false)) && get(l->pw.dn_d, tc::prefill_scale_elems(d, false) * 4);
-        if (okp && q4g) okp = get(l->pw.gu_c, tc::prefill_scale_elems(d, true) * 4);
-        if (okp && q4d) okp = get(l->pw.dn_c, tc::prefill_scale_elems(d, false) * 4);
+        bool okp = get(l->pw.gu_t, tc::prefill_weight_bytes(dp, true)) && get(l->pw.gu_d, tc::prefill_scale_elems(dp, true) * 4) &&
+                   get(l->pw.dn_t, tc::prefill_weight_bytes(dp, false)) && get(l->pw.dn_d, tc::prefill_scale_elems(dp, false) * 4);
+        if (okp && q4g) okp = get(l->pw.gu_c, tc::prefill_scale_elems(dp, true) * 4);
+        if (okp && q4d) okp = get(l->pw.dn_c, tc::prefill_scale_elems(dp, false) * 4);
         if (!okp) {
             tc_moe_layer_free(l);
             return nullptr;
         }
-        tc::tile_prefill_weights(d, gate_up->dev, true, l->pw.gu_t, l->pw.gu_d, l->pw.gu_c, ctx->stream);
-        tc::tile_prefill_weights(d, down->dev, false, l->pw.dn_t, l->pw.dn_d, l->pw.dn_c, ctx->stream);
+        tc::tile_prefill_weights(dp, gate_up->dev, true, l->pw.gu_t, l->pw.gu_d, l->pw.gu_c, ctx->stream);
+        tc::tile_prefill_weights(dp, down->dev, false, l->pw.dn_t, l->pw.dn_d, l->pw.dn_c, ctx->stream);
     }
     if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "weight tiling")) {
         tc_moe_layer_free(l);
@@ -634,7 +636,9 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
         if (ctx->capturing) return fail(ctx, "the expert-parallel block reads exchange sizes on the host: it cannot be captured");
         const char* why = tc::ep_forward(ctx->ep, layer->epb, d, static_cast<const uint16_t*>(layer->router->dev.data),
                                          layer->bias, layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
-                                         layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
+                                         layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n,
+                                         ctx->arith == tc::ARITH_CPU_LANES ? nullptr : &layer->pw, &ctx->pre,
+                                         ctx->prefill_min_avg);
         ctx->launches += n;
         layer->last_t = t;
         if (why) return fail(ctx, "expert-parallel block: %s", why);

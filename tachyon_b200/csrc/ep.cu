@@ -536,7 +536,8 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                        const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                        const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
-                       cudaStream_t stream, int* launches) {
+                       cudaStream_t stream, int* launches, const PrefillWeights* pw,
+                       const PrefillScratch* ps, int prefill_min_avg) {
     NcclApi& n = nccl();
     const int R = st.size;
     const int nbp = (d.hidden / QK + 7) / 8 * 8;
@@ -610,8 +611,16 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
         }
         lw.hidden_f = b.hidden_f;
         lw.out = b.out_recv;
-        *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, t, lw, sms, stream);
-        *launches += launch_down_fast_rows(ld, down, down_tiled, lw, b.slot_row, sms, stream);
+        if (pw && ps && pw->gu_t && received >= size_t(prefill_min_avg) * size_t(b.local)) {
+            // Prefill-size groups: the tcgen05 kernels, on this rank's tiles.
+            *launches += launch_prefill(ld, true, gate_up.kind == 2, *pw, *ps, lw, int(received), b.hidden_f, nullptr,
+                                        stream);
+            *launches += launch_prefill(ld, false, down.kind == 2, *pw, *ps, lw, int(received), b.out_recv,
+                                        b.slot_row, stream);
+        } else {
+            *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, t, lw, sms, stream);
+            *launches += launch_down_fast_rows(ld, down, down_tiled, lw, b.slot_row, sms, stream);
+        }
     }
 
     // Outputs back to the ranks the slots came from, into their expert-contiguous order.

@@ -92,6 +92,7 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                        const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                        const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
-                       cudaStream_t stream, int* launches);
+                       cudaStream_t stream, int* launches, const PrefillWeights* pw = nullptr,
+                       const PrefillScratch* ps = nullptr, int prefill_min_avg = 32);
 
 }  // namespace tc
