@@ -52,6 +52,8 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=32, help="decode tokens per step per GPU")
     ap.add_argument("--layers", type=int, default=workloads.GRANITE_1B.layers)
+    ap.add_argument("--model", default="1b-a400m", choices=["1b-a400m", "3b-a800m-q8"],
+                    help="expert shape: the headline granite-1b-a400m, or the 3b-a800m shape with int8 weights")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -188,7 +190,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    shape = workloads.GRANITE_1B
+    shape = workloads.GRANITE_1B if args.model == "1b-a400m" else workloads.GRANITE_3B_Q8
     host_threads = max(1, (os.cpu_count() or 8) // max(1, world) - 1)
 
     if args.impl == "reference":
