@@ -541,7 +541,8 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
     tc::tile_weights(dl, down->dev, false, l->down_tiled, ctx->stream);
     // (Expert-parallel layers: tiles of this rank's experts; scratch for every rank's tokens.)
     const tc::MoeDims& dp = ep ? dl : d;
-    if (tc::prefill_fits(dp) && prefill_reserve(ctx, d, ep ? max_tokens * ctx->ep.size : max_tokens)) {
+    if (tc::prefill_fits(dp, gate_up->dev.kind == TC_Q4, down->dev.kind == TC_Q4) &&
+        prefill_reserve(ctx, d, ep ? max_tokens * ctx->ep.size : max_tokens)) {
         // Third copy of the experts, for prefill-size groups: int8 tiles in the tensor core's
         // canonical order and f32 block scales.
         auto get = [&](auto*& dst, size_t bytes) {

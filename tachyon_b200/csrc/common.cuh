@@ -294,7 +294,7 @@ struct PrefillScratch {  // per context
     int max_tiles = 0;
 };
 void init_kernels_prefill();
-bool prefill_fits(const MoeDims& d);
+bool prefill_fits(const MoeDims& d, bool q4_gate_up, bool q4_down);
 size_t prefill_weight_bytes(const MoeDims& d, bool gate_up);
 size_t prefill_scale_elems(const MoeDims& d, bool gate_up);
 int prefill_max_token_tiles(int slots, int experts);

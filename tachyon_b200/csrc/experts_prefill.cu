@@ -542,8 +542,9 @@ int prefill_row_tiles(const MoeDims& d, bool gate_up) {
     return gate_up ? (d.inter + 63) / 64 : (d.hidden + P_ROWS - 1) / P_ROWS;
 }
 
-bool prefill_fits(const MoeDims& d) {
-    return prefill_smem(d.hidden / QK, true) <= size_t(P_SMEM_LIMIT) && prefill_smem(d.inter / QK, true) <= size_t(P_SMEM_LIMIT);
+bool prefill_fits(const MoeDims& d, bool q4_gate_up, bool q4_down) {
+    return prefill_smem(d.hidden / QK, q4_gate_up) <= size_t(P_SMEM_LIMIT) &&
+           prefill_smem(d.inter / QK, q4_down) <= size_t(P_SMEM_LIMIT);
 }
 
 size_t prefill_weight_bytes(const MoeDims& d, bool gate_up) {
