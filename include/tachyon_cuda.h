@@ -173,6 +173,14 @@ int tc_ep_set_uniform_batch(tc_ctx *ctx, int on);
  * never signals leaves an error status for tc_sync, not a hang). No collective
  * library call runs inside a block; same values as one GPU. */
 int tc_ep_enable_peer_exchange(tc_ctx *ctx, int hidden, int experts_per_token, int max_tokens);
+/* How long a kernel of the peer-memory exchange polls another rank's flag before it
+ * gives up, leaves an error status for tc_sync and goes on (default 2^23 polls,
+ * about ten seconds). Applies to blocks enqueued (or captured) afterwards. */
+int tc_ep_set_wait_limit(tc_ctx *ctx, uint32_t polls);
+/* Testing hook: the next `blocks` blocks store this rank's rows into the windows but
+ * do not announce them, as if the rank never signalled; the kernels waiting for it
+ * then run into the limit above. No fault is injected and nothing hangs. */
+int tc_ep_test_mute_signals(tc_ctx *ctx, int blocks);
 /* Collective: returns when every rank has reached it (host-side barrier). */
 int tc_ep_barrier(tc_ctx *ctx);
 tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int experts_per_token, int inter,

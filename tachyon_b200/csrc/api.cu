@@ -37,6 +37,7 @@ struct tc_ctx {
     float* host_x = nullptr;  // device staging for the host-buffer entry point
     float* host_y = nullptr;
     size_t host_elems = 0;
+    int* static_status = nullptr;  // status word of tc_dispatch_static on this device, once it has been used
 };
 
 struct tc_matrix {
@@ -137,13 +138,19 @@ void ws_release(tc_ctx* ctx) {
     ctx->ws = tc::Workspace{};
 }
 
-// Scratch of the tcgen05 path: token tiles for up to max_tokens * topk slots.
+// Scratch of the tcgen05 path: token tiles for up to max_tokens * topk slots. Shared by
+// the context's layers, so it only ever grows: every dimension is the largest any
+// layer has asked for. Growing it frees the old buffers, which invalidates graphs
+// captured earlier; create every layer before capturing.
 bool prefill_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
     const int tiles = tc::prefill_max_token_tiles(max_tokens * d.topk, d.experts);
     const int nb = std::max(d.hidden, d.inter) / 32;
-    const size_t xt_bytes = size_t(tiles) * nb * 64 * 32, xst_elems = size_t(tiles) * nb * 64;
     tc::PrefillScratch& p = ctx->pre;
-    if (p.max_tiles >= tiles && p.xt_bytes >= xt_bytes) return true;
+    const size_t per_tile = size_t(nb) * tc::prefill_token_tile() * 32;
+    if (p.max_tiles >= tiles && p.xt_bytes >= size_t(tiles) * per_tile && p.tile_bytes >= per_tile) return true;
+    const int T = std::max(tiles, p.max_tiles);
+    const size_t tile_bytes = std::max(per_tile, p.tile_bytes);
+    const size_t xt_bytes = size_t(T) * tile_bytes, xst_elems = xt_bytes / 32;
     cudaStreamSynchronize(ctx->stream);
     for (void* q : ctx->pre_allocs) cudaFree(q);
     ctx->pre_allocs.clear();
@@ -155,12 +162,16 @@ bool prefill_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
         dst = static_cast<std::remove_reference_t<decltype(dst)>>(raw);
         return true;
     };
-    const int T = std::max(tiles, p.max_tiles);
     if (!(get(p.tile_expert, size_t(T) * 4) && get(p.tile_n, size_t(T) * 4) && get(p.tile_count, 4) &&
           get(p.tile_p0, size_t(T) * 4) && get(p.xt, xt_bytes) && get(p.xst, xst_elems * 4) &&
-          get(p.xsumt, xst_elems * 4)))
+          get(p.xsumt, xst_elems * 4))) {
+        for (void* q : ctx->pre_allocs) cudaFree(q);
+        ctx->pre_allocs.clear();
+        p = tc::PrefillScratch{};
         return false;
+    }
     p.max_tiles = T;
+    p.tile_bytes = tile_bytes;
     p.xt_bytes = xt_bytes;
     p.xst_elems = xst_elems;
     return true;
@@ -191,13 +202,14 @@ bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
               ws_alloc(ctx, w.hs, slots * pad8(n.inter / 32)) &&
               ws_alloc(ctx, w.hsum, slots * pad8(n.inter / 32)) &&
               ws_alloc(ctx, w.out, slots * n.hidden) && ws_alloc(ctx, w.status, size_t(1)) &&
-              ws_alloc(ctx, w.ticket, size_t(1));
+              ws_alloc(ctx, w.ticket, size_t(1)) && ws_alloc(ctx, w.grid_sync, size_t(tc::GRID_SYNC_WORDS));
     if (!ok) {
         ws_release(ctx);
         return false;
     }
     cudaMemset(w.status, 0, sizeof(int));
     cudaMemset(w.ticket, 0, sizeof(int));
+    cudaMemset(w.grid_sync, 0, tc::GRID_SYNC_WORDS * sizeof(uint32_t));
     w.max_tokens = T;
     w.hidden = n.hidden;
     w.experts = n.experts;
@@ -272,17 +284,37 @@ size_t tc_last_error(tc_ctx* ctx, char* out, size_t len) {
 
 void* tc_stream(tc_ctx* ctx) { return ctx->stream; }
 
+namespace {
+const char* status_text(int status) {
+    switch (status) {
+        case tc::ERR_COPY_WAIT_TIMEOUT: return "a staged copy did not arrive within a kernel's wait limit";
+        case tc::ERR_PEER_WAIT_TIMEOUT: return "another rank's signal did not arrive within a kernel's wait limit";
+        case tc::ERR_BAD_EXPERT_ID: return "the dispatch met an expert id out of range or named twice by one token";
+        case tc::ERR_GRID_WAIT_TIMEOUT: return "a kernel's CTAs gave up waiting for one another";
+        default: return "unknown status";
+    }
+}
+}  // namespace
+
 int tc_sync(tc_ctx* ctx) {
     if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return -1;
-    if (ctx->ws.status) {
+    int* words[2] = {ctx->ws.status, ctx->static_status};
+    int worst = 0;
+    for (int* w : words) {
+        if (!w) continue;
         int status = 0;
-        if (!cuda_ok(ctx, cudaMemcpy(&status, ctx->ws.status, sizeof status, cudaMemcpyDeviceToHost),
-                     "status readback"))
+        if (!cuda_ok(ctx, cudaMemcpy(&status, w, sizeof status, cudaMemcpyDeviceToHost), "status readback"))
             return -1;
         if (status != 0) {
-            cudaMemset(ctx->ws.status, 0, sizeof(int));
-            return fail(ctx, "a kernel gave up a bounded wait (status %d)", status);
+            cudaMemset(w, 0, sizeof(int));
+            worst = status;
         }
+    }
+    if (worst) {
+        // A kernel that gave up may have left its arrival counters part-way: start clean.
+        if (ctx->ws.ticket) cudaMemset(ctx->ws.ticket, 0, sizeof(int));
+        if (ctx->ws.grid_sync) cudaMemset(ctx->ws.grid_sync, 0, tc::GRID_SYNC_WORDS * sizeof(uint32_t));
+        return fail(ctx, "a kernel reported status %d: %s", worst, status_text(worst));
     }
     return 0;
 }
@@ -464,6 +496,18 @@ int tc_ep_enable_peer_exchange(tc_ctx* ctx, int hidden, int experts_per_token, i
     cudaSetDevice(ctx->device);
     const char* why = tc::ep_peer_enable(ctx->ep, hidden, experts_per_token, max_tokens);
     return why ? fail(ctx, "tc_ep_enable_peer_exchange: %s", why) : 0;
+}
+
+int tc_ep_set_wait_limit(tc_ctx* ctx, uint32_t polls) {
+    if (polls == 0) return fail(ctx, "the wait limit must be at least one poll");
+    ctx->ep.peer.wait_limit = polls;
+    return 0;
+}
+
+int tc_ep_test_mute_signals(tc_ctx* ctx, int blocks) {
+    if (!ctx->ep.peer.on) return fail(ctx, "tc_ep_test_mute_signals: the peer-memory exchange is not enabled");
+    ctx->ep.peer.mute_next = blocks < 0 ? 0 : blocks;
+    return 0;
 }
 
 int tc_ep_barrier(tc_ctx* ctx) {
@@ -755,7 +799,7 @@ int tc_moe_last_dispatch(tc_moe_layer* layer, uint32_t* offsets, uint32_t* perm)
 int tc_dispatch_static(tc_ctx* ctx, const uint32_t* ids, int t, int experts, int topk, uint32_t* counts,
                        uint32_t* offsets, uint32_t* perm, uint32_t* pos, uint32_t* slot_token, int* active) {
     const char* why = tc::dispatch_static(ctx->device, ids, t, experts, topk, counts, offsets, perm, pos,
-                                          slot_token, active, ctx->stream);
+                                          slot_token, active, ctx->stream, &ctx->static_status);
     if (why) return fail(ctx, "tc_dispatch_static: %s", why);
     ctx->launches += 3;
     return 0;
@@ -781,7 +825,7 @@ int tc_umma_selftest(tc_ctx* ctx, const int8_t* a_rows, const int8_t* b_rows, in
         cudaMemcpy(db, tb.data(), tb.size(), cudaMemcpyHostToDevice);
         cudaMemset(dd, 0xFF, size_t(128) * n * 4);
         cudaMemset(ds, 0, 4);
-        ctx->launches += tc::launch_umma_probe(static_cast<int8_t*>(da), static_cast<int8_t*>(db), n,
+        ctx->launches += tc::launch_umma_selftest(static_cast<int8_t*>(da), static_cast<int8_t*>(db), n,
                                               static_cast<int*>(dd), static_cast<int*>(ds), ctx->stream);
         ok = cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "tcgen05 self-test");
         if (ok) {

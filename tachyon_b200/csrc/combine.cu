@@ -17,15 +17,15 @@ constexpr int COMBINE_THREADS = 256;
 
 __global__ void __launch_bounds__(COMBINE_THREADS)
 combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates,
-               const uint32_t* __restrict__ pos, const float* __restrict__ out, int hidden, int topk,
+               const uint32_t* __restrict__ pos, const float* out, int hidden, int topk,
                float* y, const PeerWait pw) {
+    // (`out` without __restrict__: in the peer-memory exchange other GPUs store these rows
+    // while this kernel is already resident, up to the wait below.)
     __shared__ uint32_t s_pos[MAX_TOPK];
     __shared__ float s_gate[MAX_TOPK];
     const int token = blockIdx.x, tid = threadIdx.x;
-    KTL_BEGIN(3)
     grid_launch_dependents();
     grid_dependency_wait();
-    KTL_MARK(2)
     if (pw.flags) {  // expert outputs arrive from other ranks: all of them have signalled this block
         if (tid < pw.ranks) peer_wait(pw, tid);
         __syncthreads();
@@ -57,7 +57,6 @@ combine_kernel(const uint32_t* __restrict__ ids, const float* __restrict__ gates
         r.w = r.w + proj.w;
         *reinterpret_cast<float4*>(yr + c) = r;
     }
-    KTL_MARK(3)
 }
 
 }  // namespace
@@ -72,4 +71,3 @@ int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_
 
 }  // namespace tc
 
-KTL_DUMP(tc_debug_ktl_combine)

@@ -17,6 +17,7 @@ constexpr int SUPER = 8;        // 4-bit blocks per packed super-block (src/kern
 constexpr int SUPER_WORDS = 5;  // words per super-block (src/kernels.rs:167)
 
 constexpr int MAX_EXPERTS = 256;
+constexpr int GRID_SYNC_WORDS = 8;
 constexpr int MAX_TOPK = 32;
 
 // Error codes a kernel may leave in the context's status word.
@@ -24,6 +25,8 @@ enum : int {
     ERR_NONE = 0,
     ERR_COPY_WAIT_TIMEOUT = 1,  // a staged weight copy did not arrive within the spin limit
     ERR_PEER_WAIT_TIMEOUT = 2,  // another rank's signal did not arrive within the spin limit
+    ERR_BAD_EXPERT_ID = 3,      // the dispatch met an expert id out of range, or twice in one token
+    ERR_GRID_WAIT_TIMEOUT = 4,  // a CTA gave up waiting for the other CTAs of its own grid
 };
 
 struct MatrixDev {
@@ -41,6 +44,7 @@ struct PeerWait {
     const uint32_t* epoch = nullptr;
     int ranks = 0;
     int* status = nullptr;
+    uint32_t limit = 1u << 23;        // polls before the wait gives up (about ten seconds by default)
 };
 
 // Sending this rank's rows to every rank's window, then announcing it (or, with t = 0,
@@ -53,6 +57,7 @@ struct PeerPlan {
     const uint32_t* ids = nullptr;
     int t = 0, hidden = 0, nbp = 0, topk = 0, me = 0, ranks = 0, flag_set = 0;
     uint32_t* epoch = nullptr;  // this rank's counters, one per flag set
+    int mute = 0;               // testing: send the rows but not the announcement (a rank that never signals)
 };
 
 // The sorted slots cut into runs of at most 16 slots of one expert, for callers
@@ -88,6 +93,7 @@ struct Workspace {
     float* out = nullptr;         // [T*k, H] expert outputs, sorted order
     int* status = nullptr;        // device status word
     int* ticket = nullptr;        // arrival counter of the router CTAs (zero between launches)
+    uint32_t* grid_sync = nullptr;  // [GRID_SYNC_WORDS] arrival counters of the one-kernel decode block (zero between launches)
     RunList runs;                 // when set: the expert kernels walk these instead of counts/offsets/active
     PeerWait combine_wait;        // set for the peer-memory exchange only
     PeerWait dispatch_wait;       // the same, before the dispatch over every rank's tokens
@@ -129,10 +135,11 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
 int launch_dispatch(const MoeDims& d, int t, Workspace& ws, cudaStream_t stream);
 
 // The three-pass dispatch with its scratch in an array built into the library
-// (no allocation). Returns null, or why the call was refused.
+// (no allocation). Returns null, or why the call was refused. *status_word receives the
+// device address of the status word the kernels report bad expert ids in.
 const char* dispatch_static(int device, const uint32_t* ids, int t, int experts, int topk,
                             uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* pos,
-                            uint32_t* slot_token, int* active, cudaStream_t stream);
+                            uint32_t* slot_token, int* active, cudaStream_t stream, int** status_word);
 
 // gate_up rows of each expert times its tokens, SwiGLU, into ws.hidden_f.
 int launch_gate_up_exact(const MoeDims& d, const MatrixDev& gate_up, int t, Workspace& ws, int sms,
@@ -199,43 +206,13 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
 }
 #endif
 
-#if defined(TC_TIMELINE) && defined(__CUDACC__)
-// Diagnostic build only: wall-clock stamps (ns) of CTA 0 of each launch in this
-// translation unit: kind, entry, after the dependency wait, exit.
-static __device__ unsigned long long g_ktl[2048][4];
-static __device__ unsigned g_ktl_n;
-__device__ __forceinline__ unsigned long long ktl_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define KTL_BEGIN(kind)                                                  \
-    unsigned ktl_slot = 0xffffffffu;                                     \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {        \
-        ktl_slot = atomicAdd(&g_ktl_n, 1u) % 2048u;                      \
-        g_ktl[ktl_slot][0] = (kind);                                     \
-        g_ktl[ktl_slot][1] = ktl_now();                                  \
-    }
-#define KTL_MARK(i) \
-    if (ktl_slot != 0xffffffffu) g_ktl[ktl_slot][i] = ktl_now();
-#define KTL_DUMP(name)                                                               \
-    extern "C" int name(unsigned long long* out, unsigned* n) {                      \
-        cudaMemcpyFromSymbol(n, tc::g_ktl_n, sizeof(unsigned));                      \
-        return int(cudaMemcpyFromSymbol(out, tc::g_ktl, sizeof(tc::g_ktl)));         \
-    }
-#else
-#define KTL_BEGIN(kind)
-#define KTL_MARK(i)
-#define KTL_DUMP(name)
-#endif
-
 #ifdef __CUDACC__
-// Bounded wait for rank r's signal: about ten seconds of polling (ranks of one job
-// can be seconds apart when they enqueue their first block), then an error status;
-// the caller goes on, so the context stays usable.
+// Bounded wait for rank r's signal: pw.limit polls (by default about ten seconds: ranks
+// of one job can be seconds apart when they enqueue their first block), then an error
+// status; the caller goes on, so the context stays usable.
 __device__ __forceinline__ void peer_wait(const PeerWait& pw, int r) {
     const uint32_t want = *pw.epoch;
-    for (uint32_t i = 0; i < (1u << 23); i++) {
+    for (uint32_t i = 0; i < pw.limit; i++) {
         uint32_t seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(pw.flags + r) : "memory");
         if (int32_t(seen - want) >= 0) return;
@@ -268,7 +245,7 @@ __device__ __forceinline__ void peer_scatter_signal(const PeerPlan& a, uint32_t*
         a.epoch[a.flag_set] = *s_epoch;
     }
     __syncthreads();
-    if (tid < a.ranks) {
+    if (tid < a.ranks && !a.mute) {
         uint32_t* flag = reinterpret_cast<uint32_t*>(a.base[tid] + a.off_flags) + a.flag_set * 8 + a.me;
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(*s_epoch) : "memory");
     }
@@ -291,6 +268,7 @@ struct PrefillScratch {  // per context
     int8_t* xt = nullptr;
     float *xst = nullptr, *xsumt = nullptr;
     size_t xt_bytes = 0, xst_elems = 0;
+    size_t tile_bytes = 0;  // bytes of one token tile's 8-bit rows at the widest layer so far
     int max_tiles = 0;
 };
 void init_kernels_prefill();
@@ -298,13 +276,14 @@ bool prefill_fits(const MoeDims& d, bool q4_gate_up, bool q4_down);
 size_t prefill_weight_bytes(const MoeDims& d, bool gate_up);
 size_t prefill_scale_elems(const MoeDims& d, bool gate_up);
 int prefill_max_token_tiles(int slots, int experts);
+int prefill_token_tile();  // tokens per tile
 void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, int8_t* wt, float* wd, float* wc,
                           cudaStream_t stream);
 int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights& w, const PrefillScratch& s,
                    const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream);
 
 // One 128 x n x 32 int8 tcgen05 MMA (n = 64 or 128) through TMEM: a self-check of the encodings.
-int launch_umma_probe(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
+int launch_umma_selftest(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
                       cudaStream_t stream);
 
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);

@@ -11,17 +11,32 @@ constexpr int DISPATCH_THREADS = 256;
 constexpr int DISPATCH_WARPS = DISPATCH_THREADS / 32;
 
 // Sets this token's bits and returns with bits[e][w] complete (after a CTA barrier).
+// An id outside [0, experts) or an expert named twice by one token is not marked:
+// the slot is left out of the dispatch and *status is set to ERR_BAD_EXPERT_ID.
 __device__ __forceinline__ void mark_picks(uint32_t (*bits)[DISPATCH_WARPS], const uint32_t* ids,
-                                           int token, int t, int experts, int topk) {
+                                           int token, int t, int experts, int topk, int* status) {
     const int tid = threadIdx.x;
     for (int i = tid; i < experts * DISPATCH_WARPS; i += DISPATCH_THREADS) (&bits[0][0])[i] = 0;
     __syncthreads();
     if (token < t) {
         const int warp = tid >> 5, lane = tid & 31;
-        for (int q = 0; q < topk; q++)
-            atomicOr(&bits[ids[size_t(token) * topk + q]][warp], 1u << lane);
+        for (int q = 0; q < topk; q++) {
+            const uint32_t e = ids[size_t(token) * topk + q];
+            const bool bad = e >= uint32_t(experts) || ((atomicOr(&bits[e][warp], 1u << lane) >> lane) & 1u);
+            if (bad && status) atomicExch(status, ERR_BAD_EXPERT_ID);
+        }
     }
     __syncthreads();
+}
+
+// True for a pick the dispatch places: a valid expert id, and the first of the token's
+// picks to name that expert.
+__device__ __forceinline__ bool pick_is_placed(const uint32_t* ids, int token, int q, int experts, int topk) {
+    const uint32_t e = ids[size_t(token) * topk + q];
+    if (e >= uint32_t(experts)) return false;
+    for (int p = 0; p < q; p++)
+        if (ids[size_t(token) * topk + p] == e) return false;
+    return true;
 }
 
 __device__ __forceinline__ uint32_t row_count(const uint32_t (*bits)[DISPATCH_WARPS], int e) {
@@ -94,12 +109,12 @@ struct DispatchSmem {
 __device__ __forceinline__ void dispatch_small_body(DispatchSmem& sm, const uint32_t* ids, int t, int experts,
                                                     int topk, uint32_t* counts, uint32_t* offsets,
                                                     uint32_t* perm, uint32_t* pos, uint32_t* slot_token,
-                                                    int* active) {
+                                                    int* active, int* status) {
     uint32_t (*bits)[DISPATCH_WARPS] = sm.bits;
     uint32_t* scount = sm.scount;
     uint32_t* soff = sm.soff;
     const int tid = threadIdx.x;
-    mark_picks(bits, ids, tid, t, experts, topk);
+    mark_picks(bits, ids, tid, t, experts, topk, status);
     for (int e = tid; e < experts; e += DISPATCH_THREADS) {
         const uint32_t n = row_count(bits, e);
         scount[e] = n;
@@ -113,6 +128,7 @@ __device__ __forceinline__ void dispatch_small_body(DispatchSmem& sm, const uint
     if (tid < t) {
         for (int q = 0; q < topk; q++) {
             const uint32_t slot = uint32_t(tid) * topk + q;
+            if (!pick_is_placed(ids, tid, q, experts, topk)) continue;
             const int e = ids[slot];
             const uint32_t p = soff[e] + rank_in_cta(bits, e, tid);
             perm[p] = slot;

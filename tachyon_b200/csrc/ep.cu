@@ -372,21 +372,15 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
 // n+1 after its combine of block n, which waited for every rank's step 5 of block n,
 // i.e. for every reader of the rows of block n.
 __global__ void __launch_bounds__(1024) peer_scatter_signal_kernel(const PeerPlan a) {
-    KTL_BEGIN(4 + a.flag_set)
-    KTL_MARK(2)
     __shared__ uint32_t s_epoch;
     peer_scatter_signal(a, &s_epoch);
-    KTL_MARK(3)
 }
 
 // The signal alone (t = 0 rows): after the down kernel, whose stores into the other
 // ranks' windows are complete when this kernel starts.
 __global__ void peer_wait_kernel(const PeerWait pw) {
-    KTL_BEGIN(6)
-    KTL_MARK(2)
     if (int(threadIdx.x) < pw.ranks) peer_wait(pw, threadIdx.x);
     __syncwarp();
-    KTL_MARK(3)
 }
 
 const char* ep_barrier(EpState& st, cudaStream_t stream) {
@@ -470,6 +464,10 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     plan.t = t, plan.hidden = d.hidden, plan.nbp = nbp, plan.topk = d.topk, plan.me = st.rank, plan.ranks = R;
     plan.flag_set = 0;
     plan.epoch = p.epoch;
+    if (p.mute_next > 0) {
+        plan.mute = 1;
+        p.mute_next--;
+    }
     Workspace rw = ws;
     rw.route_scatter = plan;  // batches of up to one CTA's worth of tokens: sent by the router's last CTA
     *launches += launch_route(d, router, bias, x, norm_w, eps, t, rw, stream);
@@ -494,6 +492,7 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     gw.dispatch_wait.epoch = p.epoch;
     gw.dispatch_wait.ranks = R;
     gw.dispatch_wait.status = ws.status;
+    gw.dispatch_wait.limit = p.wait_limit;
     *launches += launch_dispatch(d, G, gw, stream);
     if (gate_up.kind == 2) {
         const size_t want_blocks = (size_t(G) * nbp + 7) / 8;
@@ -526,6 +525,7 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     cw.combine_wait.epoch = p.epoch + 1;
     cw.combine_wait.ranks = R;
     cw.combine_wait.status = ws.status;
+    cw.combine_wait.limit = p.wait_limit;
     *launches += launch_combine(d, t, cw, y, stream);
     return nullptr;
 }
@@ -637,4 +637,3 @@ const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const u
 
 }  // namespace tc
 
-KTL_DUMP(tc_debug_ktl_ep)

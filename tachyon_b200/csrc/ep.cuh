@@ -38,6 +38,8 @@ struct EpPeer {
     uint8_t* window = nullptr;                 // this rank's
     uint8_t* base[8] = {};                     // every rank's window as mapped here (base[rank] == window)
     size_t off_xq = 0, off_xs = 0, off_ids = 0, off_out = 0, off_flags = 0, bytes = 0;
+    uint32_t wait_limit = 1u << 23;            // polls a kernel spends on another rank's flag before giving up
+    int mute_next = 0;                         // testing: this many coming blocks send rows without announcing them
     uint32_t* epoch = nullptr;                 // [0], [1]: this rank's signal counters (rows sent, outputs
                                                // sent); [2]: arrival counter of the down kernel's CTAs
 };

@@ -192,7 +192,6 @@ __device__ __forceinline__ float offset_dot(const uint32_t* words, const float* 
     return ((acc[0] + acc[4]) + (acc[1] + acc[5])) + ((acc[2] + acc[6]) + (acc[3] + acc[7]));
 }
 
-
 // Two IEEE f32 operations per instruction (the results are those of the
 // scalar forms): a - m, a * b, fma(a, b, c) on register pairs.
 __device__ __forceinline__ float2 sub2(float2 a, float2 m) {
@@ -225,6 +224,5 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
         : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
     return r;
 }
-
 
 }  // namespace tc

@@ -331,19 +331,6 @@ __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t
     }
 }
 
-#ifdef TC_TIMELINE
-// Diagnostic build only: cycle stamps per (CTA, warp, event).
-__device__ long long g_timeline[148][F_MAX_WARPS][16];
-#define TL(k)                                                                       \
-    do {                                                                            \
-        if (GATE_UP && lane == 0 && blockIdx.x < 148) g_timeline[blockIdx.x][warp][k] = clock64(); \
-    } while (0)
-#else
-#define TL(k) \
-    do {      \
-    } while (0)
-#endif
-
 // One segment of the CTA's walk: an expert and up to F_TOK of its tokens.
 struct Segment {
     int ai, e, sg0, ntok, G;
@@ -360,9 +347,7 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
     const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
     const Layout<KIND> L(nwarps, f.stages, a.cols, f.nbp);
     const int STAGES = f.stages;
-    KTL_BEGIN(GATE_UP ? 1 : 2)
     grid_launch_dependents();
-    TL(0);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * F_MAX_STAGES;
     if (lane == 0) {
@@ -371,7 +356,6 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
-    TL(1);
     const int upe = a.units_per_expert;
     const int nchunks = (a.cols + F_KC - 1) / F_KC;
     // Dense walk (batches that reach nearly every expert): the partition of units over
@@ -396,7 +380,6 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         }
     }
     grid_dependency_wait();  // everything below reads what earlier kernels wrote
-    KTL_MARK(2)
     const int total = (a.runs.expert ? *a.runs.n : f.dense ? a.experts : int(a.active[a.experts])) * upe;
     const int lo = int((long long)blockIdx.x * total / gridDim.x);
     const int hi = int((long long)(blockIdx.x + 1) * total / gridDim.x);
@@ -424,17 +407,12 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
         wk.advance(prod);
     }
     for (int s = npre; s < STAGES - 1; s++) fill_next();
-    TL(2);
 
     const int g = lane >> 2, t = lane & 3;
     const int nb = a.cols / QK;
     float acc[F_GMAX][4], off[F_GMAX][4];
     bool ok = true;
     uint32_t xphase = 0, xtok = 0;
-#ifdef TC_TIMELINE
-    long long tl_wait = 0, tl_compute = 0, tl_chunks = 0, tl_fill = 0, tl_epi = 0;
-    int seg_index = 0;
-#endif
 
     // The CTA's segments in order, the same walk in every thread.
     Segment next;
@@ -573,24 +551,13 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
             __syncthreads();
             asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
         }
-#ifdef TC_TIMELINE
-        if (seg_index < 3) TL(3 + 4 * seg_index);
-        bool first_chunk = true;
-#endif
         // ---- this warp's units of the group's segments
         for (int sx = 0; sx < nseg; sx++) {
             const Segment& sg = seg[sx];
             const uint32_t xq_s = smem_addr(smem + L.xq(sx)), xsT_s = smem_addr(smem + L.xsT(sx)),
                            xsumT_s = smem_addr(smem + L.xsumT(sx));
             while (ok && cons.valid && cons.ai == sg.ai && cons.sg0 == sg.sg0) {
-#ifdef TC_TIMELINE
-                const long long tf0 = clock64();
-#endif
                 if (fills - takes < uint32_t(STAGES)) fill_next();
-#ifdef TC_TIMELINE
-                __syncwarp();
-                tl_fill += clock64() - tf0;
-#endif
                 if (cons.c == 0) {
 #pragma unroll
                     for (int nt = 0; nt < F_GMAX; nt++) {
@@ -599,22 +566,11 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                     }
                 }
                 const uint32_t stage = takes % STAGES;
-#ifdef TC_TIMELINE
-                const long long tw0 = clock64();
-#endif
                 const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
-#ifdef TC_TIMELINE
-                const long long tw1 = clock64();
-                tl_wait += tw1 - tw0;
-#endif
                 if (!__all_sync(0xffffffffu, landed)) {
                     ok = false;
                     break;
                 }
-#ifdef TC_TIMELINE
-                if (first_chunk && seg_index < 3) TL(4 + 4 * seg_index);
-                first_chunk = false;
-#endif
                 const uint32_t wtok = uint32_t(landed);
                 const uint32_t rec = smem_addr(ring + stage * R::BYTES);
                 const int nblk = min(F_NBC, nb - cons.c * F_NBC);
@@ -624,11 +580,6 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                 else if (sg.G == 2)  // (0: an expert without tokens in a dense walk; its records are only drained)
                     fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 __syncwarp();
-#ifdef TC_TIMELINE
-                const long long te0 = clock64();
-                tl_compute += te0 - tw1;
-                tl_chunks++;
-#endif
 
                 if (cons.c == wk.nchunks - 1) {
                     const int u = cons.a - sg.ai * upe;
@@ -668,33 +619,11 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                 }
                 takes++;
                 wk.advance(cons);
-#ifdef TC_TIMELINE
-                __syncwarp();
-                tl_epi += clock64() - te0;
-#endif
             }
         }
-#ifdef TC_TIMELINE
-        if (seg_index < 3) TL(5 + 4 * seg_index);
-#endif
         // Keep the decision to stop uniform across the CTA's barriers.
         ok = __syncthreads_and(ok);
-#ifdef TC_TIMELINE
-        if (seg_index < 3) TL(6 + 4 * seg_index);
-        seg_index++;
-#endif
     }
-    TL(15);
-    KTL_MARK(3)
-#ifdef TC_TIMELINE
-    if (GATE_UP && lane == 0 && blockIdx.x < 148) {
-        g_timeline[blockIdx.x][warp][12] = tl_wait;
-        g_timeline[blockIdx.x][warp][13] = tl_compute;
-        g_timeline[blockIdx.x][warp][14] = tl_chunks;
-        g_timeline[blockIdx.x][warp][10] = tl_fill;
-        g_timeline[blockIdx.x][warp][11] = tl_epi;
-    }
-#endif
     if (!GATE_UP && a.peer_ranks) {
         // Rows went into other ranks' windows. Order this CTA's stores before its ticket
         // (CTA barrier, then a cumulative system-scope fence); the last CTA to arrive then
@@ -821,12 +750,6 @@ void run_tiling(const ExpertArgs& e, uint8_t* tiled, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef TC_TIMELINE
-extern "C" int tc_debug_timeline(long long* out) {
-    return int(cudaMemcpyFromSymbol(out, g_timeline, sizeof(g_timeline)));
-}
-#endif
-
 void init_kernels_fast() {
     const int lim = int(F_SMEM_LIMIT);
     cudaFuncSetAttribute(expert_fast_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
@@ -938,4 +861,3 @@ int launch_down_fast_rows(const MoeDims& d, const MatrixDev& m, const uint8_t* t
 
 }  // namespace tc
 
-KTL_DUMP(tc_debug_ktl_experts)

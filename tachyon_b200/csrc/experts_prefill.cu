@@ -91,20 +91,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
 
-#ifdef TC_TIMELINE
-// Diagnostic build only: cycle stamps of the first 148 CTAs, per role.
-__device__ long long g_ptl[148][10][40];
-#define PTL(role, k)                                                                          \
-    do {                                                                                      \
-        const int cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                 \
-        if (GATE_UP && cta_ < 148 && (k) < 40) g_ptl[cta_][role][k] = clock64();              \
-    } while (0)
-#else
-#define PTL(role, k) \
-    do {             \
-    } while (0)
-#endif
-
 template <bool Q4, bool GATE_UP>
 __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const PrefillArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -125,7 +111,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int tt = blockIdx.y, rt = blockIdx.x;
-    if (tid == 0) PTL(3, 0);
     if (tt >= *a.tile_count) return;  // uniform: the whole CTA leaves before touching TMEM
     const int e = a.tile_expert[tt];
     const int tile_n = a.tile_n[tt];
@@ -183,7 +168,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = s_tmem;
-    if (tid == 0) PTL(3, 1);
     volatile int* abort_flag = &s_abort;
 
     if (warp == P_EW) {
@@ -193,7 +177,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
             for (; c < nchunks; c++) {
                 const int s = c % P_STAGES;
                 if (!wait_or_abort(empty + s, ((c / P_STAGES) & 1) ^ 1, abort_flag)) break;
-                PTL(0, c);
                 issue_chunk(c);
             }
             if (*abort_flag) {
@@ -223,14 +206,11 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                 const int c = b / P_CHUNK, k = b % P_CHUNK, s = c % P_STAGES, buf = b % P_TBUF;
                 if (k < P_MW && !wait_or_abort(full + s, (c / P_STAGES) & 1, abort_flag)) break;
                 umma::fence_after_sync();
-                PTL(1, b);
                 const uint32_t sa = smem_addr(stages + s * P_STAGE_BYTES + k * P_A_BLOCK);
                 const uint32_t sb = smem_addr(stages + s * P_STAGE_BYTES + P_CHUNK * P_A_BLOCK + k * P_B_BLOCK);
                 umma::mma_s8(tmem + buf * P_TOK, umma::smem_desc(sa, P_ROWS * 16, 128),
                              umma::smem_desc(sb, P_TOK * 16, 128), idesc, 0u);
-                PTL(4, b);
                 umma::commit(tfull + gi);
-                PTL(5, b);
                 // This thread's last block of the chunk. (A ragged last chunk may leave
                 // `empty` short of arrivals: nothing waits for it.)
                 if (k + P_MW >= P_CHUNK || b + P_MW >= nb) umma::commit(empty + s);
@@ -307,19 +287,14 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
         if (ok) ok = fetch(0, va);
         for (int b = 0; ok && b < nb; b += 2) {
             umma::wait_ld(va);
-            if (tid == 0) PTL(2, b);
             release(b);
-            if (tid == 0) PTL(6, b);
             if (b + 1 < nb && !fetch(b + 1, vb)) {
                 ok = false;
                 break;
             }
-            if (tid == 0) PTL(7, b);
             consume(b, va);
-            if (tid == 0) PTL(8, b);
             if (b + 1 < nb) {
                 umma::wait_ld(vb);
-                if (tid == 0) PTL(2, b + 1);
                 release(b + 1);
                 if (b + 2 < nb && !fetch(b + 2, va)) {
                     ok = false;
@@ -328,7 +303,6 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                 consume(b + 1, vb);
             }
         }
-        if (tid == 0) PTL(3, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             if (GATE_UP) {
@@ -365,10 +339,8 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
             }
         }
     }
-    if (tid == 0) PTL(3, 3);
     umma::fence_before_sync();
     __syncthreads();
-    if (tid == 0) PTL(3, 4);
     if (warp == P_EW + 1) umma::tmem_dealloc(tmem, P_TBUF * P_TOK);
     if (tid == 0 && s_abort) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
 }
@@ -558,6 +530,7 @@ size_t prefill_scale_elems(const MoeDims& d, bool gate_up) {
 }
 
 int prefill_max_token_tiles(int slots, int experts) { return (slots + P_TOK - 1) / P_TOK + experts; }
+int prefill_token_tile() { return P_TOK; }
 
 void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, int8_t* wt, float* wd, float* wc,
                           cudaStream_t stream) {
@@ -631,8 +604,3 @@ int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights
 
 }  // namespace tc
 
-#ifdef TC_TIMELINE
-extern "C" int tc_debug_prefill_timeline(long long* out) {
-    return int(cudaMemcpyFromSymbol(out, tc::g_ptl, sizeof(tc::g_ptl)));
-}
-#endif

@@ -97,18 +97,6 @@ struct RouteArgs {
     PeerPlan scatter;      // ranks > 0: the last CTA sends the rows to every rank instead of dispatching
 };
 
-#ifdef TC_TIMELINE
-__device__ long long g_route_tl[256][8];
-#define RTL(k)                                                                      \
-    do {                                                                            \
-        if (threadIdx.x == 0 && blockIdx.x < 256) g_route_tl[blockIdx.x][k] = clock64(); \
-    } while (0)
-#else
-#define RTL(k) \
-    do {       \
-    } while (0)
-#endif
-
 __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a) {
     extern __shared__ __align__(128) float smem[];
     float* xrow = smem;                 // [hidden] the block's input row (after the norm)
@@ -118,7 +106,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     __shared__ __align__(8) uint64_t s_wbar;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int hidden = a.hidden, experts = a.experts, topk = a.topk;
-    KTL_BEGIN(0)
     grid_launch_dependents();
     // The router matrix, one bulk copy per row, into rows padded by 32 bytes (so the four-thread
     // groups of a half-warp read distinct banks). Issued first: it lands while the row is normed.
@@ -139,13 +126,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // The router matrix is a constant: it streams in while the kernel in front of this
     // one (the previous block's combine) finishes. Everything below reads its output.
     grid_dependency_wait();
-    KTL_MARK(2)
     // A CTA walks tokens blockIdx.x, blockIdx.x + gridDim.x, ...: one each as launched today.
     bool w_landed = true;
     for (int token = blockIdx.x; token < a.t; token += gridDim.x) {
     if (token != int(blockIdx.x)) __syncthreads();  // the previous token's row and logits are no longer read
     const float* xin = a.x + size_t(token) * hidden;
-    RTL(0);
     for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
         *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
     __syncthreads();
@@ -161,7 +146,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         __syncthreads();
     }
 
-    RTL(1);
     // ---- logits. Four threads per expert, each holding four of the dot's
     // sixteen float lanes: thread q owns elements 16j+4q..16j+4q+3, so q = 0,1
     // hold the first 8-lane accumulator and q = 2,3 the second. The weights of
@@ -224,7 +208,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
     __syncthreads();
-    RTL(2);
 
     // ---- top-k and gates: warp 0. Lane l holds experts l, l+32, ...
     if (warp == 0) {
@@ -279,7 +262,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         }
     }
 
-    RTL(3);
     // ---- 8-bit quantization of the row, a warp per 32-block.
     const int nb = hidden / QK;
     const int padded = (nb + SUPER - 1) / SUPER * SUPER;
@@ -316,7 +298,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     }  // tokens of this CTA
 
     // ---- the dispatch, by the last CTA to get here (batches of up to one CTA's worth of tokens).
-    RTL(4);
     if (a.stage_router && !w_landed) {
         // The staged copy did not arrive within the spin limit (the logits came from
         // global memory instead). Report it, and give the copy a last bounded chance to
@@ -329,7 +310,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         __syncthreads();
         if (tid == 0) s_last = atomicAdd(a.ticket, 1) == a.t - 1;
         __syncthreads();
-        RTL(5);
         if (s_last) {
             __threadfence();
             if (a.scatter.ranks) {
@@ -340,15 +320,12 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
             } else {
                 DispatchSmem& sm = *reinterpret_cast<DispatchSmem*>(smem);
                 dispatch_small_body(sm, a.ids, a.t, experts, topk, a.counts, a.offsets, a.perm, a.pos,
-                                    a.slot_token, a.active);
+                                    a.slot_token, a.active, a.status);
             }
             if (tid == 0) *a.ticket = 0;  // ready for the next launch on this stream
         }
     }
-    RTL(6);
-    KTL_MARK(3)
 }
-
 
 // One warp per row.
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, float eps, int t, int n,
@@ -369,12 +346,6 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
 void init_kernels_route() {
     cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ROUTE_SMEM_LIMIT));
 }
-
-#ifdef TC_TIMELINE
-extern "C" int tc_debug_route_timeline(long long* out) {
-    return int(cudaMemcpyFromSymbol(out, g_route_tl, sizeof(g_route_tl)));
-}
-#endif
 
 int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x,
                  const float* norm_w, float eps, int t, Workspace& ws, cudaStream_t stream) {
@@ -426,4 +397,3 @@ int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, floa
 
 }  // namespace tc
 
-KTL_DUMP(tc_debug_ktl_route)

@@ -11,7 +11,7 @@ namespace {
 
 template <int N>
 __global__ void __launch_bounds__(128, 1)
-umma_probe_kernel(const int8_t* __restrict__ a_tile, const int8_t* __restrict__ b_tile, int* __restrict__ d_out,
+umma_selftest_kernel(const int8_t* __restrict__ a_tile, const int8_t* __restrict__ b_tile, int* __restrict__ d_out,
                   int* __restrict__ status) {
     __shared__ __align__(128) uint8_t s_a[128 * 32];
     __shared__ __align__(128) uint8_t s_b[N * 32];
@@ -67,12 +67,12 @@ umma_probe_kernel(const int8_t* __restrict__ a_tile, const int8_t* __restrict__ 
 
 // a_tile: 128 x 32 int8, b_tile: n x 32 int8, both in the canonical tile order;
 // d_out: 128 x n int32 row-major. n is 64 or 128.
-int launch_umma_probe(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
+int launch_umma_selftest(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,
                       cudaStream_t stream) {
     if (n == 64)
-        umma_probe_kernel<64><<<1, 128, 0, stream>>>(a_tile, b_tile, d_out, status);
+        umma_selftest_kernel<64><<<1, 128, 0, stream>>>(a_tile, b_tile, d_out, status);
     else if (n == 128)
-        umma_probe_kernel<128><<<1, 128, 0, stream>>>(a_tile, b_tile, d_out, status);
+        umma_selftest_kernel<128><<<1, 128, 0, stream>>>(a_tile, b_tile, d_out, status);
     else
         return -1;
     return 1;

@@ -55,6 +55,8 @@ SYMBOLS = {
     "tc_ep_expert_range": (_i, [_i, _i, _i, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "tc_ep_set_uniform_batch": (_i, [_vp, _i]),
     "tc_ep_enable_peer_exchange": (_i, [_vp, _i, _i, _i]),
+    "tc_ep_set_wait_limit": (_i, [_vp, C.c_uint32]),
+    "tc_ep_test_mute_signals": (_i, [_vp, _i]),
     "tc_ep_barrier": (_i, [_vp]),
     "tc_moe_ep_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "tc_umma_selftest": (_i, [_vp, _vp, _vp, _i, _vp]),

@@ -82,3 +82,31 @@ def test_default_threshold_switches_by_batch_size(oracle, ctx):
     small = forward(ctx, layer, x[:40], y0[:40])     # 10 per expert: bandwidth path
     layer.free()
     assert np.array_equal(big[:40], small)
+
+
+def test_scratch_shared_by_layers_only_grows(oracle, ctx):
+    """Two layers in one context share the token-tile scratch of the tensor-core path. A
+    wide layer is created first, then a narrow one that needs more tiles but fewer bytes
+    per tile; the wide layer's next prefill-size block must still fit (and be right)."""
+    wide = MoeShape("wide", 1024, 8, 2, 256, fmt="q8")
+    narrow = MoeShape("narrow", 256, 16, 4, 64, fmt="q8")
+    lw_w, lw_n = layer_weights(oracle, wide, 21), layer_weights(oracle, narrow, 22)
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    la = make_layer(ctx, lw_w, wide.topk, 600)
+    lb = make_layer(ctx, lw_n, narrow.topk, 1200)
+    ctx.set_prefill_threshold(0)
+    try:
+        for layer, shape, lw, t in [(la, wide, lw_w, 600), (lb, narrow, lw_n, 1200), (la, wide, lw_w, 600)]:
+            x = workloads.hidden_states(shape, t, seed=23)
+            y0 = np.zeros_like(x)
+            got = forward(ctx, layer, x, y0)
+            with oracle.fast_arithmetic_model():
+                from test_gpu_parity import oracle_moe
+
+                want = oracle_moe(oracle, lw, x, shape.topk).proj
+            assert np.abs(got - want).max() <= 2e-3
+            assert np.mean(np.all(got == want, axis=1)) > 0.5
+    finally:
+        ctx.set_prefill_threshold(32)
+        la.free()
+        lb.free()
