@@ -61,6 +61,8 @@ def parse_args():
                     help="N > 1: NVLink stores into mapped peer windows with flag waits (no NCCL call in a block), "
                          "all-gather + reduce-scatter of fixed size (both from a CUDA graph), or the "
                          "variable-size all-to-all enqueued directly")
+    ap.add_argument("--four-kernels", action="store_true",
+                    help="decode-size blocks as four kernels (router, gate_up, down, combine) instead of one")
     ap.add_argument("--no-overlap", action="store_true",
                     help="plain stream order between the kernels of a block (no programmatic dependent launch)")
     return ap.parse_args()
@@ -226,6 +228,8 @@ def main():
     ctx = cuda.Context(local_rank)
     if args.no_overlap:
         ctx.set_launch_overlap(False)
+    if args.four_kernels:
+        ctx.set_decode_block(False)
 
     if world == 1:
         weights_host, gen_s = build_weights(shape, args.layers, args.seed, host_threads)
@@ -371,6 +375,11 @@ def main():
     gu_bytes = (mean_u * eb_gu + args.batch * (shape.hidden + 4 * nbp)
                 + args.batch * shape.topk * shape.inter * 4)
     stage_ms = {k: v[0] / max(1, v[1]) for k, v in prof.items() if v[1]}
+    if "decode_block" in stage_ms:
+        one_kernel_block = True
+        gu_bytes = float(np.mean([workloads.decode_algorithmic_bytes(shape, args.batch, u) for u in distinct]))
+        stage_ms["gate_up"] = stage_ms["decode_block"]
+        stage_ms["down"] = stage_ms["decode_block"]
     gu_ms = stage_ms["gate_up"]
     achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
     total_prof = sum(v[0] for v in prof.values())

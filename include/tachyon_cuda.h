@@ -62,6 +62,12 @@ int tc_set_launch_overlap(tc_ctx *ctx, int on);
  * = never. Both give the same values (same fma chain per output). */
 int tc_set_prefill_threshold(tc_ctx *ctx, int avg_tokens_per_expert);
 
+/* Decode-size blocks (up to 32 tokens, 8-bit or 4-bit experts, default arithmetic) run
+ * as ONE kernel whose CTAs meet at grid-wide counters (no counterpart in the reference,
+ * whose Metal backend encodes a dispatch per step: src/gpu/mod.rs:651-702). On by
+ * default; off = the four-kernel path. Both give the same values. */
+int tc_set_decode_block(tc_ctx *ctx, int on);
+
 /* ---- device buffers: replace tm_buffer / tm_buffer_contents / tm_buffer_free
  *      (src/gpu/mod.rs:125-127). HBM is not host-visible, hence the copies. */
 void *tc_malloc(tc_ctx *ctx, size_t bytes);
@@ -216,10 +222,19 @@ float tc_timer_stop_ms(tc_ctx *ctx);
  * the library enqueues is bracketed by CUDA events on the context's stream.
  * tc_profile_read() waits, then adds up milliseconds and launches per stage
  * since the last read: stage 0 route, 1 dispatch, 2 gate_up, 3 quantize
- * hidden, 4 down, 5 combine, 6 rmsnorm (TC_PROFILE_STAGES entries each). */
+ * hidden, 4 down, 5 combine, 6 rmsnorm, 7 the one-kernel decode block
+ * (TC_PROFILE_STAGES entries each). */
 #define TC_PROFILE_STAGES 8
 int tc_profile_enable(tc_ctx *ctx, int on);
 int tc_profile_read(tc_ctx *ctx, float *ms, uint64_t *launches);
+
+/* Phase timing inside the one-kernel decode block. While on, CTA 0 of every such
+ * kernel stores the GPU's wall clock (ns) at: entry, after its wait for the previous
+ * kernel, after the router phase, after gate_up, after down, at exit.
+ * tc_profile_read_phases() waits for the stream and returns the six stamps of the
+ * last block that ran (also from a replayed graph captured while this was on). */
+int tc_profile_phases(tc_ctx *ctx, int on);
+int tc_profile_read_phases(tc_ctx *ctx, uint64_t *ns6);
 
 /* Number of kernel launches this context has enqueued so far. */
 uint64_t tc_launch_count(tc_ctx *ctx);

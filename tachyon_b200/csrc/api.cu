@@ -37,6 +37,9 @@ struct tc_ctx {
     float* host_x = nullptr;  // device staging for the host-buffer entry point
     float* host_y = nullptr;
     size_t host_elems = 0;
+    bool decode_block = true;      // decode-size blocks as one kernel (moe_decode.cu)
+    uint32_t grid_spin_limit = 1u << 22;
+    unsigned long long* phase_stamps = nullptr;  // device [8], while phase profiling is on
     int* static_status = nullptr;  // status word of tc_dispatch_static on this device, once it has been used
 };
 
@@ -54,6 +57,7 @@ struct tc_moe_layer {
     float* bias = nullptr;
     int max_tokens;
     int last_t = 0;
+    bool dispatch_stale = false;       // the last forward built no dispatch (one-kernel block): built on demand
     uint8_t* gate_up_tiled = nullptr;  // the fast kernels' record layout of the two expert matrices
     uint8_t* down_tiled = nullptr;
     tc::PrefillWeights pw;             // the tcgen05 kernels' tiles of the two expert matrices
@@ -211,6 +215,7 @@ bool ws_reserve(tc_ctx* ctx, const tc::MoeDims& d, int max_tokens) {
     cudaMemset(w.ticket, 0, sizeof(int));
     cudaMemset(w.grid_sync, 0, tc::GRID_SYNC_WORDS * sizeof(uint32_t));
     w.max_tokens = T;
+    w.sms = ctx->sms;
     w.hidden = n.hidden;
     w.experts = n.experts;
     w.topk = n.topk;
@@ -250,6 +255,7 @@ tc_ctx* tc_create(int device_ordinal, char* err, size_t errlen) {
     tc::init_kernels_fast();
     tc::init_kernels_route();
     tc::init_kernels_prefill();
+    tc::init_kernels_decode();
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_start) != cudaSuccess ||
         cudaEventCreate(&ctx->ev_stop) != cudaSuccess) {
@@ -267,6 +273,7 @@ void tc_destroy(tc_ctx* ctx) {
     for (void* q : ctx->pre_allocs) cudaFree(q);
     if (ctx->host_x) cudaFree(ctx->host_x);
     if (ctx->host_y) cudaFree(ctx->host_y);
+    if (ctx->phase_stamps) cudaFree(ctx->phase_stamps);
     tc::ep_destroy(ctx->ep);
     for (cudaEvent_t e : ctx->ev_pool) cudaEventDestroy(e);
     cudaEventDestroy(ctx->ev_start);
@@ -374,6 +381,33 @@ int tc_set_launch_overlap(tc_ctx* ctx, int on) {
     (void)ctx;
     tc::g_launch_overlap = on != 0;
     return 0;
+}
+
+int tc_set_decode_block(tc_ctx* ctx, int on) {
+    ctx->decode_block = on != 0;
+    return 0;
+}
+
+int tc_profile_phases(tc_ctx* ctx, int on) {
+    if (on && !ctx->phase_stamps) {
+        cudaSetDevice(ctx->device);
+        if (!cuda_ok(ctx, cudaMalloc(reinterpret_cast<void**>(&ctx->phase_stamps), 8 * sizeof(unsigned long long)),
+                     "cudaMalloc(phase stamps)"))
+            return -1;
+        cudaMemset(ctx->phase_stamps, 0, 8 * sizeof(unsigned long long));
+    } else if (!on && ctx->phase_stamps) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->phase_stamps);
+        ctx->phase_stamps = nullptr;
+    }
+    return 0;
+}
+
+int tc_profile_read_phases(tc_ctx* ctx, uint64_t* ns6) {
+    if (!ctx->phase_stamps) return fail(ctx, "phase profiling is off");
+    if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return -1;
+    return cuda_ok(ctx, cudaMemcpy(ns6, ctx->phase_stamps, 6 * sizeof(uint64_t), cudaMemcpyDeviceToHost),
+                   "phase stamp readback") ? 0 : -1;
 }
 
 int tc_set_prefill_threshold(tc_ctx* ctx, int avg_tokens_per_expert) {
@@ -690,11 +724,27 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
         if (!cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
         return 0;
     }
+    const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
+    layer->dispatch_stale = false;
+    if (!lanes && ctx->decode_block &&
+        tc::decode_block_applies(d, layer->gate_up->dev.kind, layer->down->dev.kind, t)) {
+        // Decode-size batch: the whole block is one kernel (no dispatch is built).
+        n += staged(ctx, 7, [&] {
+            return tc::launch_decode_block(d, layer->gate_up->dev.kind,
+                                           static_cast<const uint16_t*>(layer->router->dev.data), layer->bias, x,
+                                           norm_w, eps, t, y, layer->gate_up_tiled, layer->down_tiled, ws, ctx->sms,
+                                           ctx->grid_spin_limit, ctx->phase_stamps, s);
+        });
+        ctx->launches += n;
+        layer->last_t = t;
+        layer->dispatch_stale = true;
+        if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
+        return 0;
+    }
     n += staged(ctx, 0, [&] {
         return tc::launch_route(d, static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
                                 x, norm_w, eps, t, ws, s);
     });
-    const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
     const bool prefill = !lanes && layer->pw.gu_t &&
                          (long long)t * d.topk >= (long long)ctx->prefill_min_avg * d.experts;
     if (prefill) {
@@ -767,9 +817,26 @@ int tc_moe_forward_host(tc_moe_layer* layer, const float* x_host, int t, float* 
     return tc_sync(ctx);
 }
 
+}  // extern "C"
+
+namespace {
+// The one-kernel block keeps no dispatch; the taps below build it from the ids it left.
+int refresh_dispatch(tc_moe_layer* layer) {
+    tc_ctx* ctx = layer->ctx;
+    if (!layer->dispatch_stale) return 0;
+    if (ctx->capturing) return fail(ctx, "the routing taps cannot run inside a capture");
+    ctx->launches += tc::launch_dispatch(layer->dims, layer->last_t, ctx->ws, ctx->stream);
+    layer->dispatch_stale = false;
+    return cuda_ok(ctx, cudaGetLastError(), "dispatch launch") ? 0 : -1;
+}
+}  // namespace
+
+extern "C" {
+
 int tc_moe_last_routing(tc_moe_layer* layer, uint32_t* ids, float* gates, uint32_t* counts,
                         float* logits) {
     tc_ctx* ctx = layer->ctx;
+    if (refresh_dispatch(layer) != 0) return -1;
     if (tc_sync(ctx) != 0) return -1;
     const tc::MoeDims& d = layer->dims;
     size_t slots = size_t(layer->last_t) * d.topk;
@@ -785,6 +852,7 @@ int tc_moe_last_routing(tc_moe_layer* layer, uint32_t* ids, float* gates, uint32
 
 int tc_moe_last_dispatch(tc_moe_layer* layer, uint32_t* offsets, uint32_t* perm) {
     tc_ctx* ctx = layer->ctx;
+    if (refresh_dispatch(layer) != 0) return -1;
     if (tc_sync(ctx) != 0) return -1;
     const tc::MoeDims& d = layer->dims;
     if (offsets && !cuda_ok(ctx, cudaMemcpy(offsets, ctx->ws.offsets, size_t(d.experts + 1) * 4,

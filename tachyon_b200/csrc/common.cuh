@@ -73,6 +73,7 @@ struct RunList {
 
 struct Workspace {
     int max_tokens = 0, hidden = 0, experts = 0, topk = 0, inter = 0;
+    int sms = 0;                  // multiprocessors of the context's device
     float* logits = nullptr;      // [T, E]
     uint32_t* ids = nullptr;      // [T, k] descending score order
     float* gates = nullptr;       // [T, k]
@@ -287,6 +288,18 @@ int launch_umma_selftest(const int8_t* a_tile, const int8_t* b_tile, int n, int*
                       cudaStream_t stream);
 
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);
+
+// ---- the whole block of a decode-size batch as one kernel (moe_decode.cu)
+void init_kernels_decode();
+// True if a block of t tokens of this shape can take the one-kernel path.
+bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t);
+// y[t, hidden] += moe(x) (or moe(rmsnorm(x)) when norm_w is set). Leaves the routing in
+// ws.ids / ws.gates / ws.logits and the 8-bit rows in ws.xq / ws.xs; builds no dispatch.
+// stamps: null, or 8 words that CTA 0 fills with the wall clock at its phase boundaries.
+int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
+                        const float* norm_w, float eps, int t, float* y, const uint8_t* gate_up_tiled,
+                        const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit,
+                        unsigned long long* stamps, cudaStream_t stream);
 
 int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, float* out,
                    cudaStream_t stream);

@@ -31,7 +31,7 @@
 //    16 tokens at a time, usually the whole range) are staged once per CTA:
 //    int8 rows by bulk copies, their scales transposed by plain loads; for the
 //    down projection the SwiGLU rows are quantized as they are staged.
-#include "experts_common.cuh"
+#include "experts_fast.cuh"
 
 namespace tc {
 
@@ -39,22 +39,10 @@ namespace {
 
 constexpr int F_MAX_WARPS = 16;   // warps per CTA: 16, or fewer when that buys a deeper ring
 constexpr int F_XBUF = 2;         // segments whose tokens are staged at the same time
-constexpr int F_KC = 256;         // columns per record
-constexpr int F_NBC = F_KC / QK;  // blocks per record
-constexpr int F_ROWS = 16;        // weight rows per unit (one m16 tile)
 constexpr int F_GMAX = 2;         // token tiles of 8 held in registers
 constexpr int F_TOK = 8 * F_GMAX; // tokens staged per segment
 constexpr int F_MAX_STAGES = 6;
 constexpr size_t F_SMEM_LIMIT = 227 * 1024;
-
-template <int KIND>
-struct Rec {
-    // 8-bit: 16 rows x (256 weights + 8 f16 scales).
-    // 4-bit: 16 rows x (128 nibble bytes + words 0..3 of the super-block), then
-    //        word 4 of each row.
-    static constexpr int ROW_STRIDE = KIND == 1 ? F_KC + 16 : F_KC / 2 + 16;
-    static constexpr int BYTES = KIND == 1 ? F_ROWS * ROW_STRIDE : F_ROWS * ROW_STRIDE + F_ROWS * 4;
-};
 
 struct FastArgs {
     ExpertArgs e;
@@ -89,54 +77,6 @@ struct Layout {
     __host__ __device__ int xsT(int buf) const { return x0 + buf * xbytes + xs_off; }
     __host__ __device__ int xsumT(int buf) const { return x0 + buf * xbytes + xsum_off; }
 };
-
-// Shared-memory reads below are plain (non-volatile) asm so the compiler may
-// interleave them across unrolled blocks; what keeps them behind the mbarrier
-// wait that made their data visible is the `token` operand, a value that wait
-// produced.
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t token, int& r0, int& r1, int& r2, int& r3) {
-    asm("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4]; // %5"
-        : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
-        : "r"(addr), "r"(token));
-}
-
-__device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t token, int& r0, int& r1) {
-    asm("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2]; // %3" : "=r"(r0), "=r"(r1) : "r"(addr), "r"(token));
-}
-
-// D = A(16x32 s8, row) * B(32x8 s8, col) + c, s32 accumulate.
-__device__ __forceinline__ void mma_s8(int (&d)[4], int a0, int a1, int a2, int a3, int b0, int b1,
-                                       int c) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};"
-        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c));
-}
-
-__device__ __forceinline__ uint32_t lds32(uint32_t addr, uint32_t token) {
-    uint32_t v;
-    asm("ld.shared.u32 %0, [%1]; // %2" : "=r"(v) : "r"(addr), "r"(token));
-    return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr, uint32_t token) {
-    uint4 v;
-    asm("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4]; // %5"
-        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-        : "r"(addr), "r"(token));
-    return v;
-}
-__device__ __forceinline__ float2 lds_f2(uint32_t addr, uint32_t token) {
-    float2 v;
-    asm("ld.shared.v2.f32 {%0,%1}, [%2]; // %3" : "=f"(v.x), "=f"(v.y) : "r"(addr), "r"(token));
-    return v;
-}
-
-// f16 bits of a weight scale (finite, as every scale Tachyon stores is) to f32
-// on the full-rate pipes: the bits shifted into place, times 2^112
-// (src/kernels.rs:127-130). Exact for normals and subnormals of either sign.
-__device__ __forceinline__ float f16_scale_to_f32(uint32_t h) {
-    return __uint_as_float(((h & 0x8000u) << 16) | ((h & 0x7FFFu) << 13)) * __uint_as_float(0x77800000u);
-}
 
 // A warp's place in its sequence of (expert, token segment, unit, chunk) steps.
 // Units are numbered over the experts that have tokens; a CTA owns [lo, hi).
@@ -210,126 +150,6 @@ struct FWalker {
         return f.tiled + (size_t(cur.e * upe + u) * nchunks + cur.c) * Rec<KIND>::BYTES;
     }
 };
-
-// One record (16 rows x up to 8 blocks) against G tiles of 8 staged tokens.
-template <int KIND, int G>
-__device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t xsT_s, uint32_t xsumT_s,
-                                           int x_stride, int nblk, int blk0, int lane, uint32_t wtok,
-                                           uint32_t xtok, float (&acc)[F_GMAX][4],
-                                           float (&off)[F_GMAX][4]) {
-    using R = Rec<KIND>;
-    const int g = lane >> 2, t = lane & 3;
-    const int mat = lane >> 3, mr = lane & 7;
-    // This thread's two rows' scales for the record's eight blocks.
-    float wd[2][F_NBC], wc[2][F_NBC];
-    if (KIND == 1) {
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC, wtok);
-            const uint32_t hw[4] = {s.x, s.y, s.z, s.w};
-#pragma unroll
-            for (int b = 0; b < F_NBC; b++) wd[h][b] = f16_scale_to_f32((hw[b >> 1] >> (16 * (b & 1))) & 0xFFFFu);
-        }
-    } else {
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC / 2, wtok);
-            const uint32_t o23 = lds32(rec + F_ROWS * R::ROW_STRIDE + (g + 8 * h) * 4, wtok);
-            const float step_d = f16_bits_to_f32(uint16_t(s.x)), step_c = f16_bits_to_f32(uint16_t(s.x >> 16));
-#pragma unroll
-            for (int b = 0; b < F_NBC; b++) {
-                wd[h][b] = step_d * float(((b < 4 ? s.y : s.z) >> (8 * (b & 3))) & 0xFFu);
-                wc[h][b] = step_c * float(int(int8_t(uint8_t((b < 4 ? s.w : o23) >> (8 * (b & 3))))));
-            }
-        }
-    }
-    uint32_t a_addr;
-    if (KIND == 1)
-        a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE + (mat >> 1) * 16;
-    else
-        a_addr = rec + (mr + (mat & 1) * 8) * R::ROW_STRIDE;
-    // B: token row (mr) of a tile, 16-byte half (mat & 1) of block b + (mat >> 1).
-    const uint32_t b_addr = xq_s + mr * x_stride + blk0 * 32 + (mat & 1) * 16 + (mat >> 1) * 32;
-    // Four blocks at a time, in three phases so that the loads, the matrix
-    // instructions and the float chains of different blocks overlap: all
-    // operand loads, then all matrix instructions, then the scaling.
-#pragma unroll
-    for (int h4 = 0; h4 < F_NBC; h4 += 4) {
-        if (h4 < nblk) {
-            int A[4][4];
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                if (KIND == 1) {
-                    ldmatrix_x4(a_addr + (h4 + k) * 32, wtok, A[k][0], A[k][1], A[k][2], A[k][3]);
-                } else {
-                    // Word t of rows g and g+8: low nibbles are elements 4t..4t+3,
-                    // high nibbles elements 16+4t..16+4t+3.
-                    int w0, w1;
-                    ldmatrix_x2(a_addr + (h4 + k) * 16, wtok, w0, w1);
-                    A[k][0] = nibbles_minus8(uint32_t(w0) & 0x0F0F0F0Fu);
-                    A[k][2] = nibbles_minus8((uint32_t(w0) >> 4) & 0x0F0F0F0Fu);
-                    A[k][1] = nibbles_minus8(uint32_t(w1) & 0x0F0F0F0Fu);
-                    A[k][3] = nibbles_minus8((uint32_t(w1) >> 4) & 0x0F0F0F0Fu);
-                }
-            }
-#pragma unroll
-            for (int n0 = 0; n0 < G; n0 += 2) {
-                constexpr int PAIR = 2;
-                int B[PAIR][4][2];
-                float2 XS[PAIR][4], SU[PAIR][4];
-#pragma unroll
-                for (int p = 0; p < PAIR; p++) {
-                    if (n0 + p < G) {
-                        const uint32_t row = b_addr + (n0 + p) * 8 * x_stride + h4 * 32;
-                        ldmatrix_x4(row, xtok, B[p][0][0], B[p][0][1], B[p][1][0], B[p][1][1]);
-                        ldmatrix_x4(row + 64, xtok, B[p][2][0], B[p][2][1], B[p][3][0], B[p][3][1]);
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            const uint32_t so = ((blk0 + h4 + k) * F_TOK + (n0 + p) * 8 + 2 * t) * 4;
-                            XS[p][k] = lds_f2(xsT_s + so, xtok);
-                            if (KIND == 2) SU[p][k] = lds_f2(xsumT_s + so, xtok);
-                        }
-                    }
-                }
-                int D[PAIR][4][4];
-#pragma unroll
-                for (int p = 0; p < PAIR; p++)
-                    if (n0 + p < G) {
-#pragma unroll
-                        for (int k = 0; k < 4; k++)
-                            mma_s8(D[p][k], A[k][0], A[k][1], A[k][2], A[k][3], B[p][k][0], B[p][k][1], MAGIC_I);
-                    }
-#pragma unroll
-                for (int p = 0; p < PAIR; p++)
-                    if (n0 + p < G) {
-                        const int nt = n0 + p;
-#pragma unroll
-                        for (int k = 0; k < 4; k++) {
-                            if (h4 + k < nblk) {
-                                const int b = h4 + k;
-                                const float2 magic = make_float2(MAGIC_F, MAGIC_F);
-#pragma unroll
-                                for (int h = 0; h < 2; h++) {  // rows g and g+8; tokens 2t, 2t+1 side by side
-                                    const float2 sum = sub2(make_float2(__int_as_float(D[p][k][2 * h]),
-                                                                        __int_as_float(D[p][k][2 * h + 1])), magic);
-                                    const float2 d = mul2(make_float2(wd[h][b], wd[h][b]), XS[p][k]);
-                                    const float2 r = fma2(sum, d, make_float2(acc[nt][2 * h], acc[nt][2 * h + 1]));
-                                    acc[nt][2 * h] = r.x;
-                                    acc[nt][2 * h + 1] = r.y;
-                                    if (KIND == 2) {
-                                        const float2 o = fma2(make_float2(wc[h][b], wc[h][b]), SU[p][k],
-                                                              make_float2(off[nt][2 * h], off[nt][2 * h + 1]));
-                                        off[nt][2 * h] = o.x;
-                                        off[nt][2 * h + 1] = o.y;
-                                    }
-                                }
-                            }
-                        }
-                    }
-            }
-        }
-    }
-}
 
 // One segment of the CTA's walk: an expert and up to F_TOK of its tokens.
 struct Segment {
@@ -576,9 +396,9 @@ __global__ void __launch_bounds__(F_MAX_WARPS * 32, 1) expert_fast_kernel(const 
                 const int nblk = min(F_NBC, nb - cons.c * F_NBC);
                 const int blk0 = cons.c * F_NBC;
                 if (sg.G == 1)
-                    fast_chunk<KIND, 1>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
+                    fast_chunk<KIND, 1, F_GMAX>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 else if (sg.G == 2)  // (0: an expert without tokens in a dense walk; its records are only drained)
-                    fast_chunk<KIND, 2>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
+                    fast_chunk<KIND, 2, F_GMAX>(rec, xq_s, xsT_s, xsumT_s, f.x_stride, nblk, blk0, lane, wtok, xtok, acc, off);
                 __syncwarp();
 
                 if (cons.c == wk.nchunks - 1) {

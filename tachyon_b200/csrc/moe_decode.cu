@@ -1,0 +1,610 @@
+// The whole MoE block of a decode-size batch (up to 32 tokens) as ONE kernel:
+// [RMSNorm +] router + top-k + gates + row quantization, gate_up + SwiGLU, down,
+// weighted combine + residual add, by persistent CTAs (one per SM) that meet at
+// three grid-wide arrival counters instead of at kernel boundaries.
+//
+// Why one kernel. At these sizes the block is a chain of short dependent steps around
+// one large stream of bytes (the selected experts' weights, read once). As four
+// launches, each step paid a launch boundary and its own ramp, and HBM idled through
+// the router and the combine. Here the weight stream is decoupled from the steps:
+//  - Every warp owns a private ring of shared-memory stages and a fixed sequence of
+//    weight records: its 16-row units of gate_up, then its units of down. Lane 0
+//    keeps the ring full with bulk async copies (cp.async.bulk + mbarrier); the copies
+//    for the next step land while the current one computes.
+//  - For batches that reach nearly every expert (dense_walk) the partition of units
+//    over CTAs and warps does not depend on the routing, so the ring starts filling
+//    before the kernel even waits for the previous kernel in the stream
+//    (programmatic dependent launch), and keeps filling through the router phase.
+//    Smaller batches walk only the experts that were picked: their sequence is known
+//    after the router phase.
+//  - The router phase runs on CTAs 0..t-1 (a token each); the others only stream.
+//    The combine runs on the same CTAs; the rest have exited by then, which lets the
+//    next block's kernel start streaming its weights under this block's combine.
+//
+// No token -> expert permutation is built: with at most 32 tokens every CTA keeps
+// the batch's expert ids in shared memory and lists, per expert of its range, the
+// (token, pick) slots that named it (ascending tokens, the order of the per-expert
+// lists of src/model.rs:474-482). SwiGLU rows and expert outputs are stored by slot
+// (token * k + pick).
+//
+// Arithmetic: identical to the grouped kernels (experts_fast.cuh: one fma chain per
+// output over the exact integer block sums), the router and quantization of
+// route_common.cuh, and the combine order of combine.cu (ascending expert, product
+// rounded then added: src/model.rs:513-519, src/kernels.rs:606-610), so a token's
+// output has the same bits whichever path ran.
+//
+// Every wait is bounded: staged copies (mbar_wait_bounded) and the grid-wide counters
+// (grid_wait). A wait that runs out sets the status word, and the CTA skips to the end,
+// waits (bounded) for its copies in flight and returns; tc_sync reports it and clears
+// the counters.
+#include "experts_fast.cuh"
+#include "route_common.cuh"
+
+namespace tc {
+
+namespace {
+
+constexpr int D_MAX_WARPS = 16;
+constexpr int D_MAX_STAGES = 8;
+constexpr int D_GMAX = 4;          // token tiles of 8 held in registers
+constexpr int D_TOK = 8 * D_GMAX;  // tokens per block this kernel takes; rows staged at a time
+constexpr int D_NSEG = 4;          // experts of a CTA's range whose slot lists are held at a time
+constexpr size_t D_SMEM_LIMIT = 227 * 1024;
+
+struct DecodeArgs {
+    // router phase
+    const uint16_t* router;
+    const float* bias;
+    const float* x;       // [t, hidden] normed input, or the residual stream when norm_w is set
+    const float* norm_w;
+    float eps;
+    float* y;             // [t, hidden] residual stream: y += moe(x)
+    int t, hidden, experts, topk, inter;
+    float* logits;
+    uint32_t* ids;
+    float* gates;
+    int8_t* xq;
+    float* xs;
+    float* xsum;
+    // expert phases
+    const uint8_t* gu_tiled;  // records [expert][unit][chunk]
+    const uint8_t* dn_tiled;
+    float* hidden_f;          // [t * k, inter] SwiGLU rows by slot
+    float* out;               // [t * k, hidden] expert outputs by slot
+    int stages, xcap;         // ring depth per warp; staged rows at a time (a multiple of 8, at most D_TOK)
+    int dense;
+    uint32_t* sync;           // [GRID_SYNC_WORDS], zero between launches
+    uint32_t spin_limit;
+    int* status;
+    unsigned long long* stamps;  // when set: CTA 0 stores the wall clock (ns) at its phase boundaries [8]
+};
+
+// Shared memory carve-up (bytes). The token area is reused by the phases: the router's
+// row and logits, then gate_up's staged rows, then down's.
+template <int KIND>
+struct DLayout {
+    int ring, x0, xbytes, ids, lists, bars, total;
+    __host__ __device__ DLayout(int nwarps, int stages, int xcap, int hidden, int inter, int experts, int topk) {
+        int o = nwarps * stages * Rec<KIND>::BYTES;
+        ring = 0;
+        o = (o + 127) / 128 * 128;
+        x0 = o;
+        const int cols = hidden > inter ? hidden : inter;
+        const int nbp = (cols / QK + 7) / 8 * 8;
+        xbytes = xcap * (cols + 16) + nbp * D_TOK * 4 * (KIND == 2 ? 2 : 1);
+        const int route_bytes = (hidden + experts) * 4 + 64;
+        if (xbytes < route_bytes) xbytes = route_bytes;
+        xbytes = (xbytes + 127) / 128 * 128;
+        o += xbytes;
+        ids = o;
+        o += D_TOK * topk * 4;
+        lists = o;
+        o += D_NSEG * D_TOK * 2;
+        o = (o + 15) / 16 * 16;
+        bars = o;
+        o += D_MAX_WARPS * D_MAX_STAGES * 8;
+        total = o;
+    }
+};
+
+__device__ __forceinline__ uint32_t ld_acquire(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One thread: waits until *ctr >= target, at most `limit` polls.
+__device__ __forceinline__ bool grid_wait(const uint32_t* ctr, uint32_t target, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++) {
+        if (ld_acquire(ctr) >= target) return true;
+        __nanosleep(32);
+    }
+    return false;
+}
+
+__device__ __forceinline__ unsigned long long wall_clock_ns() {
+    unsigned long long v;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
+    return v;
+}
+
+// After a CTA barrier: this CTA's writes so far are ordered before its arrival.
+__device__ __forceinline__ void grid_arrive(uint32_t* ctr) {
+    __threadfence();
+    atomicAdd(ctr, 1u);
+}
+
+// One of the two expert phases' description.
+struct Phase {
+    const uint8_t* tiled;
+    int cols, upe, nchunks, nb, nbp, x_stride;
+    int lo, hi;        // this CTA's units, in walk space (all experts, or the picked ones)
+    int first, n;      // this warp's first unit and how many it owns (stride nwarps)
+};
+
+template <int KIND>
+__global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const DecodeArgs a) {
+    using R = Rec<KIND>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ float s_inv;
+    __shared__ int s_abort;
+    __shared__ int s_nactive;
+    __shared__ int s_seg_count[D_NSEG];
+    __shared__ uint8_t s_picked[MAX_EXPERTS];
+    __shared__ uint16_t s_active[MAX_EXPERTS];
+    __shared__ uint32_t s_cpos[MAX_TOPK];
+    __shared__ float s_cgate[MAX_TOPK];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = blockDim.x >> 5, nthreads = blockDim.x;
+    const int bid = blockIdx.x, nctas = gridDim.x;
+    const int STAGES = a.stages;
+    const int t = a.t, hidden = a.hidden, experts = a.experts, topk = a.topk, inter = a.inter;
+    const int slots = t * topk;
+    const DLayout<KIND> L(nwarps, STAGES, a.xcap, hidden, inter, experts, topk);
+    uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * D_MAX_STAGES;
+    uint32_t* s_ids = reinterpret_cast<uint32_t*>(smem + L.ids);
+    uint16_t* s_lists = reinterpret_cast<uint16_t*>(smem + L.lists);
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (tid == 0) s_abort = 0;
+    __syncthreads();
+    grid_launch_dependents();
+    const bool stamping = a.stamps && bid == 0 && tid == 0;
+    if (stamping) a.stamps[0] = wall_clock_ns();
+
+    // ---- the two expert phases and this warp's record sequence: gate_up records, then down's
+    Phase ph[2];
+    ph[0].tiled = a.gu_tiled, ph[0].cols = hidden, ph[0].upe = (inter + 7) / 8;
+    ph[1].tiled = a.dn_tiled, ph[1].cols = inter, ph[1].upe = (hidden + 15) / 16;
+#pragma unroll
+    for (int p = 0; p < 2; p++) {
+        ph[p].nchunks = (ph[p].cols + F_KC - 1) / F_KC;
+        ph[p].nb = ph[p].cols / QK;
+        ph[p].nbp = (ph[p].nb + 7) / 8 * 8;
+        ph[p].x_stride = ph[p].cols + 16;
+    }
+    auto partition = [&](int walk_experts) {
+#pragma unroll
+        for (int p = 0; p < 2; p++) {
+            const int total = walk_experts * ph[p].upe;
+            ph[p].lo = int((long long)bid * total / nctas);
+            ph[p].hi = int((long long)(bid + 1) * total / nctas);
+            ph[p].first = ph[p].lo + warp;
+            ph[p].n = ph[p].first < ph[p].hi ? (ph[p].hi - ph[p].first + nwarps - 1) / nwarps : 0;
+        }
+    };
+    auto expert_of = [&](int walk_index) { return a.dense ? walk_index : int(s_active[walk_index]); };
+    // Producer cursor over the warp's sequence.
+    uint32_t fills = 0, takes = 0;
+    int pp = 0, pu = 0, pc = 0;  // phase, unit ordinal within the warp's share, chunk
+    uint32_t nrec = 0;
+    auto fill_next = [&]() {
+        while (pp < 2 && pu >= ph[pp].n) pp++, pu = 0, pc = 0;
+        if (pp >= 2) return;
+        const Phase& P = ph[pp];
+        const int wu = P.first + pu * nwarps;              // unit in walk space
+        const int e = expert_of(wu / P.upe);
+        const size_t flat = size_t(e) * P.upe + wu % P.upe;  // unit in the tiled matrix
+        if (lane == 0) {
+            uint64_t* bar = bars + fills % STAGES;
+            mbar_expect_tx(bar, R::BYTES);
+            bulk_copy(ring + (fills % STAGES) * R::BYTES, P.tiled + (flat * P.nchunks + pc) * R::BYTES, R::BYTES, bar);
+        }
+        fills++;
+        if (++pc == P.nchunks) pc = 0, pu++;
+    };
+    if (a.dense) {
+        // The partition does not depend on the routing: the ring fills before this grid waits
+        // for the kernel in front of it, and through the router phase.
+        partition(experts);
+        nrec = uint32_t(ph[0].n * ph[0].nchunks + ph[1].n * ph[1].nchunks);
+        while (fills < nrec && fills < uint32_t(STAGES)) fill_next();
+    }
+    grid_dependency_wait();  // everything below reads or writes what other kernels touch
+    if (stamping) a.stamps[1] = wall_clock_ns();
+
+    // ---- router phase: CTA i < t takes token i
+    if (bid < t) {
+        float* xrow = reinterpret_cast<float*>(smem + L.x0);
+        float* slog = xrow + hidden;
+        const float* xin = a.x + size_t(bid) * hidden;
+        for (int c = tid * 4; c < hidden; c += nthreads * 4)
+            *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
+        __syncthreads();
+        if (a.norm_w) route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, nthreads);
+        route_logits(a.router, nullptr, 0, xrow, a.bias, hidden, experts, slog,
+                     a.logits ? a.logits + size_t(bid) * experts : nullptr, tid, nthreads);
+        __syncthreads();
+        if (warp == 0)
+            route_topk_gates(slog, experts, topk, a.ids + size_t(bid) * topk, a.gates + size_t(bid) * topk, lane);
+        route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * ph[0].nbp,
+                           a.xsum + size_t(bid) * ph[0].nbp, warp, lane, 1, nwarps - 1);
+        __syncthreads();
+        if (tid == 0) grid_arrive(a.sync + 0);
+    }
+    bool ok = true;
+    if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) s_abort = 1;
+    __syncthreads();
+    ok = !s_abort;
+    if (stamping) a.stamps[2] = wall_clock_ns();
+
+    // ---- the batch's expert ids; for small batches the experts that were picked
+    if (ok) {
+        for (int i = tid; i < slots; i += nthreads) s_ids[i] = __ldcg(a.ids + i);
+        if (!a.dense)
+            for (int e = tid; e < experts; e += nthreads) s_picked[e] = 0;
+        __syncthreads();
+        if (!a.dense) {
+            for (int i = tid; i < slots; i += nthreads) s_picked[s_ids[i]] = 1;
+            __syncthreads();
+            if (warp == 0) {
+                int n = 0;
+                for (int e0 = 0; e0 < experts; e0 += 32) {
+                    const int e = e0 + lane;
+                    const bool on = e < experts && s_picked[e];
+                    const unsigned ballot = __ballot_sync(0xffffffffu, on);
+                    if (on) s_active[n + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(e);
+                    n += __popc(ballot);
+                }
+                if (lane == 0) s_nactive = n;
+            }
+            __syncthreads();
+            partition(s_nactive);
+            nrec = uint32_t(ph[0].n * ph[0].nchunks + ph[1].n * ph[1].nchunks);
+            while (fills < nrec && fills < uint32_t(STAGES)) fill_next();
+        }
+    }
+
+    const int g = lane >> 2, tq = lane & 3;
+    float acc[D_GMAX][4], off[D_GMAX][4];
+    uint32_t xphase = 0, xtok = 0;
+    int arrived = 0;  // expert phases this CTA has announced
+
+#pragma unroll 1
+    for (int p = 0; p < 2 && ok; p++) {
+        const Phase& P = ph[p];
+        const bool gate_up = p == 0;
+        int cu = 0, cc = 0;  // consumer cursor: unit ordinal, chunk
+        const int xs_off = a.xcap * P.x_stride;
+        const int xsum_off = xs_off + P.nbp * D_TOK * 4;
+        float* xsT = reinterpret_cast<float*>(smem + L.x0 + xs_off);
+        float* xsumT = reinterpret_cast<float*>(smem + L.x0 + xsum_off);
+        const int seg_first = P.lo < P.hi ? P.lo / P.upe : 0;
+        const int seg_last = P.lo < P.hi ? (P.hi - 1) / P.upe : -1;
+#pragma unroll 1
+        for (int sb = seg_first; sb <= seg_last && ok; sb += D_NSEG) {
+            const int nseg = min(D_NSEG, seg_last - sb + 1);
+            __syncthreads();  // the previous lists and staged rows are no longer read
+            // ---- the slots that named each expert of this batch of segments, ascending
+            if (warp < nseg) {
+                const uint32_t e = uint32_t(expert_of(sb + warp));
+                int count = 0;
+                for (int base = 0; base < slots; base += 32) {
+                    const bool hit = base + lane < slots && s_ids[base + lane] == e;
+                    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+                    if (hit) s_lists[warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(base + lane);
+                    count += __popc(ballot);
+                }
+                if (lane == 0) s_seg_count[warp] = count;
+            }
+            __syncthreads();
+            int si = 0;
+#pragma unroll 1
+            while (si < nseg && ok) {
+                // ---- a group: consecutive segments whose rows (in tiles of 8) fit the staged area
+                int row0[D_NSEG] = {0, 0, 0, 0}, sj = si, rows = 0;
+#pragma unroll
+                for (int k = 0; k < D_NSEG; k++) {  // (constant indices keep row0 in registers)
+                    if (k == sj && k < nseg) {
+                        const int need = (s_seg_count[k] + 7) & ~7;
+                        if (k == si || rows + need <= a.xcap) {
+                            row0[k] = rows;
+                            rows += need;
+                            sj = k + 1;
+                        }
+                    }
+                }
+                auto row_of = [&](int sx) { return sx == 0 ? row0[0] : sx == 1 ? row0[1] : sx == 2 ? row0[2] : row0[3]; };
+                if (si > 0) __syncthreads();  // the previous group's rows are no longer read
+                if (gate_up) {
+                    // Token rows by plain 16-byte loads (L2 hits: the router phase just wrote them).
+                    const int vec_per_row = P.cols / 16;
+                    for (int sx = si; sx < sj; sx++) {
+                        const int cnt = s_seg_count[sx], n = ((cnt + 7) & ~7) * vec_per_row, r0x = row_of(sx);
+                        const uint16_t* list = s_lists + sx * D_TOK;
+#pragma unroll 4
+                        for (int i = tid; i < n; i += nthreads) {
+                            const int j = i / vec_per_row, v = i - j * vec_per_row;
+                            const uint32_t token = uint32_t(list[min(j, cnt - 1)]) / uint32_t(topk);
+                            const uint4 val = __ldcg(reinterpret_cast<const uint4*>(a.xq + size_t(token) * P.cols) + v);
+                            *reinterpret_cast<uint4*>(smem + L.x0 + (r0x + j) * P.x_stride + v * 16) = val;
+                        }
+                    }
+                    for (int sx = si; sx < sj; sx++) {
+                        // Scales transposed to [block][token]; token fastest, so stores do not conflict.
+                        const int cnt = s_seg_count[sx], n8 = (cnt + 7) & ~7, n = P.nb * n8, r0x = row_of(sx);
+                        const uint16_t* list = s_lists + sx * D_TOK;
+#pragma unroll 2
+                        for (int i = tid; i < n; i += nthreads) {
+                            const int b = i / n8, j = i - b * n8;
+                            const uint32_t token = uint32_t(list[min(j, cnt - 1)]) / uint32_t(topk);
+                            const size_t src = size_t(token) * P.nbp + b;
+                            xsT[b * D_TOK + r0x + j] = __ldcg(a.xs + src);
+                            if (KIND == 2) xsumT[b * D_TOK + r0x + j] = __ldcg(a.xsum + src);
+                        }
+                    }
+                } else {
+                    // The down projection's inputs are the SwiGLU rows in f32: quantized here exactly as
+                    // quantize_q8 does (src/kernels.rs:84-98, applied per gathered row by
+                    // src/weights.rs:652-664), straight into the staged layout. A thread per
+                    // (row, 32-block).
+                    for (int sx = si; sx < sj; sx++) {
+                        const int cnt = s_seg_count[sx], n8 = (cnt + 7) & ~7, r0x = row_of(sx);
+                        const uint16_t* list = s_lists + sx * D_TOK;
+                        for (int task = tid; task < n8 * P.nb; task += nthreads) {
+                            const int j = task / P.nb, b = task - j * P.nb;
+                            const size_t row = list[min(j, cnt - 1)];
+                            const float4* src = reinterpret_cast<const float4*>(a.hidden_f + row * P.cols + b * QK);
+                            float4 v[8];
+#pragma unroll
+                            for (int i = 0; i < 8; i++) v[i] = __ldcg(src + i);
+                            float amax = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 8; i++)
+                                amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
+                                             fabsf(v[i].w));
+                            const float d = __fdiv_rn(amax, 127.0f);
+                            const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                            auto q8 = [&](float x) {
+                                const float rr = roundf(x * id);
+                                return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                            };
+                            uint32_t packed[8];
+                            int qsum = 0;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+                                qsum += q0 + q1 + q2 + q3;
+                                packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) |
+                                            (uint32_t(q2 & 0xFF) << 16) | (uint32_t(q3 & 0xFF) << 24);
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>(smem + L.x0 + (r0x + j) * P.x_stride + b * QK);
+                            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                            xsT[b * D_TOK + r0x + j] = d;
+                            if (KIND == 2) xsumT[b * D_TOK + r0x + j] = d * float(qsum);
+                        }
+                    }
+                }
+                __syncthreads();
+                // A value the compiler cannot know before the barrier: the staged reads depend on it.
+                asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
+
+                // ---- this warp's records of the group's segments
+                while (ok && cu < P.n) {
+                    const int wu = P.first + cu * nwarps;
+                    const int sx = wu / P.upe - sb;  // segment of the unit within this batch
+                    if (sx >= sj) break;
+                    if (fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
+                    if (cc == 0) {
+#pragma unroll
+                        for (int nt = 0; nt < D_GMAX; nt++) {
+                            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+                            off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
+                        }
+                    }
+                    const uint32_t stage = takes % STAGES;
+                    const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
+                    if (!__all_sync(0xffffffffu, landed)) {
+                        ok = false;
+                        break;
+                    }
+                    const int cnt = s_seg_count[sx], G = (cnt + 7) >> 3;
+                    if (G > 0) {
+                        const uint32_t wtok = uint32_t(landed);
+                        const uint32_t rec = smem_addr(ring + stage * R::BYTES);
+                        const int nblk = min(F_NBC, P.nb - cc * F_NBC), blk0 = cc * F_NBC;
+                        const int r0x = row_of(sx);
+                        const uint32_t xq_s = smem_addr(smem + L.x0 + r0x * P.x_stride);
+                        const uint32_t xsT_s = smem_addr(xsT + r0x), xsumT_s = smem_addr(xsumT + r0x);
+                        switch (G) {
+                            case 1: fast_chunk<KIND, 1, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            case 2: fast_chunk<KIND, 2, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            case 3: fast_chunk<KIND, 3, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            default: fast_chunk<KIND, 4, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                        }
+                        __syncwarp();
+                        if (cc == P.nchunks - 1) {
+                            const int u = wu % P.upe;
+                            const uint16_t* list = s_lists + sx * D_TOK;
+#pragma unroll
+                            for (int nt = 0; nt < D_GMAX; nt++) {
+#pragma unroll
+                                for (int i = 0; i < 2; i++) {
+                                    const int j = nt * 8 + 2 * tq + i;
+                                    if (nt < G && j < cnt) {
+                                        float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
+                                        if (KIND == 2) {
+                                            y0 = y0 + off[nt][i];
+                                            y1 = y1 + off[nt][2 + i];
+                                        }
+                                        const size_t slot = list[j];
+                                        if (gate_up) {
+                                            const int col = u * 8 + g;
+                                            if (col < inter) {
+                                                const float ex = exp_poly(-y0);
+                                                a.hidden_f[slot * inter + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
+                                            }
+                                        } else {
+                                            const int r0 = u * F_ROWS + g;
+                                            if (r0 < hidden) a.out[slot * hidden + r0] = y0;
+                                            if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                    }
+                    takes++;
+                    if (++cc == P.nchunks) cc = 0, cu++;
+                }
+                ok = __syncthreads_and(ok);  // keep the decision to stop uniform across the CTA's barriers
+                xphase++;
+                si = sj;
+            }
+        }
+        // The ring is topped up with the next phase's records before this CTA waits for the others.
+        while (ok && fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
+        // ---- every CTA's part of this phase is in global memory before anyone reads it
+        __syncthreads();
+        arrived = p + 1;
+        if (tid == 0) {
+            if (!ok) s_abort = 3;
+            grid_arrive(a.sync + 1 + p);
+            // After gate_up everyone goes on to down; after down only the combining CTAs stay.
+            if (ok && (p == 0 || bid < t) && !grid_wait(a.sync + 1 + p, uint32_t(nctas), a.spin_limit)) s_abort = 2;
+        }
+        __syncthreads();
+        ok = !s_abort;
+        if (stamping) a.stamps[3 + p] = wall_clock_ns();
+    }
+
+    // ---- weighted combine + residual add: CTA i < t takes token i (src/model.rs:513-519, 681)
+    if (ok && bid < t) {
+        if (tid < topk) {
+            const uint32_t mine = s_ids[bid * topk + tid];
+            int rank = 0;
+            for (int j = 0; j < topk; j++) rank += s_ids[bid * topk + j] < mine ? 1 : 0;
+            s_cpos[rank] = uint32_t(bid * topk + tid);
+            s_cgate[rank] = __ldcg(a.gates + size_t(bid) * topk + tid);
+        }
+        __syncthreads();
+        float* yr = a.y + size_t(bid) * hidden;
+        for (int c = tid * 4; c < hidden; c += nthreads * 4) {
+            float4 proj = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+            for (int j = 0; j < topk; j++) {
+                const float gt = s_cgate[j];
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(a.out + size_t(s_cpos[j]) * hidden + c));
+                proj.x = proj.x + gt * v.x;
+                proj.y = proj.y + gt * v.y;
+                proj.z = proj.z + gt * v.z;
+                proj.w = proj.w + gt * v.w;
+            }
+            float4 r = *reinterpret_cast<float4*>(yr + c);
+            r.x = r.x + proj.x;
+            r.y = r.y + proj.y;
+            r.z = r.z + proj.z;
+            r.w = r.w + proj.w;
+            *reinterpret_cast<float4*>(yr + c) = r;
+        }
+        // The last combining CTA leaves the counters at zero for the next launch. Every CTA
+        // has passed its waits on them by now (all arrived at the last one).
+        if (tid == 0 && atomicAdd(a.sync + 3, 1u) == uint32_t(t) - 1) {
+            a.sync[0] = a.sync[1] = a.sync[2] = a.sync[3] = 0;
+            __threadfence();
+        }
+    }
+    if (stamping) a.stamps[5] = wall_clock_ns();
+    if (!ok) {
+        if (tid == 0) {
+            atomicExch(a.status, s_abort == 3 ? ERR_COPY_WAIT_TIMEOUT : ERR_GRID_WAIT_TIMEOUT);
+            // Announce the phases this CTA will not run, so that nobody waits for it in vain.
+            for (int p = arrived; p < 2; p++) atomicAdd(a.sync + 1 + p, 1u);
+        }
+        // Give copies already in flight a bounded chance to land before the shared memory
+        // they target is released.
+        for (uint32_t k = takes; k < fills; k++) mbar_wait_bounded(bars + k % STAGES, (k / STAGES) & 1);
+    }
+}
+
+// Warps per CTA, ring depth and staged rows: as many warps as possible while each still
+// gets a ring of at least three stages; then the deepest ring that fits.
+template <int KIND>
+bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap) {
+    xcap = min(D_TOK, (t + 7) / 8 * 8);
+    auto deepest = [&](int w) {
+        for (int k = D_MAX_STAGES; k >= 2; k--)
+            if (size_t(DLayout<KIND>(w, k, xcap, d.hidden, d.inter, d.experts, d.topk).total) + 1024 <= D_SMEM_LIMIT) return k;
+        return 0;
+    };
+    int best_w = 0, best_s = 0;
+    for (int w = D_MAX_WARPS; w >= 8; w -= 2) {
+        const int s = deepest(w);
+        if (s >= 3) {
+            nwarps = w, stages = s;
+            return true;
+        }
+        if (s > best_s) best_s = s, best_w = w;
+    }
+    nwarps = best_w, stages = best_s;
+    return best_s >= 2;
+}
+
+}  // namespace
+
+void init_kernels_decode() {
+    const int lim = int(D_SMEM_LIMIT);
+    cudaFuncSetAttribute(moe_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(moe_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+}
+
+bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t) {
+    if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK) return false;
+    int w, s, x;
+    return kind_gate_up == 1 ? decode_config<1>(d, t, w, s, x) : decode_config<2>(d, t, w, s, x);
+}
+
+int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
+                        const float* norm_w, float eps, int t, float* y, const uint8_t* gate_up_tiled,
+                        const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit, cudaStream_t stream) {
+    DecodeArgs a{};
+    a.router = router, a.bias = bias, a.x = x, a.norm_w = norm_w, a.eps = eps, a.y = y;
+    a.t = t, a.hidden = d.hidden, a.experts = d.experts, a.topk = d.topk, a.inter = d.inter;
+    a.logits = ws.logits, a.ids = ws.ids, a.gates = ws.gates, a.xq = ws.xq, a.xs = ws.xs, a.xsum = ws.xsum;
+    a.gu_tiled = gate_up_tiled, a.dn_tiled = down_tiled;
+    a.hidden_f = ws.hidden_f, a.out = ws.out;
+    a.dense = dense_walk(d, t) ? 1 : 0;
+    a.sync = ws.grid_sync;
+    a.spin_limit = spin_limit;
+    a.status = ws.status;
+    int nwarps = 0;
+    const bool fits = kind == 1 ? decode_config<1>(d, t, nwarps, a.stages, a.xcap) : decode_config<2>(d, t, nwarps, a.stages, a.xcap);
+    if (!fits) return -1;
+    // One CTA per SM, all resident at once (they wait for one another): never more CTAs than SMs.
+    const int grid = sms;
+    if (kind == 1) {
+        const DLayout<1> L(nwarps, a.stages, a.xcap, d.hidden, d.inter, d.experts, d.topk);
+        launch_overlapped(moe_decode_kernel<1>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
+    } else {
+        const DLayout<2> L(nwarps, a.stages, a.xcap, d.hidden, d.inter, d.experts, d.topk);
+        launch_overlapped(moe_decode_kernel<2>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
+    }
+    return 1;
+}
+
+}  // namespace tc

@@ -20,56 +20,11 @@
 // itself is not correctly rounded, hence the 1e-5 tolerance on gates.
 #include "dispatch_common.cuh"
 #include "experts_common.cuh"
+#include "route_common.cuh"
 
 namespace tc {
 
 namespace {
-
-__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
-
-// f32::total_cmp as an integer key (larger key = later in total order).
-__device__ __forceinline__ int total_key(float v) {
-    int b = __float_as_int(v);
-    return b ^ int(unsigned(b >> 31) >> 1);
-}
-
-// The hsum tree of src/kernels_x86.rs:33-38 over 8 values held by lanes
-// j..j+7 of an aligned 8-lane group: (v0+v4, v1+v5, v2+v6, v3+v7) ->
-// (s0+s2, s1+s3) -> s0+s1. Lane j%8==0 ends with the sum.
-__device__ __forceinline__ float hsum8(float v, unsigned mask) {
-    v = v + __shfl_down_sync(mask, v, 4, 8);
-    v = v + __shfl_down_sync(mask, v, 2, 8);
-    v = v + __shfl_down_sync(mask, v, 1, 8);
-    return v;
-}
-
-// Sum of squares of a row in dot_f32's order, by one warp: lane L owns the
-// elements L, L+32, ... (the four 8-lane accumulators of the main loop side by
-// side); leftover groups of eight go to the first accumulator; then
-// (acc0+acc1)+(acc2+acc3) lane-wise, the hsum tree, and the scalar tail.
-__device__ __forceinline__ float sum_squares_avx_order(const float* xr, int n, int lane) {
-    float acc = 0.0f;
-    int i = 0;
-#pragma unroll 8
-    for (; i + 32 <= n; i += 32) {
-        const float v = xr[i + lane];
-        acc = fmaf(v, v, acc);
-    }
-    for (; i + 8 <= n; i += 8) {
-        if (lane < 8) {
-            const float v = xr[i + lane];
-            acc = fmaf(v, v, acc);
-        }
-    }
-    float s = acc + __shfl_down_sync(0xffffffffu, acc, 8);  // lanes 0-7: a0+a1; 16-23: a2+a3
-    s = s + __shfl_down_sync(0xffffffffu, s, 16);           // lanes 0-7: the four summed
-    s = hsum8(s, 0xffffffffu);
-    float tail = 0.0f;
-    for (int j = i; j < n; j++) tail = tail + xr[j] * xr[j];
-    s = s + tail;
-    return __shfl_sync(0xffffffffu, s, 0);
-}
 
 constexpr size_t ROUTE_SMEM_LIMIT = 200 * 1024;
 constexpr int ROUTE_THREADS = DISPATCH_THREADS;  // the last CTA runs the dispatch with the same threads
@@ -126,175 +81,50 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     // The router matrix is a constant: it streams in while the kernel in front of this
     // one (the previous block's combine) finishes. Everything below reads its output.
     grid_dependency_wait();
-    // A CTA walks tokens blockIdx.x, blockIdx.x + gridDim.x, ...: one each as launched today.
+    // A CTA walks tokens blockIdx.x, blockIdx.x + gridDim.x, ...: one each for batches of up to a few
+    // CTAs per SM, several for prefill-size batches (the staged router matrix is then read once per
+    // CTA instead of once per token). The next token's row is requested before this one is worked on.
     bool w_landed = true;
+    constexpr int ROW_VEC = 4;  // float4 per thread held ahead: rows of up to 4096 floats
+    float4 ahead[ROW_VEC];
+    auto request_row = [&](int token) {
+#pragma unroll
+        for (int i = 0; i < ROW_VEC; i++) {
+            const int c = (tid + i * ROUTE_THREADS) * 4;
+            if (token < a.t && c < hidden)
+                ahead[i] = *reinterpret_cast<const float4*>(a.x + size_t(token) * hidden + c);
+        }
+    };
+    const bool rows_ahead = hidden <= ROW_VEC * ROUTE_THREADS * 4;
+    if (rows_ahead) request_row(blockIdx.x);
     for (int token = blockIdx.x; token < a.t; token += gridDim.x) {
-    if (token != int(blockIdx.x)) __syncthreads();  // the previous token's row and logits are no longer read
-    const float* xin = a.x + size_t(token) * hidden;
-    for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
-        *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
-    __syncthreads();
-
-    if (a.norm_w) {
-        if (warp == 0) {
-            const float ss = __fdiv_rn(sum_squares_avx_order(xrow, hidden, lane), float(hidden));
-            if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(ss + a.eps));
+        if (token != int(blockIdx.x)) __syncthreads();  // the previous token's row and logits are no longer read
+        if (rows_ahead) {
+#pragma unroll
+            for (int i = 0; i < ROW_VEC; i++) {
+                const int c = (tid + i * ROUTE_THREADS) * 4;
+                if (c < hidden) *reinterpret_cast<float4*>(xrow + c) = ahead[i];
+            }
+            request_row(token + gridDim.x);
+        } else {
+            const float* xin = a.x + size_t(token) * hidden;
+            for (int c = tid * 4; c < hidden; c += ROUTE_THREADS * 4)
+                *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
         }
         __syncthreads();
-        const float inv = s_inv;
-        for (int c = tid; c < hidden; c += ROUTE_THREADS) xrow[c] = xrow[c] * inv * a.norm_w[c];
+        if (a.norm_w) route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, ROUTE_THREADS);
+
+        if (a.stage_router && token == int(blockIdx.x)) w_landed = mbar_wait_bounded(&s_wbar, 0);
+        route_logits(a.router, a.stage_router && w_landed ? wsm : nullptr, wstride, xrow, a.bias, hidden, experts,
+                     slog, a.logits ? a.logits + size_t(token) * experts : nullptr, tid, ROUTE_THREADS);
         __syncthreads();
-    }
 
-    // ---- logits. Four threads per expert, each holding four of the dot's
-    // sixteen float lanes: thread q owns elements 16j+4q..16j+4q+3, so q = 0,1
-    // hold the first 8-lane accumulator and q = 2,3 the second. The weights of
-    // a whole batch of steps are requested before the chains run, so the loads
-    // overlap instead of each waiting for the previous fma.
-    constexpr int BATCH = 16;
-    if (a.stage_router && token == int(blockIdx.x)) w_landed = mbar_wait_bounded(&s_wbar, 0);
-    for (int e0 = 0; e0 < experts; e0 += ROUTE_THREADS / 4) {
-        const int e = e0 + (tid >> 2), q = tid & 3;
-        const bool valid = e < experts;
-        const uint16_t* w = a.router + size_t(valid ? e : 0) * hidden + q * 4;
-        const float* xr = xrow + q * 4;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (a.stage_router && w_landed) {
-            const uint8_t* ws = wsm + size_t(valid ? e : 0) * wstride + q * 8;
-#pragma unroll 8
-            for (int c = 0; c < hidden; c += 16) {
-                const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
-                const float4 xv = *reinterpret_cast<const float4*>(xr + c);
-                acc[0] = fmaf(bf16_lo(wv.x), xv.x, acc[0]);
-                acc[1] = fmaf(bf16_hi(wv.x), xv.y, acc[1]);
-                acc[2] = fmaf(bf16_lo(wv.y), xv.z, acc[2]);
-                acc[3] = fmaf(bf16_hi(wv.y), xv.w, acc[3]);
-            }
-        } else
-        for (int c0 = 0; c0 < hidden; c0 += 16 * BATCH) {
-            uint2 wv[BATCH];
-#pragma unroll
-            for (int u = 0; u < BATCH; u++)
-                wv[u] = c0 + 16 * u < hidden ? __ldg(reinterpret_cast<const uint2*>(w + c0 + 16 * u))
-                                             : make_uint2(0u, 0u);
-#pragma unroll
-            for (int u = 0; u < BATCH; u++) {
-                if (c0 + 16 * u < hidden) {
-                    const float4 xv = *reinterpret_cast<const float4*>(xr + c0 + 16 * u);
-                    acc[0] = fmaf(bf16_lo(wv[u].x), xv.x, acc[0]);
-                    acc[1] = fmaf(bf16_hi(wv[u].x), xv.y, acc[1]);
-                    acc[2] = fmaf(bf16_lo(wv[u].y), xv.z, acc[2]);
-                    acc[3] = fmaf(bf16_hi(wv[u].y), xv.w, acc[3]);
-                }
-            }
-        }
-        // acc0 + acc1 lane-wise: lane l of the first accumulator (q = l/4) plus
-        // lane l of the second (q = 2 + l/4): the thread two to the right.
-        float v[4];
-#pragma unroll
-        for (int l = 0; l < 4; l++) v[l] = acc[l] + __shfl_xor_sync(0xffffffffu, acc[l], 2);
-        // Now q = 0 holds v0..v3 and q = 1 holds v4..v7 (q = 2,3 hold copies).
-        // hsum: (v0+v4, v1+v5, v2+v6, v3+v7) -> (s0+s2, s1+s3) -> sum.
-        float sv[4];
-#pragma unroll
-        for (int l = 0; l < 4; l++) sv[l] = v[l] + __shfl_xor_sync(0xffffffffu, v[l], 1);
-        float y = (sv[0] + sv[2]) + (sv[1] + sv[3]);
-        if (valid && q == 0) {
-            // The dot's scalar tail is an empty sum (hidden is a multiple of 32): hsum + 0.0.
-            y = y + 0.0f;
-            if (a.bias) y = y + a.bias[e];
-            slog[e] = y;
-            if (a.logits) a.logits[size_t(token) * experts + e] = y;
-        }
-    }
-    __syncthreads();
-
-    // ---- top-k and gates: warp 0. Lane l holds experts l, l+32, ...
-    if (warp == 0) {
-        constexpr int SLOTS = MAX_EXPERTS / 32;
-        const int nslots = (experts + 31) >> 5;
-        unsigned ukeys[SLOTS];  // order-preserving unsigned keys; 0 = not a candidate
-        unsigned taken = 0;
-#pragma unroll
-        for (int s = 0; s < SLOTS; s++) {
-            const int e = lane + 32 * s;
-            // total_key is a signed order; flipping the sign bit makes it unsigned. +1 keeps 0 free
-            // (the all-ones key, -NaN's neighbour in this order, cannot occur: it would be key 2^32).
-            ukeys[s] = (s < nslots && e < experts) ? (unsigned(total_key(slog[e])) ^ 0x80000000u) : 0u;
-            if (!(s < nslots && e < experts)) taken |= 1u << s;
-        }
-        int my_id = 0;
-        float my_val = 0.0f;
-        for (int j = 0; j < topk; j++) {
-            unsigned best_key = 0;
-            int best_idx = 0x7fffffff;
-#pragma unroll
-            for (int s = 0; s < SLOTS; s++) {
-                if (s < nslots && !((taken >> s) & 1u)) {
-                    if (best_idx == 0x7fffffff || ukeys[s] > best_key) {
-                        best_key = ukeys[s];
-                        best_idx = lane + 32 * s;
-                    }
-                }
-            }
-            // The largest key in the warp, then the lowest expert index among its holders.
-            const bool have = best_idx != 0x7fffffff;
-            const unsigned all_have = __ballot_sync(0xffffffffu, have);
-            const unsigned wmax = __reduce_max_sync(0xffffffffu, have ? best_key : 0u);
-            const bool tie = have && best_key == wmax;
-            const unsigned widx = __reduce_min_sync(0xffffffffu, tie ? unsigned(best_idx) : 0xffffffffu);
-            (void)all_have;
-            const int win = int(widx);
-            if ((win & 31) == lane) taken |= 1u << (win >> 5);
-            if (lane == j) {
-                my_id = win;
-                my_val = slog[win];
-            }
-        }
-        const float mx = __shfl_sync(0xffffffffu, my_val, 0);
-        float ej = 0.0f;
-        if (lane < topk) ej = float(exp(double(my_val - mx)));
-        float sum = 0.0f;
-        for (int j = 0; j < topk; j++) sum = sum + __shfl_sync(0xffffffffu, ej, j);
-        if (lane < topk) {
-            a.ids[size_t(token) * topk + lane] = uint32_t(my_id);
-            a.gates[size_t(token) * topk + lane] = __fdiv_rn(ej, sum);
-        }
-    }
-
-    // ---- 8-bit quantization of the row, a warp per 32-block.
-    const int nb = hidden / QK;
-    const int padded = (nb + SUPER - 1) / SUPER * SUPER;
-    // Warps 1.. take the blocks while warp 0 is still ranking the logits above (the two do
-    // not depend on each other); a single-warp launch would do both in turn.
-    constexpr int QWARPS = ROUTE_THREADS / 32 - 1;
-    for (int b = warp - 1; warp > 0 && b < padded; b += QWARPS) {
-        if (b >= nb) {  // zero padding up to whole super-blocks
-            if (lane == 0) {
-                a.xs[size_t(token) * padded + b] = 0.0f;
-                a.xsum[size_t(token) * padded + b] = 0.0f;
-            }
-            continue;
-        }
-        const float v = xrow[b * QK + lane];
-        float amax = fabsf(v);
-        // f32::max drops NaN operands, as fmaxf does.
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float d = __fdiv_rn(amax, 127.0f);
-        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-        float r = roundf(v * id);
-        int q = (r != r) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, r)));
-        a.xq[size_t(token) * hidden + b * QK + lane] = int8_t(q);
-        int qsum = q;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
-        if (lane == 0) {
-            a.xs[size_t(token) * padded + b] = d;
-            a.xsum[size_t(token) * padded + b] = d * float(qsum);
-        }
-    }
-
+        // Warp 0 ranks the logits while warps 1.. quantize the row (the two do not depend on each other).
+        if (warp == 0)
+            route_topk_gates(slog, experts, topk, a.ids + size_t(token) * topk, a.gates + size_t(token) * topk, lane);
+        const int padded = (hidden / QK + SUPER - 1) / SUPER * SUPER;
+        route_quantize_row(xrow, hidden, a.xq + size_t(token) * hidden, a.xs + size_t(token) * padded,
+                           a.xsum + size_t(token) * padded, warp, lane, 1, ROUTE_THREADS / 32 - 1);
     }  // tokens of this CTA
 
     // ---- the dispatch, by the last CTA to get here (batches of up to one CTA's worth of tokens).
@@ -380,9 +210,12 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
     if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
-    // One CTA per token at every batch size: measured faster than fewer CTAs that walk several
-    // tokens each (which the kernel's token loop would allow), since short CTAs overlap better.
-    launch_overlapped(route_kernel, dim3(t), dim3(ROUTE_THREADS), smem, stream, a);
+    // One CTA per token while that is at most three CTAs per SM (short CTAs overlap best);
+    // beyond that a fixed grid whose CTAs walk several tokens each, so that a prefill-size
+    // batch stages the router matrix a few hundred times instead of once per token.
+    const int sms = ws.sms > 0 ? ws.sms : 148;
+    const int grid = a.fuse_dispatch || t <= 3 * sms ? t : 3 * sms;
+    launch_overlapped(route_kernel, dim3(grid), dim3(ROUTE_THREADS), smem, stream, a);
     int launched = 1;
     if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
     return launched;

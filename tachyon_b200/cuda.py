@@ -30,6 +30,9 @@ SYMBOLS = {
     "tc_set_arithmetic": (_i, [_vp, _i]),
     "tc_set_prefill_threshold": (_i, [_vp, _i]),
     "tc_set_launch_overlap": (_i, [_vp, _i]),
+    "tc_set_decode_block": (_i, [_vp, _i]),
+    "tc_profile_phases": (_i, [_vp, _i]),
+    "tc_profile_read_phases": (_i, [_vp, _vp]),
     "tc_malloc": (_vp, [_vp, _sz]),
     "tc_free": (None, [_vp, _vp]),
     "tc_upload": (_i, [_vp, _vp, _vp, _sz]),
@@ -153,6 +156,22 @@ class Context:
         """Programmatic dependent launch between the kernels of a block (default on)."""
         self._check(self.lib.tc_set_launch_overlap(self.handle, int(on)), "tc_set_launch_overlap")
 
+    def set_decode_block(self, on: bool):
+        """Decode-size blocks (up to 32 tokens) as one kernel (default on) or as four."""
+        self._check(self.lib.tc_set_decode_block(self.handle, int(on)), "tc_set_decode_block")
+
+    def profile_phases(self, on: bool):
+        self._check(self.lib.tc_profile_phases(self.handle, int(on)), "tc_profile_phases")
+
+    PHASES = ("wait_previous", "route", "gate_up", "down", "combine")
+
+    def read_phases(self) -> dict:
+        """Microseconds CTA 0 of the last one-kernel block spent up to each phase boundary."""
+        ns = np.zeros(6, np.uint64)
+        self._check(self.lib.tc_profile_read_phases(self.handle, _ptr(ns)), "tc_profile_read_phases")
+        d = np.diff(ns.astype(np.int64)) / 1e3
+        return {name: float(v) for name, v in zip(self.PHASES, d)}
+
     def set_prefill_threshold(self, avg_tokens_per_expert: int):
         """Average tokens per expert from which the tcgen05 kernels take over (default 32; 0 = always)."""
         self._check(self.lib.tc_set_prefill_threshold(self.handle, avg_tokens_per_expert),
@@ -198,7 +217,7 @@ class Context:
         buf = (C.c_byte * (n * dtype.itemsize)).from_address(p)
         return np.frombuffer(buf, dtype=dtype).reshape(shape)
 
-    PROFILE_STAGES = ("route", "dispatch", "gate_up", "quant_hidden", "down", "combine", "rmsnorm", "other")
+    PROFILE_STAGES = ("route", "dispatch", "gate_up", "quant_hidden", "down", "combine", "rmsnorm", "decode_block")
 
     def profile_enable(self, on: bool):
         self._check(self.lib.tc_profile_enable(self.handle, int(on)), "tc_profile_enable")
