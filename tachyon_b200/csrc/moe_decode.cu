@@ -581,8 +581,10 @@ bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int
 
 int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
                         const float* norm_w, float eps, int t, float* y, const uint8_t* gate_up_tiled,
-                        const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit, cudaStream_t stream) {
+                        const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit,
+                        unsigned long long* stamps, cudaStream_t stream) {
     DecodeArgs a{};
+    a.stamps = stamps;
     a.router = router, a.bias = bias, a.x = x, a.norm_w = norm_w, a.eps = eps, a.y = y;
     a.t = t, a.hidden = d.hidden, a.experts = d.experts, a.topk = d.topk, a.inter = d.inter;
     a.logits = ws.logits, a.ids = ws.ids, a.gates = ws.gates, a.xq = ws.xq, a.xs = ws.xs, a.xsum = ws.xsum;
