@@ -49,7 +49,7 @@ constexpr int D_MAX_STAGES = 8;
 constexpr int D_GMAX = 4;          // token tiles of 8 held in registers
 constexpr int D_TOK = 8 * D_GMAX;  // tokens per block this kernel takes; rows staged at a time
 constexpr int D_NSEG = 4;          // experts of a CTA's range whose slot lists are held at a time
-constexpr size_t D_SMEM_LIMIT = 227 * 1024;
+constexpr size_t D_SMEM_LIMIT = 227 * 1024 - 2048;  // dynamic part: the kernel also has about 1.2 KB of static shared memory
 
 struct DecodeArgs {
     // router phase
@@ -549,7 +549,7 @@ bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap)
     xcap = min(D_TOK, (t + 7) / 8 * 8);
     auto deepest = [&](int w) {
         for (int k = D_MAX_STAGES; k >= 2; k--)
-            if (size_t(DLayout<KIND>(w, k, xcap, d.hidden, d.inter, d.experts, d.topk).total) + 1024 <= D_SMEM_LIMIT) return k;
+            if (size_t(DLayout<KIND>(w, k, xcap, d.hidden, d.inter, d.experts, d.topk).total) <= D_SMEM_LIMIT) return k;
         return 0;
     };
     int best_w = 0, best_s = 0;
