@@ -131,11 +131,46 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return false;
 }
 
+// The same for waits on a kernel's critical path: plain probes a few tens of nanoseconds
+// apart. (A suspended try_wait was seen to return microseconds after the phase had
+// completed.) Bounded: about a second of probing.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (SPIN_LIMIT << 4); i++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_addr(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        __nanosleep(20);
+    }
+    return false;
+}
+
 __device__ __forceinline__ void bulk_copy(void* dst_smem, const void* src_gmem, uint32_t bytes,
                                           uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+
+// The same for data that is read once (the weight stream): the lines are marked to be
+// evicted first from L2, so that they do not push out what is read again and again
+// between them (the activations, the routing, the kernel's own instructions).
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_copy_once(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar,
+                                               uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
         : "memory");
 }
 

@@ -69,11 +69,10 @@ __device__ __forceinline__ float2 lds_f2(uint32_t addr, uint32_t token) {
     return v;
 }
 
-// f16 bits of a weight scale (finite, as every scale Tachyon stores is) to f32
-// on the full-rate pipes: the bits shifted into place, times 2^112
-// (src/kernels.rs:127-130). Exact for normals and subnormals of either sign.
+// f16 bits of a weight scale to f32 (src/kernels.rs:127-130): one conversion
+// instruction, exact for every half value.
 __device__ __forceinline__ float f16_scale_to_f32(uint32_t h) {
-    return __uint_as_float(((h & 0x8000u) << 16) | ((h & 0x7FFFu) << 13)) * __uint_as_float(0x77800000u);
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h)));
 }
 
 // One record (16 rows x up to 8 blocks) against G tiles of 8 staged tokens. The staged
@@ -94,7 +93,11 @@ __device__ __forceinline__ void fast_chunk(uint32_t rec, uint32_t xq_s, uint32_t
             const uint4 s = lds128(rec + (g + 8 * h) * R::ROW_STRIDE + F_KC, wtok);
             const uint32_t hw[4] = {s.x, s.y, s.z, s.w};
 #pragma unroll
-            for (int b = 0; b < F_NBC; b++) wd[h][b] = f16_scale_to_f32((hw[b >> 1] >> (16 * (b & 1))) & 0xFFFFu);
+            for (int b = 0; b < F_NBC; b += 2) {
+                const uint32_t word = hw[b >> 1];
+                wd[h][b] = f16_scale_to_f32(word & 0xFFFFu);
+                wd[h][b + 1] = f16_scale_to_f32(word >> 16);
+            }
         }
     } else {
 #pragma unroll

@@ -37,6 +37,8 @@
 // (grid_wait). A wait that runs out sets the status word, and the CTA skips to the end,
 // waits (bounded) for its copies in flight and returns; tc_sync reports it and clears
 // the counters.
+#include <type_traits>
+
 #include "experts_fast.cuh"
 #include "route_common.cuh"
 
@@ -48,6 +50,7 @@ constexpr int D_MAX_WARPS = 16;
 constexpr int D_MAX_STAGES = 8;
 constexpr int D_GMAX = 4;          // token tiles of 8 held in registers
 constexpr int D_TOK = 8 * D_GMAX;  // tokens per block this kernel takes; rows staged at a time
+constexpr int D_ROUTE_VEC = 10;    // 16-byte pieces of the router matrix a thread holds at a time
 constexpr int D_NSEG = 4;          // experts of a CTA's range whose slot lists are held at a time
 constexpr size_t D_SMEM_LIMIT = 227 * 1024 - 2048;  // dynamic part: the kernel also has about 1.2 KB of static shared memory
 
@@ -72,6 +75,7 @@ struct DecodeArgs {
     float* hidden_f;          // [t * k, inter] SwiGLU rows by slot
     float* out;               // [t * k, hidden] expert outputs by slot
     int stages, xcap;         // ring depth per warp; staged rows at a time (a multiple of 8, at most D_TOK)
+    int route_rows;           // rows of the router matrix staged at a time in the router phase
     int dense;
     uint32_t* sync;           // [GRID_SYNC_WORDS], zero between launches
     uint32_t spin_limit;
@@ -84,15 +88,21 @@ struct DecodeArgs {
 template <int KIND>
 struct DLayout {
     int ring, x0, xbytes, ids, lists, bars, total;
-    __host__ __device__ DLayout(int nwarps, int stages, int xcap, int hidden, int inter, int experts, int topk) {
+    __host__ __device__ static int token_bytes(int xcap, int hidden, int inter) {
+        const int cols = hidden > inter ? hidden : inter;
+        const int nbp = (cols / QK + 7) / 8 * 8;
+        return xcap * (cols + 16) + nbp * D_TOK * 4 * (KIND == 2 ? 2 : 1);
+    }
+    __host__ __device__ static int route_base(int hidden, int experts) { return ((hidden + experts) * 4 + 127) / 128 * 128; }
+    __host__ __device__ DLayout(int nwarps, int stages, int xcap, int route_rows, int hidden, int inter, int experts,
+                                int topk) {
         int o = nwarps * stages * Rec<KIND>::BYTES;
         ring = 0;
         o = (o + 127) / 128 * 128;
         x0 = o;
-        const int cols = hidden > inter ? hidden : inter;
-        const int nbp = (cols / QK + 7) / 8 * 8;
-        xbytes = xcap * (cols + 16) + nbp * D_TOK * 4 * (KIND == 2 ? 2 : 1);
-        const int route_bytes = (hidden + experts) * 4 + 64;
+        xbytes = token_bytes(xcap, hidden, inter);
+        // The router phase keeps the token's row, its logits and route_rows rows of the router matrix here.
+        const int route_bytes = route_base(hidden, experts) + route_rows * (2 * hidden + 32) + 64;
         if (xbytes < route_bytes) xbytes = route_bytes;
         xbytes = (xbytes + 127) / 128 * 128;
         o += xbytes;
@@ -128,13 +138,13 @@ __device__ __forceinline__ unsigned long long wall_clock_ns() {
     return v;
 }
 
-// After a CTA barrier: this CTA's writes so far are ordered before its arrival.
+// After a CTA barrier: a release at GPU scope orders this CTA's writes so far (cumulatively,
+// through the barrier) before its arrival.
 __device__ __forceinline__ void grid_arrive(uint32_t* ctr) {
-    __threadfence();
-    atomicAdd(ctr, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
 }
 
-// One of the two expert phases' description.
+// What one of the two expert phases needs to know about its matrix and this warp's share.
 struct Phase {
     const uint8_t* tiled;
     int cols, upe, nchunks, nb, nbp, x_stride;
@@ -160,7 +170,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     const int STAGES = a.stages;
     const int t = a.t, hidden = a.hidden, experts = a.experts, topk = a.topk, inter = a.inter;
     const int slots = t * topk;
-    const DLayout<KIND> L(nwarps, STAGES, a.xcap, hidden, inter, experts, topk);
+    const DLayout<KIND> L(nwarps, STAGES, a.xcap, a.route_rows, hidden, inter, experts, topk);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * D_MAX_STAGES;
     uint32_t* s_ids = reinterpret_cast<uint32_t*>(smem + L.ids);
@@ -177,76 +187,167 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     if (stamping) a.stamps[0] = wall_clock_ns();
 
     // ---- the two expert phases and this warp's record sequence: gate_up records, then down's
-    Phase ph[2];
-    ph[0].tiled = a.gu_tiled, ph[0].cols = hidden, ph[0].upe = (inter + 7) / 8;
-    ph[1].tiled = a.dn_tiled, ph[1].cols = inter, ph[1].upe = (hidden + 15) / 16;
-#pragma unroll
-    for (int p = 0; p < 2; p++) {
-        ph[p].nchunks = (ph[p].cols + F_KC - 1) / F_KC;
-        ph[p].nb = ph[p].cols / QK;
-        ph[p].nbp = (ph[p].nb + 7) / 8 * 8;
-        ph[p].x_stride = ph[p].cols + 16;
-    }
-    auto partition = [&](int walk_experts) {
-#pragma unroll
-        for (int p = 0; p < 2; p++) {
-            const int total = walk_experts * ph[p].upe;
-            ph[p].lo = int((long long)bid * total / nctas);
-            ph[p].hi = int((long long)(bid + 1) * total / nctas);
-            ph[p].first = ph[p].lo + warp;
-            ph[p].n = ph[p].first < ph[p].hi ? (ph[p].hi - ph[p].first + nwarps - 1) / nwarps : 0;
-        }
+    Phase P0, P1;
+    P0.tiled = a.gu_tiled, P0.cols = hidden, P0.upe = (inter + 7) / 8;
+    P1.tiled = a.dn_tiled, P1.cols = inter, P1.upe = (hidden + 15) / 16;
+    auto derive = [&](Phase& P) {
+        P.nchunks = (P.cols + F_KC - 1) / F_KC;
+        P.nb = P.cols / QK;
+        P.nbp = (P.nb + 7) / 8 * 8;
+        P.x_stride = P.cols + 16;
     };
-    auto expert_of = [&](int walk_index) { return a.dense ? walk_index : int(s_active[walk_index]); };
-    // Producer cursor over the warp's sequence.
-    uint32_t fills = 0, takes = 0;
-    int pp = 0, pu = 0, pc = 0;  // phase, unit ordinal within the warp's share, chunk
-    uint32_t nrec = 0;
-    auto fill_next = [&]() {
-        while (pp < 2 && pu >= ph[pp].n) pp++, pu = 0, pc = 0;
-        if (pp >= 2) return;
-        const Phase& P = ph[pp];
-        const int wu = P.first + pu * nwarps;              // unit in walk space
-        const int e = expert_of(wu / P.upe);
-        const size_t flat = size_t(e) * P.upe + wu % P.upe;  // unit in the tiled matrix
+    derive(P0), derive(P1);
+    auto share = [&](Phase& P, int walk_experts) {
+        const int total = walk_experts * P.upe;
+        P.lo = int((long long)bid * total / nctas);
+        P.hi = int((long long)(bid + 1) * total / nctas);
+        P.first = P.lo + warp;
+        P.n = P.first < P.hi ? (P.hi - P.first + nwarps - 1) / nwarps : 0;
+    };
+    // Where a unit's records start. Walk space counts the units of all experts (dense) or of
+    // the picked ones (then the expert comes from the list made after the router phase).
+    auto unit_ptr = [&](const Phase& P, int wu) {
+        size_t flat = size_t(wu);
+        if (!a.dense) flat = size_t(s_active[wu / P.upe]) * P.upe + wu % P.upe;
+        return P.tiled + flat * P.nchunks * R::BYTES;
+    };
+    // Producer state: the next record's address, and what is left of its unit and phase.
+    uint32_t fills = 0, takes = 0, nrec = 0;
+    const uint64_t stream_policy = l2_evict_first_policy();
+    const uint8_t* pptr = nullptr;
+    int pphase = 0, pwu = 0, pchunks = 0, punits = 0, pslot = 0;
+    auto start_phase = [&](int p) {
+        pphase = p;
+        const Phase& P = p ? P1 : P0;
+        pwu = P.first, pchunks = P.nchunks, punits = P.n;
+        if (P.n > 0) pptr = unit_ptr(P, pwu);
+    };
+    auto fill_next = [&]() {  // precondition: fills < nrec
         if (lane == 0) {
-            uint64_t* bar = bars + fills % STAGES;
-            mbar_expect_tx(bar, R::BYTES);
-            bulk_copy(ring + (fills % STAGES) * R::BYTES, P.tiled + (flat * P.nchunks + pc) * R::BYTES, R::BYTES, bar);
+            mbar_expect_tx(bars + pslot, R::BYTES);
+            bulk_copy_once(ring + pslot * R::BYTES, pptr, R::BYTES, bars + pslot, stream_policy);
         }
         fills++;
-        if (++pc == P.nchunks) pc = 0, pu++;
+        pslot = pslot + 1 == STAGES ? 0 : pslot + 1;
+        pptr += R::BYTES;
+        if (--pchunks == 0) {
+            const Phase& P = pphase ? P1 : P0;
+            if (--punits > 0) {
+                pwu += nwarps;
+                pchunks = P.nchunks;
+                pptr = a.dense ? pptr + size_t(nwarps - 1) * P.nchunks * R::BYTES : unit_ptr(P, pwu);
+            } else if (pphase == 0) {
+                start_phase(1);
+            }
+        }
     };
-    if (a.dense) {
-        // The partition does not depend on the routing: the ring fills before this grid waits
-        // for the kernel in front of it, and through the router phase.
-        partition(experts);
-        nrec = uint32_t(ph[0].n * ph[0].nchunks + ph[1].n * ph[1].nchunks);
+    auto begin_stream = [&](int walk_experts) {
+        share(P0, walk_experts), share(P1, walk_experts);
+        nrec = uint32_t(P0.n * P0.nchunks + P1.n * P1.nchunks);
+        start_phase(P0.n > 0 ? 0 : 1);
         while (fills < nrec && fills < uint32_t(STAGES)) fill_next();
+    };
+    // The partition of a dense walk does not depend on the routing: the ring fills before this
+    // grid waits for the kernel in front of it, and through the router phase.
+    if (a.dense) begin_stream(experts);
+
+    // ---- router phase, part one (constants only): CTA i < t takes token i. The router matrix
+    // is staged in shared memory beside the token's row, route_rows rows at a time (rows
+    // padded by 32 bytes, so the four-thread groups of a half-warp read distinct banks),
+    // through registers: every thread requests its 16-byte pieces of the next part before
+    // the current part is used, so a part costs one trip to memory, and the first trip is
+    // made before this grid waits for the one in front of it. The norm's weight goes to
+    // registers the same way.
+    float* xrow = reinterpret_cast<float*>(smem + L.x0);
+    float* slog = xrow + hidden;
+    const int wstride = 2 * hidden + 32;
+    uint8_t* wsm = smem + L.x0 + DLayout<KIND>::route_base(hidden, experts);
+    const int pass_rows = a.route_rows;
+    const int vec_per_wrow = hidden / 8;  // 16-byte pieces of a router row
+    constexpr int NW = 8;
+    float nw[NW];
+    uint4 rv[D_ROUTE_VEC];
+    auto request_router_rows = [&](int e_lo) {
+        const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
+        const uint4* src = reinterpret_cast<const uint4*>(a.router + size_t(e_lo) * hidden);
+#pragma unroll
+        for (int k = 0; k < D_ROUTE_VEC; k++) {
+            const int i = tid + k * nthreads;
+            if (i < n) rv[k] = __ldg(src + i);
+        }
+    };
+    auto store_router_rows = [&](int e_lo) {
+        const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
+#pragma unroll
+        for (int k = 0; k < D_ROUTE_VEC; k++) {
+            const int i = tid + k * nthreads;
+            if (i < n) {
+                const int r = i / vec_per_wrow, v = i - r * vec_per_wrow;
+                *reinterpret_cast<uint4*>(wsm + size_t(r) * wstride + v * 16) = rv[k];
+            }
+        }
+    };
+    const bool routing = bid < t;
+    const bool nw_held = a.norm_w && hidden <= NW * nthreads;
+    if (routing) {
+        if (pass_rows > 0) request_router_rows(0);
+        if (nw_held) {
+#pragma unroll
+            for (int k = 0; k < NW; k++) {
+                const int c = tid + k * nthreads;
+                nw[k] = c < hidden ? a.norm_w[c] : 0.0f;
+            }
+        }
     }
     grid_dependency_wait();  // everything below reads or writes what other kernels touch
     if (stamping) a.stamps[1] = wall_clock_ns();
 
-    // ---- router phase: CTA i < t takes token i
-    if (bid < t) {
-        float* xrow = reinterpret_cast<float*>(smem + L.x0);
-        float* slog = xrow + hidden;
+    // ---- router phase, part two
+    bool ok = true;
+    if (routing) {
         const float* xin = a.x + size_t(bid) * hidden;
         for (int c = tid * 4; c < hidden; c += nthreads * 4)
             *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
         __syncthreads();
-        if (a.norm_w) route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, nthreads);
-        route_logits(a.router, nullptr, 0, xrow, a.bias, hidden, experts, slog,
-                     a.logits ? a.logits + size_t(bid) * experts : nullptr, tid, nthreads);
-        __syncthreads();
+        if (a.norm_w) {
+            if (nw_held) {
+                if (warp == 0) {
+                    const float ss = __fdiv_rn(sum_squares_avx_order(xrow, hidden, lane), float(hidden));
+                    if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(ss + a.eps));
+                }
+                __syncthreads();
+                const float inv = s_inv;
+#pragma unroll
+                for (int k = 0; k < NW; k++) {
+                    const int c = tid + k * nthreads;
+                    if (c < hidden) xrow[c] = xrow[c] * inv * nw[k];
+                }
+                __syncthreads();
+            } else {
+                route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, nthreads);
+            }
+        }
+        float* logits_row = a.logits ? a.logits + size_t(bid) * experts : nullptr;
+        if (pass_rows > 0) {
+            for (int e_lo = 0; e_lo < experts; e_lo += pass_rows) {
+                store_router_rows(e_lo);
+                if (e_lo + pass_rows < experts) request_router_rows(e_lo + pass_rows);
+                __syncthreads();
+                route_logits(a.router, wsm, wstride, xrow, a.bias, hidden, e_lo, min(experts, e_lo + pass_rows), slog,
+                             logits_row, tid, nthreads);
+                __syncthreads();  // the staged rows are no longer read; slog is complete up to here
+            }
+        } else {
+            route_logits(a.router, nullptr, 0, xrow, a.bias, hidden, 0, experts, slog, logits_row, tid, nthreads);
+            __syncthreads();
+        }
         if (warp == 0)
             route_topk_gates(slog, experts, topk, a.ids + size_t(bid) * topk, a.gates + size_t(bid) * topk, lane);
-        route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * ph[0].nbp,
-                           a.xsum + size_t(bid) * ph[0].nbp, warp, lane, 1, nwarps - 1);
+        route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * P0.nbp,
+                           a.xsum + size_t(bid) * P0.nbp, warp, lane, 1, nwarps - 1);
         __syncthreads();
         if (tid == 0) grid_arrive(a.sync + 0);
     }
-    bool ok = true;
     if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) s_abort = 1;
     __syncthreads();
     ok = !s_abort;
@@ -273,45 +374,62 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 if (lane == 0) s_nactive = n;
             }
             __syncthreads();
-            partition(s_nactive);
-            nrec = uint32_t(ph[0].n * ph[0].nchunks + ph[1].n * ph[1].nchunks);
-            while (fills < nrec && fills < uint32_t(STAGES)) fill_next();
+            begin_stream(s_nactive);
         }
     }
+
+    // The slots that named each expert of a batch of (up to D_NSEG) segments, ascending: one
+    // warp per segment. Ends with a CTA barrier.
+    auto build_lists = [&](int sb, int nseg) {
+        if (warp < nseg) {
+            const int walk = sb + warp;
+            const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
+            int count = 0;
+            for (int base = 0; base < slots; base += 32) {
+                const bool hit = base + lane < slots && s_ids[base + lane] == e;
+                const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+                if (hit) s_lists[warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(base + lane);
+                count += __popc(ballot);
+            }
+            if (lane == 0) s_seg_count[warp] = count;
+        }
+        __syncthreads();
+    };
+    auto seg_range = [&](const Phase& P, int& first, int& last) {
+        first = P.lo < P.hi ? P.lo / P.upe : 0;
+        last = P.lo < P.hi ? (P.hi - 1) / P.upe : -1;
+    };
 
     const int g = lane >> 2, tq = lane & 3;
     float acc[D_GMAX][4], off[D_GMAX][4];
     uint32_t xphase = 0, xtok = 0;
     int arrived = 0;  // expert phases this CTA has announced
+    int cslot = 0;    // consumer's ring slot and the parity of its barrier
+    uint32_t cpar = 0;
+    if (ok) {
+        int f, l;
+        seg_range(P0, f, l);
+        if (f <= l) build_lists(f, min(D_NSEG, l - f + 1));
+    }
 
 #pragma unroll 1
     for (int p = 0; p < 2 && ok; p++) {
-        const Phase& P = ph[p];
+        const Phase& P = p ? P1 : P0;
         const bool gate_up = p == 0;
-        int cu = 0, cc = 0;  // consumer cursor: unit ordinal, chunk
+        int cu = 0;  // consumer cursor: unit ordinal within the warp's share
         const int xs_off = a.xcap * P.x_stride;
         const int xsum_off = xs_off + P.nbp * D_TOK * 4;
         float* xsT = reinterpret_cast<float*>(smem + L.x0 + xs_off);
         float* xsumT = reinterpret_cast<float*>(smem + L.x0 + xsum_off);
-        const int seg_first = P.lo < P.hi ? P.lo / P.upe : 0;
-        const int seg_last = P.lo < P.hi ? (P.hi - 1) / P.upe : -1;
+        int seg_first, seg_last;
+        seg_range(P, seg_first, seg_last);
 #pragma unroll 1
         for (int sb = seg_first; sb <= seg_last && ok; sb += D_NSEG) {
             const int nseg = min(D_NSEG, seg_last - sb + 1);
-            __syncthreads();  // the previous lists and staged rows are no longer read
-            // ---- the slots that named each expert of this batch of segments, ascending
-            if (warp < nseg) {
-                const uint32_t e = uint32_t(expert_of(sb + warp));
-                int count = 0;
-                for (int base = 0; base < slots; base += 32) {
-                    const bool hit = base + lane < slots && s_ids[base + lane] == e;
-                    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-                    if (hit) s_lists[warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(base + lane);
-                    count += __popc(ballot);
-                }
-                if (lane == 0) s_seg_count[warp] = count;
+            if (sb != seg_first) {  // (the phase's first lists were made before the wait for this phase)
+                __syncthreads();    // the previous lists and staged rows are no longer read
+                build_lists(sb, nseg);
             }
-            __syncthreads();
             int si = 0;
 #pragma unroll 1
             while (si < nseg && ok) {
@@ -330,147 +448,161 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 }
                 auto row_of = [&](int sx) { return sx == 0 ? row0[0] : sx == 1 ? row0[1] : sx == 2 ? row0[2] : row0[3]; };
                 if (si > 0) __syncthreads();  // the previous group's rows are no longer read
+                // The group's rows as one list (staged row r belongs to the last segment that starts at
+                // or before it), so that every load of the group is in flight at once.
+                auto slot_of_row = [&](int r) -> uint32_t {
+                    int sx = si;
+#pragma unroll
+                    for (int k = 1; k < D_NSEG; k++)
+                        if (k > si && k < sj && r >= row0[k]) sx = k;
+                    const int cnt = s_seg_count[sx];
+                    return s_lists[sx * D_TOK + min(r - row_of(sx), cnt - 1)];
+                };
                 if (gate_up) {
                     // Token rows by plain 16-byte loads (L2 hits: the router phase just wrote them).
-                    const int vec_per_row = P.cols / 16;
-                    for (int sx = si; sx < sj; sx++) {
-                        const int cnt = s_seg_count[sx], n = ((cnt + 7) & ~7) * vec_per_row, r0x = row_of(sx);
-                        const uint16_t* list = s_lists + sx * D_TOK;
+                    const int vec_per_row = P.cols / 16, n = rows * vec_per_row;
 #pragma unroll 4
-                        for (int i = tid; i < n; i += nthreads) {
-                            const int j = i / vec_per_row, v = i - j * vec_per_row;
-                            const uint32_t token = uint32_t(list[min(j, cnt - 1)]) / uint32_t(topk);
-                            const uint4 val = __ldcg(reinterpret_cast<const uint4*>(a.xq + size_t(token) * P.cols) + v);
-                            *reinterpret_cast<uint4*>(smem + L.x0 + (r0x + j) * P.x_stride + v * 16) = val;
-                        }
+                    for (int i = tid; i < n; i += nthreads) {
+                        const int r = i / vec_per_row, v = i - r * vec_per_row;
+                        const uint32_t token = slot_of_row(r) / uint32_t(topk);
+                        const uint4 val = __ldcg(reinterpret_cast<const uint4*>(a.xq + size_t(token) * P.cols) + v);
+                        *reinterpret_cast<uint4*>(smem + L.x0 + r * P.x_stride + v * 16) = val;
                     }
-                    for (int sx = si; sx < sj; sx++) {
-                        // Scales transposed to [block][token]; token fastest, so stores do not conflict.
-                        const int cnt = s_seg_count[sx], n8 = (cnt + 7) & ~7, n = P.nb * n8, r0x = row_of(sx);
-                        const uint16_t* list = s_lists + sx * D_TOK;
+                    // Scales transposed to [block][token]; token fastest, so stores do not conflict.
+                    const int ns = P.nb * rows;
 #pragma unroll 2
-                        for (int i = tid; i < n; i += nthreads) {
-                            const int b = i / n8, j = i - b * n8;
-                            const uint32_t token = uint32_t(list[min(j, cnt - 1)]) / uint32_t(topk);
-                            const size_t src = size_t(token) * P.nbp + b;
-                            xsT[b * D_TOK + r0x + j] = __ldcg(a.xs + src);
-                            if (KIND == 2) xsumT[b * D_TOK + r0x + j] = __ldcg(a.xsum + src);
-                        }
+                    for (int i = tid; i < ns; i += nthreads) {
+                        const int b = i / rows, r = i - b * rows;
+                        const uint32_t token = slot_of_row(r) / uint32_t(topk);
+                        const size_t src = size_t(token) * P.nbp + b;
+                        xsT[b * D_TOK + r] = __ldcg(a.xs + src);
+                        if (KIND == 2) xsumT[b * D_TOK + r] = __ldcg(a.xsum + src);
                     }
                 } else {
                     // The down projection's inputs are the SwiGLU rows in f32: quantized here exactly as
                     // quantize_q8 does (src/kernels.rs:84-98, applied per gathered row by
                     // src/weights.rs:652-664), straight into the staged layout. A thread per
                     // (row, 32-block).
-                    for (int sx = si; sx < sj; sx++) {
-                        const int cnt = s_seg_count[sx], n8 = (cnt + 7) & ~7, r0x = row_of(sx);
-                        const uint16_t* list = s_lists + sx * D_TOK;
-                        for (int task = tid; task < n8 * P.nb; task += nthreads) {
-                            const int j = task / P.nb, b = task - j * P.nb;
-                            const size_t row = list[min(j, cnt - 1)];
-                            const float4* src = reinterpret_cast<const float4*>(a.hidden_f + row * P.cols + b * QK);
-                            float4 v[8];
+                    for (int task = tid; task < rows * P.nb; task += nthreads) {
+                        const int r = task / P.nb, b = task - r * P.nb;
+                        const size_t row = slot_of_row(r);
+                        const float4* src = reinterpret_cast<const float4*>(a.hidden_f + row * P.cols + b * QK);
+                        float4 v[8];
 #pragma unroll
-                            for (int i = 0; i < 8; i++) v[i] = __ldcg(src + i);
-                            float amax = 0.0f;
+                        for (int i = 0; i < 8; i++) v[i] = __ldcg(src + i);
+                        float amax = 0.0f;
 #pragma unroll
-                            for (int i = 0; i < 8; i++)
-                                amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
-                                             fabsf(v[i].w));
-                            const float d = __fdiv_rn(amax, 127.0f);
-                            const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-                            auto q8 = [&](float x) {
-                                const float rr = roundf(x * id);
-                                return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
-                            };
-                            uint32_t packed[8];
-                            int qsum = 0;
+                        for (int i = 0; i < 8; i++)
+                            amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)),
+                                         fabsf(v[i].w));
+                        const float d = __fdiv_rn(amax, 127.0f);
+                        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+                        auto q8 = [&](float x) {
+                            const float rr = roundf(x * id);
+                            return (rr != rr) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, rr)));
+                        };
+                        uint32_t packed[8];
+                        int qsum = 0;
 #pragma unroll
-                            for (int i = 0; i < 8; i++) {
-                                const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
-                                qsum += q0 + q1 + q2 + q3;
-                                packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) |
-                                            (uint32_t(q2 & 0xFF) << 16) | (uint32_t(q3 & 0xFF) << 24);
-                            }
-                            uint4* dst = reinterpret_cast<uint4*>(smem + L.x0 + (r0x + j) * P.x_stride + b * QK);
-                            dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                            xsT[b * D_TOK + r0x + j] = d;
-                            if (KIND == 2) xsumT[b * D_TOK + r0x + j] = d * float(qsum);
+                        for (int i = 0; i < 8; i++) {
+                            const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+                            qsum += q0 + q1 + q2 + q3;
+                            packed[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) |
+                                        (uint32_t(q2 & 0xFF) << 16) | (uint32_t(q3 & 0xFF) << 24);
                         }
+                        uint4* dst = reinterpret_cast<uint4*>(smem + L.x0 + r * P.x_stride + b * QK);
+                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        xsT[b * D_TOK + r] = d;
+                        if (KIND == 2) xsumT[b * D_TOK + r] = d * float(qsum);
                     }
                 }
                 __syncthreads();
                 // A value the compiler cannot know before the barrier: the staged reads depend on it.
                 asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
 
-                // ---- this warp's records of the group's segments
+                // ---- this warp's units of the group's segments, a unit (all its chunks) at a time
                 while (ok && cu < P.n) {
                     const int wu = P.first + cu * nwarps;
-                    const int sx = wu / P.upe - sb;  // segment of the unit within this batch
+                    const int seg = wu / P.upe;
+                    const int sx = seg - sb;  // segment of the unit within this batch
                     if (sx >= sj) break;
-                    if (fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
-                    if (cc == 0) {
+                    const int u = wu - seg * P.upe;
+                    const int cnt = s_seg_count[sx], G = (cnt + 7) >> 3, r0x = row_of(sx);
+                    const uint32_t xq_s = smem_addr(smem + L.x0 + r0x * P.x_stride);
+                    const uint32_t xsT_s = smem_addr(xsT + r0x), xsumT_s = smem_addr(xsumT + r0x);
+                    // Takes the unit's next record: tops the ring up, then waits for the record.
+                    // Returns 0 if the wait ran out, else a value that the reads of the record depend on.
+                    auto next_record = [&](uint32_t& rec) -> uint32_t {
+                        if (fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
+                        const bool landed = mbar_wait_poll(bars + cslot, cpar);
+                        if (!__all_sync(0xffffffffu, landed)) return 0u;
+                        rec = smem_addr(ring + cslot * R::BYTES);
+                        if (++cslot == STAGES) cslot = 0, cpar ^= 1;
+                        return uint32_t(landed);
+                    };
+                    auto unit = [&](auto tiles) {
+                        constexpr int GT = decltype(tiles)::value;
 #pragma unroll
                         for (int nt = 0; nt < D_GMAX; nt++) {
                             acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
                             off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
                         }
-                    }
-                    const uint32_t stage = takes % STAGES;
-                    const bool landed = mbar_wait_bounded(bars + stage, (takes / STAGES) & 1);
-                    if (!__all_sync(0xffffffffu, landed)) {
-                        ok = false;
-                        break;
-                    }
-                    const int cnt = s_seg_count[sx], G = (cnt + 7) >> 3;
-                    if (G > 0) {
-                        const uint32_t wtok = uint32_t(landed);
-                        const uint32_t rec = smem_addr(ring + stage * R::BYTES);
-                        const int nblk = min(F_NBC, P.nb - cc * F_NBC), blk0 = cc * F_NBC;
-                        const int r0x = row_of(sx);
-                        const uint32_t xq_s = smem_addr(smem + L.x0 + r0x * P.x_stride);
-                        const uint32_t xsT_s = smem_addr(xsT + r0x), xsumT_s = smem_addr(xsumT + r0x);
-                        switch (G) {
-                            case 1: fast_chunk<KIND, 1, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
-                            case 2: fast_chunk<KIND, 2, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
-                            case 3: fast_chunk<KIND, 3, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
-                            default: fast_chunk<KIND, 4, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+#pragma unroll 1
+                        for (int cc = 0; cc < P.nchunks; cc++) {
+                            uint32_t rec;
+                            const uint32_t wtok = next_record(rec);
+                            if (!wtok) {
+                                ok = false;
+                                return;
+                            }
+                            fast_chunk<KIND, GT, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, min(F_NBC, P.nb - cc * F_NBC),
+                                                         cc * F_NBC, lane, wtok, xtok, acc, off);
+                            __syncwarp();
+                            takes++;
                         }
-                        __syncwarp();
-                        if (cc == P.nchunks - 1) {
-                            const int u = wu % P.upe;
-                            const uint16_t* list = s_lists + sx * D_TOK;
+                        const uint16_t* list = s_lists + sx * D_TOK;
 #pragma unroll
-                            for (int nt = 0; nt < D_GMAX; nt++) {
+                        for (int nt = 0; nt < GT; nt++) {
 #pragma unroll
-                                for (int i = 0; i < 2; i++) {
-                                    const int j = nt * 8 + 2 * tq + i;
-                                    if (nt < G && j < cnt) {
-                                        float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
-                                        if (KIND == 2) {
-                                            y0 = y0 + off[nt][i];
-                                            y1 = y1 + off[nt][2 + i];
+                            for (int i = 0; i < 2; i++) {
+                                const int j = nt * 8 + 2 * tq + i;
+                                if (j < cnt) {
+                                    float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
+                                    if (KIND == 2) {
+                                        y0 = y0 + off[nt][i];
+                                        y1 = y1 + off[nt][2 + i];
+                                    }
+                                    const size_t slot = list[j];
+                                    if (gate_up) {
+                                        const int col = u * 8 + g;
+                                        if (col < inter) {
+                                            const float ex = exp_poly(-y0);
+                                            a.hidden_f[slot * inter + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
                                         }
-                                        const size_t slot = list[j];
-                                        if (gate_up) {
-                                            const int col = u * 8 + g;
-                                            if (col < inter) {
-                                                const float ex = exp_poly(-y0);
-                                                a.hidden_f[slot * inter + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
-                                            }
-                                        } else {
-                                            const int r0 = u * F_ROWS + g;
-                                            if (r0 < hidden) a.out[slot * hidden + r0] = y0;
-                                            if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
-                                        }
+                                    } else {
+                                        const int r0 = u * F_ROWS + g;
+                                        if (r0 < hidden) a.out[slot * hidden + r0] = y0;
+                                        if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
                                     }
                                 }
                             }
                         }
+                    };
+                    switch (G) {
+                        case 0:  // an expert nobody picked (dense walk): its records are only drained
+                            for (int cc = 0; cc < P.nchunks && ok; cc++) {
+                                uint32_t rec;
+                                ok = next_record(rec) != 0u;
+                                if (ok) takes++;
+                            }
+                            break;
+                        case 1: unit(std::integral_constant<int, 1>{}); break;
+                        case 2: unit(std::integral_constant<int, 2>{}); break;
+                        case 3: unit(std::integral_constant<int, 3>{}); break;
+                        default: unit(std::integral_constant<int, 4>{}); break;
                     }
-                    takes++;
-                    if (++cc == P.nchunks) cc = 0, cu++;
+                    cu++;
                 }
                 ok = __syncthreads_and(ok);  // keep the decision to stop uniform across the CTA's barriers
                 xphase++;
@@ -485,9 +617,15 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         if (tid == 0) {
             if (!ok) s_abort = 3;
             grid_arrive(a.sync + 1 + p);
-            // After gate_up everyone goes on to down; after down only the combining CTAs stay.
-            if (ok && (p == 0 || bid < t) && !grid_wait(a.sync + 1 + p, uint32_t(nctas), a.spin_limit)) s_abort = 2;
         }
+        if (p == 0 && ok) {  // the lists of the down phase depend on the ids only: made while the others finish
+            int f, l;
+            seg_range(P1, f, l);
+            if (f <= l) build_lists(f, min(D_NSEG, l - f + 1));
+        }
+        // After gate_up everyone goes on to down; after down only the combining CTAs stay.
+        if (tid == 0 && ok && (p == 0 || bid < t) && !grid_wait(a.sync + 1 + p, uint32_t(nctas), a.spin_limit))
+            s_abort = 2;
         __syncthreads();
         ok = !s_abort;
         if (stamping) a.stamps[3 + p] = wall_clock_ns();
@@ -538,30 +676,50 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         }
         // Give copies already in flight a bounded chance to land before the shared memory
         // they target is released.
-        for (uint32_t k = takes; k < fills; k++) mbar_wait_bounded(bars + k % STAGES, (k / STAGES) & 1);
+        for (uint32_t k = takes; k < fills; k++) {
+            mbar_wait_poll(bars + cslot, cpar);
+            if (++cslot == STAGES) cslot = 0, cpar ^= 1;
+        }
     }
+}
+
+// Rows of the router matrix the router phase stages at a time: the whole matrix, or the
+// fewest equal parts, within what the token area offers anyway (a dense walk, where the
+// ring's depth matters) or within 72 KB (a sparse walk, where the ring is mostly idle).
+template <int KIND>
+int decode_route_rows(const MoeDims& d, int t, int xcap, int nthreads) {
+    const int held = D_ROUTE_VEC * nthreads / (d.hidden / 8);  // rows the CTA's registers hold at a time
+    const int tokens = DLayout<KIND>::token_bytes(xcap, d.hidden, d.inter);
+    const int base = DLayout<KIND>::route_base(d.hidden, d.experts) + 64, wstride = 2 * d.hidden + 32;
+    const int budget = dense_walk(d, t) ? tokens + 2048 : max(tokens, 72 * 1024);
+    for (int parts = 1; parts <= 8; parts++) {
+        const int rows = (d.experts + parts - 1) / parts;
+        if (rows <= held && base + rows * wstride <= budget) return rows;
+    }
+    return max(0, min(held, (tokens - base) / wstride));
 }
 
 // Warps per CTA, ring depth and staged rows: as many warps as possible while each still
 // gets a ring of at least three stages; then the deepest ring that fits.
 template <int KIND>
-bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap) {
+bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap, int& route_rows) {
     xcap = min(D_TOK, (t + 7) / 8 * 8);
-    auto deepest = [&](int w) {
+    auto deepest = [&](int w, int rr) {
         for (int k = D_MAX_STAGES; k >= 2; k--)
-            if (size_t(DLayout<KIND>(w, k, xcap, d.hidden, d.inter, d.experts, d.topk).total) <= D_SMEM_LIMIT) return k;
+            if (size_t(DLayout<KIND>(w, k, xcap, rr, d.hidden, d.inter, d.experts, d.topk).total) <= D_SMEM_LIMIT) return k;
         return 0;
     };
-    int best_w = 0, best_s = 0;
+    int best_w = 0, best_s = 0, best_r = 0;
     for (int w = D_MAX_WARPS; w >= 8; w -= 2) {
-        const int s = deepest(w);
+        const int rr = decode_route_rows<KIND>(d, t, xcap, w * 32);
+        const int s = deepest(w, rr);
         if (s >= 3) {
-            nwarps = w, stages = s;
+            nwarps = w, stages = s, route_rows = rr;
             return true;
         }
-        if (s > best_s) best_s = s, best_w = w;
+        if (s > best_s) best_s = s, best_w = w, best_r = rr;
     }
-    nwarps = best_w, stages = best_s;
+    nwarps = best_w, stages = best_s, route_rows = best_r;
     return best_s >= 2;
 }
 
@@ -575,8 +733,8 @@ void init_kernels_decode() {
 
 bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t) {
     if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK) return false;
-    int w, s, x;
-    return kind_gate_up == 1 ? decode_config<1>(d, t, w, s, x) : decode_config<2>(d, t, w, s, x);
+    int w, s, x, r;
+    return kind_gate_up == 1 ? decode_config<1>(d, t, w, s, x, r) : decode_config<2>(d, t, w, s, x, r);
 }
 
 int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
@@ -595,15 +753,16 @@ int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, cons
     a.spin_limit = spin_limit;
     a.status = ws.status;
     int nwarps = 0;
-    const bool fits = kind == 1 ? decode_config<1>(d, t, nwarps, a.stages, a.xcap) : decode_config<2>(d, t, nwarps, a.stages, a.xcap);
+    const bool fits = kind == 1 ? decode_config<1>(d, t, nwarps, a.stages, a.xcap, a.route_rows)
+                                : decode_config<2>(d, t, nwarps, a.stages, a.xcap, a.route_rows);
     if (!fits) return -1;
     // One CTA per SM, all resident at once (they wait for one another): never more CTAs than SMs.
     const int grid = sms;
     if (kind == 1) {
-        const DLayout<1> L(nwarps, a.stages, a.xcap, d.hidden, d.inter, d.experts, d.topk);
+        const DLayout<1> L(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts, d.topk);
         launch_overlapped(moe_decode_kernel<1>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
     } else {
-        const DLayout<2> L(nwarps, a.stages, a.xcap, d.hidden, d.inter, d.experts, d.topk);
+        const DLayout<2> L(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts, d.topk);
         launch_overlapped(moe_decode_kernel<2>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
     }
     return 1;

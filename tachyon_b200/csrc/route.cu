@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
         if (a.norm_w) route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, ROUTE_THREADS);
 
         if (a.stage_router && token == int(blockIdx.x)) w_landed = mbar_wait_bounded(&s_wbar, 0);
-        route_logits(a.router, a.stage_router && w_landed ? wsm : nullptr, wstride, xrow, a.bias, hidden, experts,
+        route_logits(a.router, a.stage_router && w_landed ? wsm : nullptr, wstride, xrow, a.bias, hidden, 0, experts,
                      slog, a.logits ? a.logits + size_t(token) * experts : nullptr, tid, ROUTE_THREADS);
         __syncthreads();
 

@@ -84,25 +84,26 @@ __device__ __forceinline__ void route_norm_row(float* xrow, int hidden, const fl
     __syncthreads();
 }
 
-// Router logits of one token into slog[0..experts) (and, when given, a global row).
+// Router logits of one token, experts e_lo..e_hi-1, into slog[e] (and, when given, a global row).
 // Four threads per expert, each holding four of the dot's sixteen float lanes: thread q
 // owns elements 16j+4q..16j+4q+3, so q = 0,1 hold the first 8-lane accumulator and
 // q = 2,3 the second. `staged`: the router matrix in shared memory with rows `wstride`
-// bytes apart, or null to read it from global memory (a whole batch of steps is
-// requested before the chains run, so the loads overlap instead of each waiting for the
-// previous fma). Called by every thread; the caller puts a CTA barrier after it.
+// bytes apart and row 0 holding expert e_lo, or null to read it from global memory (a whole
+// batch of steps is requested before the chains run, so the loads overlap instead of each
+// waiting for the previous fma). Called by every thread; the caller puts a CTA barrier
+// after it.
 __device__ __forceinline__ void route_logits(const uint16_t* router, const uint8_t* staged, int wstride,
-                                             const float* xrow, const float* bias, int hidden, int experts,
+                                             const float* xrow, const float* bias, int hidden, int e_lo, int e_hi,
                                              float* slog, float* logits_row, int tid, int nthreads) {
     constexpr int BATCH = 16;
-    for (int e0 = 0; e0 < experts; e0 += nthreads / 4) {
+    for (int e0 = e_lo; e0 < e_hi; e0 += nthreads / 4) {
         const int e = e0 + (tid >> 2), q = tid & 3;
-        const bool valid = e < experts;
-        const uint16_t* w = router + size_t(valid ? e : 0) * hidden + q * 4;
+        const bool valid = e < e_hi;
+        const uint16_t* w = router + size_t(valid ? e : e_lo) * hidden + q * 4;
         const float* xr = xrow + q * 4;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (staged) {
-            const uint8_t* ws = staged + size_t(valid ? e : 0) * wstride + q * 8;
+            const uint8_t* ws = staged + size_t(valid ? e - e_lo : 0) * wstride + q * 8;
 #pragma unroll 8
             for (int c = 0; c < hidden; c += 16) {
                 const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
