@@ -37,8 +37,6 @@
 // (grid_wait). A wait that runs out sets the status word, and the CTA skips to the end,
 // waits (bounded) for its copies in flight and returns; tc_sync reports it and clears
 // the counters.
-#include <type_traits>
-
 #include "experts_fast.cuh"
 #include "route_common.cuh"
 
@@ -50,6 +48,7 @@ constexpr int D_MAX_WARPS = 16;
 constexpr int D_MAX_STAGES = 8;
 constexpr int D_GMAX = 4;          // token tiles of 8 held in registers
 constexpr int D_TOK = 8 * D_GMAX;  // tokens per block this kernel takes; rows staged at a time
+constexpr int D_NORM_HELD = 8;     // elements of the norm's weight a thread holds (rows of up to 8 x 256 floats)
 constexpr int D_ROUTE_VEC = 10;    // 16-byte pieces of the router matrix a thread holds at a time
 constexpr int D_NSEG = 4;          // experts of a CTA's range whose slot lists are held at a time
 constexpr size_t D_SMEM_LIMIT = 227 * 1024 - 2048;  // dynamic part: the kernel also has about 1.2 KB of static shared memory
@@ -109,7 +108,7 @@ struct DLayout {
         ids = o;
         o += D_TOK * topk * 4;
         lists = o;
-        o += D_NSEG * D_TOK * 2;
+        o += D_NSEG * D_TOK * 2 * 2;
         o = (o + 15) / 16 * 16;
         bars = o;
         o += D_MAX_WARPS * D_MAX_STAGES * 8;
@@ -174,7 +173,8 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * D_MAX_STAGES;
     uint32_t* s_ids = reinterpret_cast<uint32_t*>(smem + L.ids);
-    uint16_t* s_lists = reinterpret_cast<uint16_t*>(smem + L.lists);
+    uint16_t* s_slot = reinterpret_cast<uint16_t*>(smem + L.lists);  // [D_NSEG][D_TOK] slots that named the segment's expert
+    uint16_t* s_tok = s_slot + D_NSEG * D_TOK;                        // the same slots' tokens
     if (lane == 0) {
         for (int s = 0; s < STAGES; s++) mbar_init(bars + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -197,10 +197,10 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         P.x_stride = P.cols + 16;
     };
     derive(P0), derive(P1);
-    auto share = [&](Phase& P, int walk_experts) {
-        const int total = walk_experts * P.upe;
-        P.lo = int((long long)bid * total / nctas);
-        P.hi = int((long long)(bid + 1) * total / nctas);
+    auto share = [&](Phase& P, unsigned walk_experts) {  // (bid + 1) * total stays far below 2^32
+        const unsigned total = walk_experts * unsigned(P.upe);
+        P.lo = int(unsigned(bid) * total / unsigned(nctas));
+        P.hi = int(unsigned(bid + 1) * total / unsigned(nctas));
         P.first = P.lo + warp;
         P.n = P.first < P.hi ? (P.hi - P.first + nwarps - 1) / nwarps : 0;
     };
@@ -222,34 +222,29 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         pwu = P.first, pchunks = P.nchunks, punits = P.n;
         if (P.n > 0) pptr = unit_ptr(P, pwu);
     };
-    auto fill_next = [&]() {  // precondition: fills < nrec
-        if (lane == 0) {
-            mbar_expect_tx(bars + pslot, R::BYTES);
-            bulk_copy_once(ring + pslot * R::BYTES, pptr, R::BYTES, bars + pslot, stream_policy);
-        }
-        fills++;
-        pslot = pslot + 1 == STAGES ? 0 : pslot + 1;
-        pptr += R::BYTES;
-        if (--pchunks == 0) {
-            const Phase& P = pphase ? P1 : P0;
-            if (--punits > 0) {
-                pwu += nwarps;
-                pchunks = P.nchunks;
-                pptr = a.dense ? pptr + size_t(nwarps - 1) * P.nchunks * R::BYTES : unit_ptr(P, pwu);
-            } else if (pphase == 0) {
-                start_phase(1);
+    // Requests records until the ring is full or the sequence ends.
+    auto top_up = [&]() {
+#pragma unroll 1
+        while (fills < nrec && fills - takes < uint32_t(STAGES)) {
+            if (lane == 0) {
+                mbar_expect_tx(bars + pslot, R::BYTES);
+                bulk_copy_once(ring + pslot * R::BYTES, pptr, R::BYTES, bars + pslot, stream_policy);
+            }
+            fills++;
+            pslot = pslot + 1 == STAGES ? 0 : pslot + 1;
+            pptr += R::BYTES;
+            if (--pchunks == 0) {
+                const Phase& P = pphase ? P1 : P0;
+                if (--punits > 0) {
+                    pwu += nwarps;
+                    pchunks = P.nchunks;
+                    pptr = a.dense ? pptr + size_t(nwarps - 1) * P.nchunks * R::BYTES : unit_ptr(P, pwu);
+                } else if (pphase == 0) {
+                    start_phase(1);
+                }
             }
         }
     };
-    auto begin_stream = [&](int walk_experts) {
-        share(P0, walk_experts), share(P1, walk_experts);
-        nrec = uint32_t(P0.n * P0.nchunks + P1.n * P1.nchunks);
-        start_phase(P0.n > 0 ? 0 : 1);
-        while (fills < nrec && fills < uint32_t(STAGES)) fill_next();
-    };
-    // The partition of a dense walk does not depend on the routing: the ring fills before this
-    // grid waits for the kernel in front of it, and through the router phase.
-    if (a.dense) begin_stream(experts);
 
     // ---- router phase, part one (constants only): CTA i < t takes token i. The router matrix
     // is staged in shared memory beside the token's row, route_rows rows at a time (rows
@@ -262,13 +257,12 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     float* slog = xrow + hidden;
     const int wstride = 2 * hidden + 32;
     uint8_t* wsm = smem + L.x0 + DLayout<KIND>::route_base(hidden, experts);
-    const int pass_rows = a.route_rows;
+    const int pass_rows = a.route_rows > 0 ? a.route_rows : experts;  // (0: the logits read global memory)
     const int vec_per_wrow = hidden / 8;  // 16-byte pieces of a router row
-    constexpr int NW = 8;
-    float nw[NW];
+    float nw[D_NORM_HELD];
     uint4 rv[D_ROUTE_VEC];
     auto request_router_rows = [&](int e_lo) {
-        const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
+        const int n = a.route_rows > 0 ? min(pass_rows, experts - e_lo) * vec_per_wrow : 0;
         const uint4* src = reinterpret_cast<const uint4*>(a.router + size_t(e_lo) * hidden);
 #pragma unroll
         for (int k = 0; k < D_ROUTE_VEC; k++) {
@@ -276,41 +270,44 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
             if (i < n) rv[k] = __ldg(src + i);
         }
     };
-    auto store_router_rows = [&](int e_lo) {
-        const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
-#pragma unroll
-        for (int k = 0; k < D_ROUTE_VEC; k++) {
-            const int i = tid + k * nthreads;
-            if (i < n) {
-                const int r = i / vec_per_wrow, v = i - r * vec_per_wrow;
-                *reinterpret_cast<uint4*>(wsm + size_t(r) * wstride + v * 16) = rv[k];
-            }
-        }
-    };
     const bool routing = bid < t;
-    const bool nw_held = a.norm_w && hidden <= NW * nthreads;
-    if (routing) {
-        if (pass_rows > 0) request_router_rows(0);
-        if (nw_held) {
+    // Every CTA starts its stream here when the partition does not depend on the routing
+    // (dense walk): the ring fills before this grid waits for the kernel in front of it, and
+    // through the router phase. Otherwise after the router phase, once the picked experts are known.
+    bool streaming = false;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; pass++) {
+        if (pass == 0 ? bool(a.dense) : !streaming) {
+            if (pass == 1 && s_abort) break;
+            const unsigned walk = a.dense ? unsigned(experts) : unsigned(s_nactive);
+            share(P0, walk), share(P1, walk);
+            nrec = uint32_t(P0.n * P0.nchunks + P1.n * P1.nchunks);
+            start_phase(P0.n > 0 ? 0 : 1);
+            top_up();
+            streaming = true;
+        }
+        if (pass == 1) break;
+        if (routing) {
+            request_router_rows(0);
+            if (a.norm_w) {
 #pragma unroll
-            for (int k = 0; k < NW; k++) {
-                const int c = tid + k * nthreads;
-                nw[k] = c < hidden ? a.norm_w[c] : 0.0f;
+                for (int k = 0; k < D_NORM_HELD; k++) {
+                    const int c = tid + k * nthreads;
+                    nw[k] = c < hidden ? a.norm_w[c] : 0.0f;
+                }
             }
         }
-    }
-    grid_dependency_wait();  // everything below reads or writes what other kernels touch
-    if (stamping) a.stamps[1] = wall_clock_ns();
+        grid_dependency_wait();  // everything below reads or writes what other kernels touch
+        if (stamping) a.stamps[1] = wall_clock_ns();
 
-    // ---- router phase, part two
-    bool ok = true;
-    if (routing) {
-        const float* xin = a.x + size_t(bid) * hidden;
-        for (int c = tid * 4; c < hidden; c += nthreads * 4)
-            *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
-        __syncthreads();
-        if (a.norm_w) {
-            if (nw_held) {
+        // ---- router phase, part two
+        if (routing) {
+            const float* xin = a.x + size_t(bid) * hidden;
+#pragma unroll 1
+            for (int c = tid * 4; c < hidden; c += nthreads * 4)
+                *reinterpret_cast<float4*>(xrow + c) = *reinterpret_cast<const float4*>(xin + c);
+            __syncthreads();
+            if (a.norm_w) {
                 if (warp == 0) {
                     const float ss = __fdiv_rn(sum_squares_avx_order(xrow, hidden, lane), float(hidden));
                     if (lane == 0) s_inv = __fdiv_rn(1.0f, __fsqrt_rn(ss + a.eps));
@@ -318,87 +315,71 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 __syncthreads();
                 const float inv = s_inv;
 #pragma unroll
-                for (int k = 0; k < NW; k++) {
+                for (int k = 0; k < D_NORM_HELD; k++) {
                     const int c = tid + k * nthreads;
                     if (c < hidden) xrow[c] = xrow[c] * inv * nw[k];
                 }
                 __syncthreads();
-            } else {
-                route_norm_row(xrow, hidden, a.norm_w, a.eps, &s_inv, tid, nthreads);
             }
-        }
-        float* logits_row = a.logits ? a.logits + size_t(bid) * experts : nullptr;
-        if (pass_rows > 0) {
+            float* logits_row = a.logits ? a.logits + size_t(bid) * experts : nullptr;
+#pragma unroll 1
             for (int e_lo = 0; e_lo < experts; e_lo += pass_rows) {
-                store_router_rows(e_lo);
-                if (e_lo + pass_rows < experts) request_router_rows(e_lo + pass_rows);
-                __syncthreads();
-                route_logits(a.router, wsm, wstride, xrow, a.bias, hidden, e_lo, min(experts, e_lo + pass_rows), slog,
-                             logits_row, tid, nthreads);
+                if (a.route_rows > 0) {
+                    const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
+                    int r = tid / vec_per_wrow, v = tid - r * vec_per_wrow;  // piece tid + k * nthreads = (row r, piece v)
+                    const int dr = nthreads / vec_per_wrow, dv = nthreads - dr * vec_per_wrow;
+#pragma unroll
+                    for (int k = 0; k < D_ROUTE_VEC; k++) {
+                        if (tid + k * nthreads < n) *reinterpret_cast<uint4*>(wsm + size_t(r) * wstride + v * 16) = rv[k];
+                        r += dr, v += dv;
+                        if (v >= vec_per_wrow) v -= vec_per_wrow, r++;
+                    }
+                    if (e_lo + pass_rows < experts) request_router_rows(e_lo + pass_rows);
+                    __syncthreads();
+                }
+                route_logits(a.router, a.route_rows > 0 ? wsm : nullptr, wstride, xrow, a.bias, hidden, e_lo,
+                             min(experts, e_lo + pass_rows), slog, logits_row, tid, nthreads);
                 __syncthreads();  // the staged rows are no longer read; slog is complete up to here
             }
-        } else {
-            route_logits(a.router, nullptr, 0, xrow, a.bias, hidden, 0, experts, slog, logits_row, tid, nthreads);
+            if (warp == 0)
+                route_topk_gates(slog, experts, topk, a.ids + size_t(bid) * topk, a.gates + size_t(bid) * topk, lane);
+            route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * P0.nbp,
+                               a.xsum + size_t(bid) * P0.nbp, warp, lane, 1, nwarps - 1);
             __syncthreads();
+            if (tid == 0) grid_arrive(a.sync + 0);
         }
-        if (warp == 0)
-            route_topk_gates(slog, experts, topk, a.ids + size_t(bid) * topk, a.gates + size_t(bid) * topk, lane);
-        route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * P0.nbp,
-                           a.xsum + size_t(bid) * P0.nbp, warp, lane, 1, nwarps - 1);
+        if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) s_abort = 1;
         __syncthreads();
-        if (tid == 0) grid_arrive(a.sync + 0);
-    }
-    if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) s_abort = 1;
-    __syncthreads();
-    ok = !s_abort;
-    if (stamping) a.stamps[2] = wall_clock_ns();
+        if (stamping) a.stamps[2] = wall_clock_ns();
 
-    // ---- the batch's expert ids; for small batches the experts that were picked
-    if (ok) {
-        for (int i = tid; i < slots; i += nthreads) s_ids[i] = __ldcg(a.ids + i);
-        if (!a.dense)
-            for (int e = tid; e < experts; e += nthreads) s_picked[e] = 0;
-        __syncthreads();
-        if (!a.dense) {
-            for (int i = tid; i < slots; i += nthreads) s_picked[s_ids[i]] = 1;
-            __syncthreads();
-            if (warp == 0) {
-                int n = 0;
-                for (int e0 = 0; e0 < experts; e0 += 32) {
-                    const int e = e0 + lane;
-                    const bool on = e < experts && s_picked[e];
-                    const unsigned ballot = __ballot_sync(0xffffffffu, on);
-                    if (on) s_active[n + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(e);
-                    n += __popc(ballot);
+        // ---- the batch's expert ids; for small batches the experts that were picked
+        if (!s_abort) {
+#pragma unroll 1
+            for (int i = tid; i < slots; i += nthreads) s_ids[i] = __ldcg(a.ids + i);
+            if (!a.dense) {
+#pragma unroll 1
+                for (int e = tid; e < experts; e += nthreads) s_picked[e] = 0;
+                __syncthreads();
+#pragma unroll 1
+                for (int i = tid; i < slots; i += nthreads) s_picked[s_ids[i]] = 1;
+                __syncthreads();
+                if (warp == 0) {
+                    int n = 0;
+#pragma unroll 1
+                    for (int e0 = 0; e0 < experts; e0 += 32) {
+                        const int e = e0 + lane;
+                        const bool on = e < experts && s_picked[e];
+                        const unsigned ballot = __ballot_sync(0xffffffffu, on);
+                        if (on) s_active[n + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(e);
+                        n += __popc(ballot);
+                    }
+                    if (lane == 0) s_nactive = n;
                 }
-                if (lane == 0) s_nactive = n;
             }
             __syncthreads();
-            begin_stream(s_nactive);
         }
     }
-
-    // The slots that named each expert of a batch of (up to D_NSEG) segments, ascending: one
-    // warp per segment. Ends with a CTA barrier.
-    auto build_lists = [&](int sb, int nseg) {
-        if (warp < nseg) {
-            const int walk = sb + warp;
-            const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
-            int count = 0;
-            for (int base = 0; base < slots; base += 32) {
-                const bool hit = base + lane < slots && s_ids[base + lane] == e;
-                const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-                if (hit) s_lists[warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u))] = uint16_t(base + lane);
-                count += __popc(ballot);
-            }
-            if (lane == 0) s_seg_count[warp] = count;
-        }
-        __syncthreads();
-    };
-    auto seg_range = [&](const Phase& P, int& first, int& last) {
-        first = P.lo < P.hi ? P.lo / P.upe : 0;
-        last = P.lo < P.hi ? (P.hi - 1) / P.upe : -1;
-    };
+    bool ok = !s_abort;
 
     const int g = lane >> 2, tq = lane & 3;
     float acc[D_GMAX][4], off[D_GMAX][4];
@@ -406,11 +387,6 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     int arrived = 0;  // expert phases this CTA has announced
     int cslot = 0;    // consumer's ring slot and the parity of its barrier
     uint32_t cpar = 0;
-    if (ok) {
-        int f, l;
-        seg_range(P0, f, l);
-        if (f <= l) build_lists(f, min(D_NSEG, l - f + 1));
-    }
 
 #pragma unroll 1
     for (int p = 0; p < 2 && ok; p++) {
@@ -421,14 +397,45 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         const int xsum_off = xs_off + P.nbp * D_TOK * 4;
         float* xsT = reinterpret_cast<float*>(smem + L.x0 + xs_off);
         float* xsumT = reinterpret_cast<float*>(smem + L.x0 + xsum_off);
-        int seg_first, seg_last;
-        seg_range(P, seg_first, seg_last);
+        const int seg_first = P.lo < P.hi ? P.lo / P.upe : 0;
+        const int seg_last = P.lo < P.hi ? (P.hi - 1) / P.upe : -1;
 #pragma unroll 1
         for (int sb = seg_first; sb <= seg_last && ok; sb += D_NSEG) {
             const int nseg = min(D_NSEG, seg_last - sb + 1);
-            if (sb != seg_first) {  // (the phase's first lists were made before the wait for this phase)
-                __syncthreads();    // the previous lists and staged rows are no longer read
-                build_lists(sb, nseg);
+            if (sb != seg_first) __syncthreads();  // the previous lists and staged rows are no longer read
+            // ---- the slots that named each expert of this batch of segments, ascending: a warp per segment
+            if (warp < nseg) {
+                const int walk = sb + warp;
+                const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
+                int count = 0, token = 0, pick = lane;  // slot base + lane = token * topk + pick
+                while (pick >= topk) pick -= topk, token++;
+#pragma unroll 1
+                for (int base = 0; base < slots; base += 32) {
+                    const bool hit = base + lane < slots && s_ids[base + lane] == e;
+                    const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+                    if (hit) {
+                        const int at = warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u));
+                        s_slot[at] = uint16_t(base + lane);
+                        s_tok[at] = uint16_t(token);
+                    }
+                    count += __popc(ballot);
+                    pick += 32;
+                    while (pick >= topk) pick -= topk, token++;
+                }
+                if (lane == 0) s_seg_count[warp] = count;
+            }
+            if (sb == seg_first && p == 1) {
+                // The lists depend on the ids only: they were made while the other CTAs finished
+                // gate_up. Their SwiGLU rows are read from here on.
+                if (tid == 0 && !grid_wait(a.sync + 1, uint32_t(nctas), a.spin_limit)) s_abort = 2;
+            }
+            __syncthreads();
+            if (sb == seg_first && p == 1) {
+                if (stamping) a.stamps[3] = wall_clock_ns();
+                if (s_abort) {
+                    ok = false;
+                    break;
+                }
             }
             int si = 0;
 #pragma unroll 1
@@ -448,44 +455,44 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 }
                 auto row_of = [&](int sx) { return sx == 0 ? row0[0] : sx == 1 ? row0[1] : sx == 2 ? row0[2] : row0[3]; };
                 if (si > 0) __syncthreads();  // the previous group's rows are no longer read
-                // The group's rows as one list (staged row r belongs to the last segment that starts at
-                // or before it), so that every load of the group is in flight at once.
-                auto slot_of_row = [&](int r) -> uint32_t {
+                // Staged row r belongs to the last segment that starts at or before it; rows past a
+                // segment's tokens (up to a whole tile of 8) repeat its last one.
+                auto entry_of_row = [&](int r) {
                     int sx = si;
 #pragma unroll
                     for (int k = 1; k < D_NSEG; k++)
                         if (k > si && k < sj && r >= row0[k]) sx = k;
-                    const int cnt = s_seg_count[sx];
-                    return s_lists[sx * D_TOK + min(r - row_of(sx), cnt - 1)];
+                    return sx * D_TOK + min(r - row_of(sx), s_seg_count[sx] - 1);
                 };
                 if (gate_up) {
-                    // Token rows by plain 16-byte loads (L2 hits: the router phase just wrote them).
-                    const int vec_per_row = P.cols / 16, n = rows * vec_per_row;
-#pragma unroll 4
-                    for (int i = tid; i < n; i += nthreads) {
-                        const int r = i / vec_per_row, v = i - r * vec_per_row;
-                        const uint32_t token = slot_of_row(r) / uint32_t(topk);
-                        const uint4 val = __ldcg(reinterpret_cast<const uint4*>(a.xq + size_t(token) * P.cols) + v);
-                        *reinterpret_cast<uint4*>(smem + L.x0 + r * P.x_stride + v * 16) = val;
-                    }
-                    // Scales transposed to [block][token]; token fastest, so stores do not conflict.
-                    const int ns = P.nb * rows;
+                    // Token rows by plain 16-byte loads (L2 hits: the router phase just wrote them), a
+                    // warp per row; then the scales transposed to [block][token], a warp per block
+                    // and a lane per row, so that the stores do not conflict.
+                    const int vec_per_row = P.cols / 16;
+#pragma unroll 1
+                    for (int r = warp; r < rows; r += nwarps) {
+                        const uint4* src = reinterpret_cast<const uint4*>(a.xq + size_t(s_tok[entry_of_row(r)]) * P.cols);
+                        uint8_t* dst = smem + L.x0 + r * P.x_stride;
 #pragma unroll 2
-                    for (int i = tid; i < ns; i += nthreads) {
-                        const int b = i / rows, r = i - b * rows;
-                        const uint32_t token = slot_of_row(r) / uint32_t(topk);
-                        const size_t src = size_t(token) * P.nbp + b;
-                        xsT[b * D_TOK + r] = __ldcg(a.xs + src);
-                        if (KIND == 2) xsumT[b * D_TOK + r] = __ldcg(a.xsum + src);
+                        for (int v = lane; v < vec_per_row; v += 32) *reinterpret_cast<uint4*>(dst + v * 16) = __ldcg(src + v);
+                    }
+                    if (lane < rows) {
+                        const size_t src = size_t(s_tok[entry_of_row(lane)]) * P.nbp;
+#pragma unroll 2
+                        for (int b = warp; b < P.nb; b += nwarps) {
+                            xsT[b * D_TOK + lane] = __ldcg(a.xs + src + b);
+                            if (KIND == 2) xsumT[b * D_TOK + lane] = __ldcg(a.xsum + src + b);
+                        }
                     }
                 } else {
                     // The down projection's inputs are the SwiGLU rows in f32: quantized here exactly as
                     // quantize_q8 does (src/kernels.rs:84-98, applied per gathered row by
                     // src/weights.rs:652-664), straight into the staged layout. A thread per
                     // (row, 32-block).
+#pragma unroll 1
                     for (int task = tid; task < rows * P.nb; task += nthreads) {
                         const int r = task / P.nb, b = task - r * P.nb;
-                        const size_t row = slot_of_row(r);
+                        const size_t row = s_slot[entry_of_row(r)];
                         const float4* src = reinterpret_cast<const float4*>(a.hidden_f + row * P.cols + b * QK);
                         float4 v[8];
 #pragma unroll
@@ -522,6 +529,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 asm volatile("mov.u32 %0, %1;" : "=r"(xtok) : "r"(xphase) : "memory");
 
                 // ---- this warp's units of the group's segments, a unit (all its chunks) at a time
+#pragma unroll 1
                 while (ok && cu < P.n) {
                     const int wu = P.first + cu * nwarps;
                     const int seg = wu / P.upe;
@@ -531,76 +539,59 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     const int cnt = s_seg_count[sx], G = (cnt + 7) >> 3, r0x = row_of(sx);
                     const uint32_t xq_s = smem_addr(smem + L.x0 + r0x * P.x_stride);
                     const uint32_t xsT_s = smem_addr(xsT + r0x), xsumT_s = smem_addr(xsumT + r0x);
-                    // Takes the unit's next record: tops the ring up, then waits for the record.
-                    // Returns 0 if the wait ran out, else a value that the reads of the record depend on.
-                    auto next_record = [&](uint32_t& rec) -> uint32_t {
-                        if (fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
-                        const bool landed = mbar_wait_poll(bars + cslot, cpar);
-                        if (!__all_sync(0xffffffffu, landed)) return 0u;
-                        rec = smem_addr(ring + cslot * R::BYTES);
-                        if (++cslot == STAGES) cslot = 0, cpar ^= 1;
-                        return uint32_t(landed);
-                    };
-                    auto unit = [&](auto tiles) {
-                        constexpr int GT = decltype(tiles)::value;
 #pragma unroll
-                        for (int nt = 0; nt < D_GMAX; nt++) {
-                            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
-                            off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
-                        }
+                    for (int nt = 0; nt < D_GMAX; nt++) {
+                        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+                        off[nt][0] = off[nt][1] = off[nt][2] = off[nt][3] = 0.0f;
+                    }
 #pragma unroll 1
-                        for (int cc = 0; cc < P.nchunks; cc++) {
-                            uint32_t rec;
-                            const uint32_t wtok = next_record(rec);
-                            if (!wtok) {
-                                ok = false;
-                                return;
-                            }
-                            fast_chunk<KIND, GT, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, min(F_NBC, P.nb - cc * F_NBC),
-                                                         cc * F_NBC, lane, wtok, xtok, acc, off);
-                            __syncwarp();
-                            takes++;
+                    for (int cc = 0; cc < P.nchunks; cc++) {
+                        // The unit's next record: the ring is topped up, then the record waited for.
+                        top_up();
+                        const bool landed = mbar_wait_poll(bars + cslot, cpar);
+                        if (!__all_sync(0xffffffffu, landed)) {
+                            ok = false;
+                            break;
                         }
-                        const uint16_t* list = s_lists + sx * D_TOK;
+                        const uint32_t rec = smem_addr(ring + cslot * R::BYTES), wtok = uint32_t(landed);
+                        const int nblk = min(F_NBC, P.nb - cc * F_NBC), blk0 = cc * F_NBC;
+                        switch (G) {
+                            case 0: break;  // an expert nobody picked (dense walk): its records are only drained
+                            case 1: fast_chunk<KIND, 1, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            case 2: fast_chunk<KIND, 2, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            case 3: fast_chunk<KIND, 3, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                            default: fast_chunk<KIND, 4, D_GMAX>(rec, xq_s, xsT_s, xsumT_s, P.x_stride, nblk, blk0, lane, wtok, xtok, acc, off); break;
+                        }
+                        __syncwarp();
+                        if (++cslot == STAGES) cslot = 0, cpar ^= 1;
+                        takes++;
+                    }
+                    if (!ok) break;
 #pragma unroll
-                        for (int nt = 0; nt < GT; nt++) {
+                    for (int nt = 0; nt < D_GMAX; nt++) {
 #pragma unroll
-                            for (int i = 0; i < 2; i++) {
-                                const int j = nt * 8 + 2 * tq + i;
-                                if (j < cnt) {
-                                    float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
-                                    if (KIND == 2) {
-                                        y0 = y0 + off[nt][i];
-                                        y1 = y1 + off[nt][2 + i];
+                        for (int i = 0; i < 2; i++) {
+                            const int j = nt * 8 + 2 * tq + i;
+                            if (j < cnt) {
+                                float y0 = acc[nt][i], y1 = acc[nt][2 + i];  // rows g and g+8
+                                if (KIND == 2) {
+                                    y0 = y0 + off[nt][i];
+                                    y1 = y1 + off[nt][2 + i];
+                                }
+                                const size_t slot = s_slot[sx * D_TOK + j];
+                                if (gate_up) {
+                                    const int col = u * 8 + g;
+                                    if (col < inter) {
+                                        const float ex = exp_poly(-y0);
+                                        a.hidden_f[slot * inter + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
                                     }
-                                    const size_t slot = list[j];
-                                    if (gate_up) {
-                                        const int col = u * 8 + g;
-                                        if (col < inter) {
-                                            const float ex = exp_poly(-y0);
-                                            a.hidden_f[slot * inter + col] = __fdiv_rn(y0, 1.0f + ex) * y1;
-                                        }
-                                    } else {
-                                        const int r0 = u * F_ROWS + g;
-                                        if (r0 < hidden) a.out[slot * hidden + r0] = y0;
-                                        if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
-                                    }
+                                } else {
+                                    const int r0 = u * F_ROWS + g;
+                                    if (r0 < hidden) a.out[slot * hidden + r0] = y0;
+                                    if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
                                 }
                             }
                         }
-                    };
-                    switch (G) {
-                        case 0:  // an expert nobody picked (dense walk): its records are only drained
-                            for (int cc = 0; cc < P.nchunks && ok; cc++) {
-                                uint32_t rec;
-                                ok = next_record(rec) != 0u;
-                                if (ok) takes++;
-                            }
-                            break;
-                        case 1: unit(std::integral_constant<int, 1>{}); break;
-                        case 2: unit(std::integral_constant<int, 2>{}); break;
-                        case 3: unit(std::integral_constant<int, 3>{}); break;
-                        default: unit(std::integral_constant<int, 4>{}); break;
                     }
                     cu++;
                 }
@@ -609,29 +600,24 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 si = sj;
             }
         }
+        if (!ok) break;
         // The ring is topped up with the next phase's records before this CTA waits for the others.
-        while (ok && fills < nrec && fills - takes < uint32_t(STAGES)) fill_next();
+        top_up();
         // ---- every CTA's part of this phase is in global memory before anyone reads it
         __syncthreads();
         arrived = p + 1;
-        if (tid == 0) {
-            if (!ok) s_abort = 3;
-            grid_arrive(a.sync + 1 + p);
-        }
-        if (p == 0 && ok) {  // the lists of the down phase depend on the ids only: made while the others finish
-            int f, l;
-            seg_range(P1, f, l);
-            if (f <= l) build_lists(f, min(D_NSEG, l - f + 1));
-        }
-        // After gate_up everyone goes on to down; after down only the combining CTAs stay.
-        if (tid == 0 && ok && (p == 0 || bid < t) && !grid_wait(a.sync + 1 + p, uint32_t(nctas), a.spin_limit))
-            s_abort = 2;
+        if (tid == 0) grid_arrive(a.sync + 1 + p);
+    }
+    if (!ok && tid == 0 && !s_abort) s_abort = 3;
+
+    // ---- weighted combine + residual add: CTA i < t takes token i (src/model.rs:513-519, 681),
+    // once every CTA's part of the down phase is in global memory.
+    if (ok && bid < t) {
+        if (tid == 0 && !grid_wait(a.sync + 2, uint32_t(nctas), a.spin_limit)) s_abort = 2;
         __syncthreads();
         ok = !s_abort;
-        if (stamping) a.stamps[3 + p] = wall_clock_ns();
+        if (stamping) a.stamps[4] = wall_clock_ns();
     }
-
-    // ---- weighted combine + residual add: CTA i < t takes token i (src/model.rs:513-519, 681)
     if (ok && bid < t) {
         if (tid < topk) {
             const uint32_t mine = s_ids[bid * topk + tid];
@@ -642,6 +628,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         }
         __syncthreads();
         float* yr = a.y + size_t(bid) * hidden;
+#pragma unroll 1
         for (int c = tid * 4; c < hidden; c += nthreads * 4) {
             float4 proj = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll 8
@@ -732,7 +719,8 @@ void init_kernels_decode() {
 }
 
 bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t) {
-    if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK) return false;
+    if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK || d.hidden > D_NORM_HELD * 256)
+        return false;
     int w, s, x, r;
     return kind_gate_up == 1 ? decode_config<1>(d, t, w, s, x, r) : decode_config<2>(d, t, w, s, x, r);
 }

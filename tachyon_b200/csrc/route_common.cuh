@@ -15,9 +15,10 @@
 //                    kept with max = the top score, sum taken in that order;
 //   quantization   - quantize_q8 (src/kernels.rs:84-98) per 32-block, as
 //                    quantize_input applies it per token (src/weights.rs:652-664).
-// The softmax exponential is evaluated in double precision and rounded to
-// float; the CPU path calls libm's expf. The two agree except where expf
-// itself is not correctly rounded, hence the 1e-5 tolerance on gates.
+// The softmax exponential is evaluated in double precision (a short polynomial of
+// this file, accurate to about 1e-16) and rounded to float; the CPU path calls libm's
+// expf. The two agree except where expf itself is not correctly rounded, hence the
+// 1e-5 tolerance on gates.
 #pragma once
 
 #include "common.cuh"
@@ -95,16 +96,19 @@ __device__ __forceinline__ void route_norm_row(float* xrow, int hidden, const fl
 __device__ __forceinline__ void route_logits(const uint16_t* router, const uint8_t* staged, int wstride,
                                              const float* xrow, const float* bias, int hidden, int e_lo, int e_hi,
                                              float* slog, float* logits_row, int tid, int nthreads) {
-    constexpr int BATCH = 16;
+    constexpr int BATCH = 8;
     for (int e0 = e_lo; e0 < e_hi; e0 += nthreads / 4) {
         const int e = e0 + (tid >> 2), q = tid & 3;
         const bool valid = e < e_hi;
         const uint16_t* w = router + size_t(valid ? e : e_lo) * hidden + q * 4;
         const float* xr = xrow + q * 4;
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        if (staged) {
+        // A warp none of whose eight experts exists skips the dot: it would only take
+        // shared-memory bandwidth from the warps that have work.
+        if (e0 + ((tid >> 5) << 3) >= e_hi) {
+        } else if (staged) {
             const uint8_t* ws = staged + size_t(valid ? e - e_lo : 0) * wstride + q * 8;
-#pragma unroll 8
+#pragma unroll 4
             for (int c = 0; c < hidden; c += 16) {
                 const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
                 const float4 xv = *reinterpret_cast<const float4*>(xr + c);
@@ -153,6 +157,36 @@ __device__ __forceinline__ void route_logits(const uint16_t* router, const uint8
     }
 }
 
+// exp(x) for x <= 0 in double precision, rounded to float: what the gating softmax needs
+// (its arguments are score - max score). Argument reduction by ln 2 in two parts, a
+// degree-13 Taylor polynomial on |r| <= ln(2)/2 (truncation error below 1e-17), and the
+// power of two put into the exponent. Results below the smallest float flush to zero as
+// the conversion would make them.
+__device__ __forceinline__ float exp_nonpositive_f64(float xf) {
+    if (xf != xf) return xf;
+    if (xf < -104.0f) return 0.0f;
+    const double x = double(xf);
+    const double n = rint(x * 1.4426950408889634);
+    double r = fma(-n, 6.93147180369123816490e-01, x);
+    r = fma(-n, 1.90821492927058770002e-10, r);
+    double p = 1.0 / 6227020800.0;
+    p = fma(p, r, 1.0 / 479001600.0);
+    p = fma(p, r, 1.0 / 39916800.0);
+    p = fma(p, r, 1.0 / 3628800.0);
+    p = fma(p, r, 1.0 / 362880.0);
+    p = fma(p, r, 1.0 / 40320.0);
+    p = fma(p, r, 1.0 / 5040.0);
+    p = fma(p, r, 1.0 / 720.0);
+    p = fma(p, r, 1.0 / 120.0);
+    p = fma(p, r, 1.0 / 24.0);
+    p = fma(p, r, 1.0 / 6.0);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);
+    const long long bits = __double_as_longlong(p) + (static_cast<long long>(n) << 52);
+    return float(__longlong_as_double(bits));
+}
+
 // Top-k and gates of one token, by ONE warp: lane l holds experts l, l+32, ...; after the
 // k rounds lane j < k holds the j-th pick and writes ids_row[j] / gates_row[j].
 __device__ __forceinline__ void route_topk_gates(const float* slog, int experts, int topk, uint32_t* ids_row,
@@ -197,7 +231,7 @@ __device__ __forceinline__ void route_topk_gates(const float* slog, int experts,
     }
     const float mx = __shfl_sync(0xffffffffu, my_val, 0);
     float ej = 0.0f;
-    if (lane < topk) ej = float(exp(double(my_val - mx)));
+    if (lane < topk) ej = exp_nonpositive_f64(my_val - mx);
     float sum = 0.0f;
     for (int j = 0; j < topk; j++) sum = sum + __shfl_sync(0xffffffffu, ej, j);
     if (lane < topk) {
