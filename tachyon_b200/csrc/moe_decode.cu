@@ -131,6 +131,20 @@ __device__ __forceinline__ bool grid_wait(const uint32_t* ctr, uint32_t target, 
     return false;
 }
 
+// Loads whose place in the program matters: requested early and used much later. (A plain
+// read-only load may be re-issued by the compiler next to its use instead of being kept
+// in registers, which would put the trip to memory back on the critical path.)
+__device__ __forceinline__ uint4 load_now_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float load_now_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ unsigned long long wall_clock_ns() {
     unsigned long long v;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v));
@@ -267,7 +281,18 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
 #pragma unroll
         for (int k = 0; k < D_ROUTE_VEC; k++) {
             const int i = tid + k * nthreads;
-            if (i < n) rv[k] = __ldg(src + i);
+            if (i < n) rv[k] = load_now_v4(src + i);
+        }
+    };
+    auto store_router_rows = [&](int e_lo) {
+        const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
+        int r = tid / vec_per_wrow, v = tid - r * vec_per_wrow;  // piece tid + k * nthreads = (row r, piece v)
+        const int dr = nthreads / vec_per_wrow, dv = nthreads - dr * vec_per_wrow;
+#pragma unroll
+        for (int k = 0; k < D_ROUTE_VEC; k++) {
+            if (tid + k * nthreads < n) *reinterpret_cast<uint4*>(wsm + size_t(r) * wstride + v * 16) = rv[k];
+            r += dr, v += dv;
+            if (v >= vec_per_wrow) v -= vec_per_wrow, r++;
         }
     };
     const bool routing = bid < t;
@@ -288,12 +313,16 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         }
         if (pass == 1) break;
         if (routing) {
+            // Part 0 of the router matrix goes all the way into shared memory before the wait,
+            // part 1 (if any) into registers.
             request_router_rows(0);
+            if (a.route_rows > 0) store_router_rows(0);
+            if (a.route_rows > 0 && pass_rows < experts) request_router_rows(pass_rows);
             if (a.norm_w) {
 #pragma unroll
                 for (int k = 0; k < D_NORM_HELD; k++) {
                     const int c = tid + k * nthreads;
-                    nw[k] = c < hidden ? a.norm_w[c] : 0.0f;
+                    nw[k] = c < hidden ? load_now_f32(a.norm_w + c) : 0.0f;
                 }
             }
         }
@@ -325,16 +354,10 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
 #pragma unroll 1
             for (int e_lo = 0; e_lo < experts; e_lo += pass_rows) {
                 if (a.route_rows > 0) {
-                    const int n = min(pass_rows, experts - e_lo) * vec_per_wrow;
-                    int r = tid / vec_per_wrow, v = tid - r * vec_per_wrow;  // piece tid + k * nthreads = (row r, piece v)
-                    const int dr = nthreads / vec_per_wrow, dv = nthreads - dr * vec_per_wrow;
-#pragma unroll
-                    for (int k = 0; k < D_ROUTE_VEC; k++) {
-                        if (tid + k * nthreads < n) *reinterpret_cast<uint4*>(wsm + size_t(r) * wstride + v * 16) = rv[k];
-                        r += dr, v += dv;
-                        if (v >= vec_per_wrow) v -= vec_per_wrow, r++;
+                    if (e_lo > 0) {  // (part 0 was stored before the wait above; the registers hold part 1)
+                        store_router_rows(e_lo);
+                        if (e_lo + pass_rows < experts) request_router_rows(e_lo + pass_rows);
                     }
-                    if (e_lo + pass_rows < experts) request_router_rows(e_lo + pass_rows);
                     __syncthreads();
                 }
                 route_logits(a.router, a.route_rows > 0 ? wsm : nullptr, wstride, xrow, a.bias, hidden, e_lo,

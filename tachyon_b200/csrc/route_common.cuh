@@ -205,6 +205,27 @@ __device__ __forceinline__ void route_topk_gates(const float* slog, int experts,
     }
     int my_id = 0;
     float my_val = 0.0f;
+    if (experts <= 32) {
+        // One expert per lane: each lane counts the experts that come before its own in the
+        // order (larger key first, lower index first among equals), all 32 comparisons
+        // independent of one another; the lane of rank j is the j-th pick. Same picks as the
+        // rounds below, without their chain of dependent steps.
+        const unsigned key = ukeys[0];
+        int rank = 0;
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const unsigned kj = __shfl_sync(0xffffffffu, key, j);
+            rank += (j < experts && (kj > key || (kj == key && j < lane))) ? 1 : 0;
+        }
+        if (lane >= experts) rank = 0x7fffffff;
+        for (int j = 0; j < topk; j++) {
+            const int win = __ffs(__ballot_sync(0xffffffffu, rank == j)) - 1;
+            if (lane == j) {
+                my_id = win;
+                my_val = slog[win];
+            }
+        }
+    } else
     for (int j = 0; j < topk; j++) {
         unsigned best_key = 0;
         int best_idx = 0x7fffffff;
