@@ -2,16 +2,24 @@
 """Granite-MoE tokens/s on B200, next to the CPU path timed on the host.
 
 A step is one pass of the hot path over one decode batch: every MoE block of
-the Granite 1b-a400m shape (24 layers: RMSNorm -> router/top-8 -> dispatch ->
-expert SwiGLU over int8 weights -> combine -> residual) for `--batch` tokens.
-Attention, embeddings and the output head are not part of this path.
+the Granite 1b-a400m shape (24 layers: RMSNorm -> router/top-8 -> expert SwiGLU
+over int8 weights -> combine -> residual) for `--batch` tokens. Attention,
+embeddings and the output head are not part of this path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
 
 Prints one JSON line (rank 0). `value` is whole-job tokens/s with inputs
-resident in HBM (CUDA-graph replay, CUDA events); `e2e` is the same metric
-through host buffers (pinned host -> device copy of the step's hidden states,
-the stack, device -> host read of the result) inside the timed region.
+resident in HBM (CUDA-graph replay, CUDA events around exactly K steps, median
+of `--repeats` such regions); `e2e` is the same metric through host buffers
+(pinned host -> device copy of the step's hidden states, the stack, device ->
+host read of the result) inside the timed region. Further keys of the same
+line cover the rest of the metric: `int8_peak` (the measured dense int8
+tensor-core rate), `prefill` (one block at 4096 tokens on the tcgen05 kernels,
+as a fraction of that rate), `decode_sweep` (other batch sizes), `skew` (the
+routing-skew shape); with N > 1 GPUs `ep_parity` (the expert-parallel block
+against one GPU, bit for bit) and `config4` (prefill-size expert-parallel
+blocks of the 3b-a800m shape).
+
 `--impl reference` times the CPU path (the oracle's restatement of Tachyon's
 AVX2 code: no Rust toolchain exists here to build the original) on the host
 cores, same config and metric.
@@ -34,22 +42,17 @@ sys.path.insert(0, ROOT)
 from tachyon_b200 import synth, workloads  # noqa: E402
 
 METRIC = "granite_moe_decode_tokens_per_s"
-
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the gate_up expert kernel,
-# from the ncu capture summarised in profiles/expert_fast_kernel_granite1b_q8_batch32.md
-# (read 35,761,408 B, written 0 B: the 0.5 MB of output stays in L2). Keyed by workload; other
-# workloads have no capture and report null.
-NCU_DRAM_BYTES_PER_LAUNCH = {("granite-1b-a400m", "q8", 32): 35761408}
 UNIT = "tokens/s"
-CLOCK_WINDOW_STEPS = 300  # untimed steps after the timed ones, for the clock sampler
 EPS = 1e-6
+DTYPE = "int8 x int8 -> i32, f32 scales"
 
 
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=250, help="steps per timed region")
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of --steps steps; the median is reported")
     ap.add_argument("--batch", type=int, default=32, help="decode tokens per step per GPU")
     ap.add_argument("--layers", type=int, default=workloads.GRANITE_1B.layers)
     ap.add_argument("--model", default="1b-a400m", choices=["1b-a400m", "3b-a800m-q8"],
@@ -57,6 +60,8 @@ def parse_args():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true",
+                    help="skip the int8 peak, prefill, batch-size, skew and config-4 sections")
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "fixed", "alltoallv"],
                     help="N > 1: NVLink stores into mapped peer windows with flag waits (no NCCL call in a block), "
                          "all-gather + reduce-scatter of fixed size (both from a CUDA graph), or the "
@@ -72,8 +77,9 @@ def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler:
@@ -135,6 +141,8 @@ def build_weights(shape, layers, seed, threads):
     return out, time.time() - t0
 
 
+# ---------------------------------------------------------------- the CPU arm
+
 def cpu_stack_step(oracle, mats, x0, topk, threads):
     """One pass of the CPU path over the stack: xb = rmsnorm(x); x += moe(xb)."""
     x = x0.copy()
@@ -145,7 +153,9 @@ def cpu_stack_step(oracle, mats, x0, topk, threads):
     return x
 
 
-def run_cpu(args, shape, weights_host, x0, steps, warmup, budget_s=25.0):
+def run_cpu(shape, weights_host, x0, steps, warmup, budget_s=25.0):
+    """Warm-up pass, then the best of the timed steps (the protocol of the reference's
+    bench-batch, src/main.rs:1135-1151), within a time budget."""
     from oracle import binding as oracle
 
     oracle.build()
@@ -162,9 +172,9 @@ def run_cpu(args, shape, weights_host, x0, steps, warmup, budget_s=25.0):
         times.append(time.perf_counter() - t0)
         if time.time() - t_begin > budget_s:
             break
-    mean = float(np.mean(times))
-    return {"tokens_per_s": x0.shape[0] / mean, "ms_per_step": mean * 1e3, "steps": len(times),
-            "threads": threads, "best_ms": float(np.min(times)) * 1e3}
+    best, mean = float(np.min(times)), float(np.mean(times))
+    return {"tokens_per_s": x0.shape[0] / best, "ms_per_step": best * 1e3, "steps": len(times),
+            "threads": threads, "mean_ms": mean * 1e3}
 
 
 def config_dict(args, shape, world):
@@ -187,6 +197,185 @@ def config_dict(args, shape, world):
     }
 
 
+def reference_arm(args, shape, world):
+    """The CPU path on the host cores, on the same global batch as the GPU arm at this N."""
+    threads = max(1, (os.cpu_count() or 8) - 2)
+    weights_host, _ = build_weights(shape, args.layers, args.seed, threads)
+    tokens = args.batch * world
+    x0 = np.concatenate([workloads.hidden_states(shape, args.batch, seed=args.seed + r) for r in range(world)])
+    r = run_cpu(shape, weights_host, x0, min(args.steps, 200), 1, budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": r["steps"], "warmup": 1, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": config_dict(args, shape, world),
+        "cpu_baseline": {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["threads"], "kind": "port",
+                         "sample": f"best of {r['steps']} full steps of the same {args.layers}-layer stack at "
+                                   f"{tokens} tokens per step (mean {r['mean_ms']:.1f} ms); C++ restatement of "
+                                   f"Tachyon's AVX2 path, not the Rust binary"},
+        "e2e": {"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------- timing helpers
+
+def timed_regions(ctx, launch, steps, repeats, barrier=None):
+    """`repeats` regions of exactly `steps` calls of launch(), each between CUDA events on the
+    context's stream with a synchronize on both sides. Returns milliseconds per region."""
+    out = []
+    for _ in range(repeats):
+        ctx.sync()
+        if barrier:
+            barrier()
+        ctx.timer_start()
+        for _ in range(steps):
+            launch()
+        out.append(ctx.timer_stop_ms())
+    return out
+
+
+def steps_for(ms_per_step, target_ms, lo=3, hi=2000):
+    return int(min(hi, max(lo, round(target_ms / max(ms_per_step, 1e-3)))))
+
+
+class Stack:
+    """The MoE blocks of a model on one context, with a residual stream of `batch` tokens."""
+
+    def __init__(self, ctx, shape, layers, batch, seed=0):
+        self.ctx, self.shape, self.layers, self.batch = ctx, shape, layers, batch
+        self.ones = ctx.to_device(np.ones(shape.hidden, np.float32))
+        self.x_host = ctx.pinned((batch, shape.hidden))
+        self.x_host[:] = workloads.hidden_states(shape, batch, seed=seed)
+        self.y_host = ctx.pinned((batch, shape.hidden))
+        self.x_in = ctx.to_device(self.x_host)
+        self.x = ctx.empty((batch, shape.hidden))
+
+    def enqueue(self):
+        self.ctx.copy(self.x, self.x_in)
+        for layer in self.layers:
+            layer.block(self.ones, EPS, self.x, t=self.batch)  # x += moe(rmsnorm(x)): src/model.rs:662-681
+
+    def capture(self):
+        self.enqueue()
+        self.ctx.sync()
+        self.ctx.capture_begin()
+        self.enqueue()
+        return self.ctx.capture_end()
+
+    def routing_spread(self):
+        """Distinct experts picked per layer (what the algorithmic bytes depend on)."""
+        distinct = []
+        self.ctx.copy(self.x, self.x_in)
+        for layer in self.layers:
+            layer.block(self.ones, EPS, self.x, t=self.batch)
+            _, _, counts, _ = layer.last_routing(self.batch)
+            distinct.append(int(np.count_nonzero(counts)))
+        return distinct
+
+    def free(self):
+        for d in (self.ones, self.x_in, self.x):
+            d.free()
+
+
+def decode_point(ctx, shape, layers, batch, target_ms, repeats, peak):
+    """ms per step and whole-step HBM fraction of the stack at one batch size."""
+    st = Stack(ctx, shape, layers, batch)
+    distinct = st.routing_spread()
+    graph = st.capture()
+    for _ in range(5):
+        graph.launch()
+    ctx.sync()
+    probe = timed_regions(ctx, graph.launch, 10, 1)[0] / 10
+    k = steps_for(probe, target_ms)
+    ms = float(np.median(timed_regions(ctx, graph.launch, k, repeats))) / k
+    nbytes = sum(workloads.decode_algorithmic_bytes(shape, batch, u) for u in distinct)
+    graph.free()
+    st.free()
+    return {"batch": batch, "ms_per_step": ms, "tokens_per_s": batch / (ms * 1e-3), "steps_per_region": k,
+            "distinct_experts_per_layer": float(np.mean(distinct)), "algorithmic_bytes_per_step": nbytes,
+            "whole_step_gbs": nbytes / (ms * 1e-3) / 1e9, "whole_step_frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+
+
+def block_point(ctx, cuda, shape, lw, tokens, bias, int8_pops, target_ms, repeats):
+    """One MoE block at `tokens` tokens (prefill-size: the tcgen05 kernels when the batch averages
+    32 tokens per expert): time per block, per-kernel shares, and the expert kernels' rate."""
+    layer = cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, tokens)
+    if bias is not None:
+        layer.set_router_bias(bias)
+    x = ctx.to_device(workloads.hidden_states(shape, tokens, seed=1))
+    y = ctx.to_device(np.zeros((tokens, shape.hidden), np.float32))
+    layer.forward(x, y)
+    ctx.sync()
+    _, _, counts, _ = layer.last_routing(tokens)
+    ctx.capture_begin()
+    layer.forward(x, y)
+    graph = ctx.capture_end()
+    for _ in range(3):
+        graph.launch()
+    ctx.sync()
+    probe = timed_regions(ctx, graph.launch, 5, 1)[0] / 5
+    k = steps_for(probe, target_ms, lo=5)
+    ms = float(np.median(timed_regions(ctx, graph.launch, k, repeats))) / k
+    # Per-kernel times from CUDA events around each launch (eager, so launches do not overlap).
+    ctx.profile_enable(True)
+    for _ in range(5):
+        layer.forward(x, y)
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    stage_us = {name: v[0] / 5 * 1e3 for name, v in prof.items() if v[1]}
+    total = sum(stage_us.values())
+    ops = 2.0 * tokens * shape.topk * 3 * shape.inter * shape.hidden  # int8 multiply-adds x 2
+    expert_us = stage_us.get("gate_up", 0.0) + stage_us.get("down", 0.0)
+    out = {"tokens": tokens, "ms_per_block": ms, "tokens_per_s": tokens / (ms * 1e-3), "steps_per_region": k,
+           "tokens_per_expert_max": int(counts.max()), "tokens_per_expert_min_nonzero": int(counts[counts > 0].min()),
+           "kernel_us_eager": stage_us, "kernel_share": {n: v / total for n, v in stage_us.items()},
+           "int8_ops_per_block": ops}
+    if expert_us > 0:
+        out["expert_kernels_pops"] = ops / (expert_us * 1e-6) / 1e15
+        out["whole_block_pops"] = ops / (ms * 1e-3) / 1e15
+        if int8_pops:
+            out["expert_kernels_frac_of_int8_peak"] = out["expert_kernels_pops"] / int8_pops
+            out["whole_block_frac_of_int8_peak"] = out["whole_block_pops"] / int8_pops
+    graph.free()
+    for d in (x, y):
+        d.free()
+    layer.free()
+    return out
+
+
+def q4_layer(shape, seed, threads):
+    """One layer's weights through the numpy mirror of the 4-bit quantizer, row ranges on a thread pool."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from tachyon_b200.q4 import quantize_q4_matrix
+    from tachyon_b200.weights import KIND_Q4, Matrix, q4_words
+
+    h, e, i = shape.hidden, shape.experts, shape.inter
+
+    def quant(stream, rows, cols):
+        words = q4_words(cols)
+        scales = np.empty(rows * words, np.uint32)
+        qs = np.empty(rows * cols // 2, np.uint8)
+        step = max(256, -(-rows // (4 * threads)))
+
+        def part(r0):
+            r1 = min(rows, r0 + step)
+            data = synth.normal(seed, stream, (r1 - r0) * cols, 0, scale=0.02, start=r0 * cols)
+            s, q = quantize_q4_matrix(data, r1 - r0, cols)
+            scales[r0 * words:r1 * words] = s
+            qs[r0 * cols // 2:r1 * cols // 2] = q
+
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(part, range(0, rows, step)))
+        return Matrix(KIND_Q4, rows, cols, scales, qs)
+
+    router = workloads._normal_matrix(seed, synth.STREAM_ROUTER, 0, e, h, "bf16")
+    return workloads.LayerWeights(router, quant(synth.STREAM_GATE_UP, e * 2 * i, h), quant(synth.STREAM_DOWN, e * h, i))
+
+
+# ---------------------------------------------------------------- the GPU arm
+
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -196,22 +385,8 @@ def main():
     host_threads = max(1, (os.cpu_count() or 8) // max(1, world) - 1)
 
     if args.impl == "reference":
-        if rank != 0:
-            return
-        weights_host, _ = build_weights(shape, args.layers, args.seed, max(1, (os.cpu_count() or 8) - 2))
-        x0 = workloads.hidden_states(shape, args.batch, seed=args.seed)
-        r = run_cpu(args, shape, weights_host, x0, args.steps, args.warmup, budget_s=150.0)
-        line = {
-            "impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
-            "steps": r["steps"], "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int8 -> i32, f32 scales", "data": "synthetic",
-            "config": config_dict(args, shape, 1),
-            "cpu_baseline": {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["threads"], "kind": "port",
-                             "sample": f"{r['steps']} full steps of the same {args.layers}-layer stack at batch "
-                                       f"{args.batch}; C++ restatement of Tachyon's AVX2 path, not the Rust binary"},
-            "e2e": {"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }
-        print(json.dumps(line))
+        if rank == 0:
+            reference_arm(args, shape, world)
         return
 
     from tachyon_b200 import build as cuda_build
@@ -230,10 +405,13 @@ def main():
         ctx.set_launch_overlap(False)
     if args.four_kernels:
         ctx.set_decode_block(False)
+    peak_hbm, peak_bf16, peak_kind = measured_peaks()
+    sweep_batches = [1, 8, 64, 128] if world == 1 and not args.headline_only else []
+    max_batch = max([args.batch] + sweep_batches)
 
     if world == 1:
         weights_host, gen_s = build_weights(shape, args.layers, args.seed, host_threads)
-        layers = [cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, args.batch) for lw in weights_host]
+        layers = [cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, max_batch) for lw in weights_host]
     else:
         from tachyon_b200 import ep
 
@@ -250,176 +428,263 @@ def main():
             layers.append(ep.EpMoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.experts, shape.topk, args.batch))
         gen_s = time.time() - t0
         weights_host = None
-    ones = ctx.to_device(np.ones(shape.hidden, np.float32))
-    x_host = ctx.pinned((args.batch, shape.hidden))
-    x_host[:] = workloads.hidden_states(shape, args.batch, seed=args.seed + rank)
-    y_host = ctx.pinned((args.batch, shape.hidden))
-    x_in = ctx.to_device(x_host)
-    x = ctx.empty((args.batch, shape.hidden))
 
-    def enqueue_stack():
-        ctx.copy(x, x_in)
-        for layer in layers:
-            layer.block(ones, EPS, x)  # x += moe(rmsnorm(x)): src/model.rs:662-681
+    def barrier():
+        if dist:
+            dist.barrier()
 
-    if dist:
-        dist.barrier()  # ranks enter their first block together: the peer exchange's waits are bounded
-    # ---- eager pass with per-kernel events: which kernel dominates, and its bandwidth
-    enqueue_stack()
+    def max_over_ranks(v):
+        if not dist:
+            return v
+        import torch
+
+        tmax = torch.tensor([v], dtype=torch.float64)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        return float(tmax.item())
+
+    stack = Stack(ctx, shape, layers, args.batch, seed=args.seed + rank)
+    barrier()  # ranks enter their first block together: the peer exchange's waits are bounded
+    stack.enqueue()
     ctx.sync()
-    distinct, prof = [], {}
-    if world == 1:
-        ctx.profile_enable(True)
-        for s in range(3):
-            ctx.copy(x, x_in)
-            for layer in layers:
-                layer.block(ones, EPS, x)
-                if s == 0:
-                    _, _, counts, _ = layer.last_routing(args.batch)
-                    distinct.append(int(np.count_nonzero(counts)))
-        prof = ctx.profile_read()
-        ctx.profile_enable(False)
+    distinct = stack.routing_spread() if world == 1 else []
 
     # ---- the timed stack, device-resident inputs: one CUDA graph per step. (The variable-size
     # expert-parallel exchange reads its sizes on the host, so that one is enqueued directly.)
     class Eager:
         def launch(self):
-            enqueue_stack()
+            stack.enqueue()
 
-    if world == 1 or args.ep_exchange != "alltoallv":
-        ctx.capture_begin()
-        enqueue_stack()
-        graph = ctx.capture_end()
-    else:
-        graph = Eager()
-    for _ in range(max(args.warmup, 3)):
+        def free(self):
+            pass
+
+    graph = stack.capture() if (world == 1 or args.ep_exchange != "alltoallv") else Eager()
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         graph.launch()
     ctx.sync()
-    if dist:
-        dist.barrier()
+    barrier()
     launches0 = ctx.launch_count()
     with ClockSampler(local_rank) as clocks:
-        ctx.timer_start()
-        for _ in range(args.steps):
-            graph.launch()
-        ms = ctx.timer_stop_ms()
-        launches = ctx.launch_count() - launches0
-        # The timed region lasts tens of milliseconds and nvidia-smi samples every 100 ms: keep the
-        # same load running (untimed; the same count on every rank) until a few samples are in.
-        for _ in range(CLOCK_WINDOW_STEPS if args.batch * args.layers <= 256 * 24 else 20):
+        regions = timed_regions(ctx, graph.launch, args.steps, args.repeats, barrier=barrier)
+        launches = (ctx.launch_count() - launches0) // args.repeats
+        # nvidia-smi samples every 100 ms: keep the same load running a little longer if the
+        # regions were short (untimed; the same count on every rank).
+        extra = steps_for(float(np.median(regions)) / args.steps, 600.0) if sum(regions) < 600.0 else 0
+        extra = int(max_over_ranks(float(extra)))
+        for _ in range(extra):
             graph.launch()
         ctx.sync()
-    ctx.sync()
-    if dist:
-        import torch
-
-        tmax = torch.tensor([ms], dtype=torch.float64)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        ms = float(tmax.item())
-        dist.barrier()
-    ms_per_step = ms / args.steps
+    regions = [max_over_ranks(r) for r in regions]
+    ms_per_step = float(np.median(regions)) / args.steps
     value = args.batch * world / (ms_per_step * 1e-3)
 
     # ---- end to end through host buffers
-    for _ in range(2):
-        ctx.upload(x_in.ptr, x_host)
+    def e2e_step():
+        ctx.upload(stack.x_in.ptr, stack.x_host)
         graph.launch()
-        ctx.download(y_host, x.ptr)
-    if dist:
-        dist.barrier()
-    ctx.timer_start()
-    for _ in range(args.steps):
-        ctx.upload(x_in.ptr, x_host)
-        graph.launch()
-        ctx.download(y_host, x.ptr)
-    e2e_ms = ctx.timer_stop_ms()
-    if dist:
-        import torch
+        ctx.download(stack.y_host, stack.x.ptr)
 
-        tmax = torch.tensor([e2e_ms], dtype=torch.float64)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        e2e_ms = float(tmax.item())
-    e2e_value = args.batch * world / (e2e_ms / args.steps * 1e-3)
-    assert np.all(np.isfinite(y_host))
-
-    if rank != 0:
-        return
-    if world > 1:
-        peak, peak_kind = measured_peaks()
-        # Bytes every rank's HBM must deliver per step: its share of the selected experts' weights
-        # (all experts are hit at these batch sizes), routers, activations.
-        step_bytes = args.layers * workloads.decode_algorithmic_bytes(shape, args.batch * world, shape.experts)
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "int8 x int8 -> i32, f32 scales", "data": "synthetic",
-            "config": config_dict(args, shape, world),
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
-                    "d2h_bytes_per_step": int(y_host.nbytes), "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": int(launches),
-            "clocks": clocks.summary(),
-            "roofline": {"bound": "hbm", "kernel": "whole step, all ranks", "achieved": step_bytes / (ms_per_step * 1e-3) / 1e9,
-                         "peak": peak * world, "unit": "GB/s", "frac": step_bytes / (ms_per_step * 1e-3) / 1e9 / (peak * world),
-                         "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs x {world} GPUs)", "traffic": None},
-            "setup_s": {"weights_host": gen_s},
-        }
-        print(json.dumps(line))
-        return
-
-    # ---- roofline of the dominant kernel (gate_up expert products)
-    peak, peak_kind = measured_peaks()
-    eb_gu = 2 * shape.inter * shape.hidden * 34 // 32            # one expert's gate_up rows as stored
-    eb_dn = shape.hidden * shape.inter * 34 // 32
-    nbp = -(-(shape.hidden // 32) // 8) * 8
-    mean_u = float(np.mean(distinct))
-    gu_bytes = (mean_u * eb_gu + args.batch * (shape.hidden + 4 * nbp)
-                + args.batch * shape.topk * shape.inter * 4)
-    stage_ms = {k: v[0] / max(1, v[1]) for k, v in prof.items() if v[1]}
-    if "decode_block" in stage_ms:
-        one_kernel_block = True
-        gu_bytes = float(np.mean([workloads.decode_algorithmic_bytes(shape, args.batch, u) for u in distinct]))
-        stage_ms["gate_up"] = stage_ms["decode_block"]
-        stage_ms["down"] = stage_ms["decode_block"]
-    gu_ms = stage_ms["gate_up"]
-    achieved = gu_bytes / (gu_ms * 1e-3) / 1e9
-    total_prof = sum(v[0] for v in prof.values())
-    roofline = {
-        "bound": "hbm", "kernel": "expert_kernel<q8, gate_up>", "achieved": achieved, "peak": peak,
-        "unit": "GB/s", "frac": achieved / peak, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
-        "frac_of_8TBs_nominal": achieved / 8000.0,
-        "algorithmic_bytes_per_launch": gu_bytes, "avg_launch_us": gu_ms * 1e3,
-        "distinct_experts_per_layer": mean_u,
-        "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get((shape.name, shape.fmt, args.batch)),
-        "kernel_share_of_step": {k: v[0] / total_prof for k, v in prof.items() if v[1]},
-        "down_kernel": {"achieved": (mean_u * eb_dn + args.batch * shape.topk * (shape.inter + 4 * 8)
-                                     + args.batch * shape.topk * shape.hidden * 4) / (stage_ms["down"] * 1e-3) / 1e9,
-                        "avg_launch_us": stage_ms["down"] * 1e3},
-        "whole_step": {"algorithmic_bytes": sum(workloads.decode_algorithmic_bytes(shape, args.batch, u) for u in distinct),
-                       "achieved": sum(workloads.decode_algorithmic_bytes(shape, args.batch, u) for u in distinct)
-                                   / (ms_per_step * 1e-3) / 1e9},
-    }
-    roofline["whole_step"]["frac"] = roofline["whole_step"]["achieved"] / peak
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = min(args.steps, 200)
+    e2e_regions = [max_over_ranks(r) for r in timed_regions(ctx, e2e_step, e2e_steps, max(3, args.repeats // 2 + 1),
+                                                             barrier=barrier)]
+    e2e_ms = float(np.median(e2e_regions)) / e2e_steps
+    e2e_value = args.batch * world / (e2e_ms * 1e-3)
+    assert np.all(np.isfinite(stack.y_host))
+    e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(stack.x_host.nbytes),
+           "d2h_bytes_per_step": int(stack.y_host.nbytes), "ms_per_step": e2e_ms, "steps_per_region": e2e_steps}
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x int8 -> i32, f32 scales", "data": "synthetic",
-        "config": config_dict(args, shape, world),
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
-                "d2h_bytes_per_step": int(y_host.nbytes), "ms_per_step": e2e_ms / args.steps},
-        "gpu_launches": int(launches),
-        "clocks": clocks.summary(),
-        "roofline": roofline,
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic", "config": config_dict(args, shape, world), "e2e": e2e,
+        "gpu_launches": int(launches), "repeats": args.repeats, "region_ms": regions,
         "setup_s": {"weights_host": gen_s},
     }
-    if world == 1 and not args.no_cpu_baseline:
-        r = run_cpu(args, shape, weights_host, np.array(x_host), steps=30, warmup=1, budget_s=20.0)
+
+    if world > 1:
+        line.update(multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world, host_threads,
+                                       peak_hbm, peak_kind, ms_per_step))
+        if rank == 0:
+            line["clocks"] = clocks.summary()
+            print(json.dumps(line))
+        return
+
+    # ---- roofline of the dominant kernel. At decode sizes the whole block is one kernel
+    # (moe_decode_kernel), so the step is `layers` launches of it plus one small copy: its average
+    # launch duration is the timed region divided by the launches in it. Per-launch CUDA events
+    # (eager, no overlap between launches) and the kernel's own phase stamps go beside it.
+    ctx.profile_enable(True)
+    for _ in range(3):
+        stack.enqueue()
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    stage_us = {k: v[0] / max(1, v[1]) * 1e3 for k, v in prof.items() if v[1]}
+    total_prof = sum(v[0] for v in prof.values())
+    step_bytes = [workloads.decode_algorithmic_bytes(shape, args.batch, u) for u in distinct]
+    mean_u = float(np.mean(distinct))
+    one_kernel = "decode_block" in stage_us
+    if one_kernel:
+        bytes_per_launch = float(np.mean(step_bytes))
+        launch_us = ms_per_step * 1e3 / args.layers
+        kernel = f"moe_decode_kernel<{shape.fmt}> (router + gate_up + down + combine of one block)"
+        ctx.profile_phases(True)
+        g2 = stack.capture()
+        for _ in range(3):
+            g2.launch()
+        phases = ctx.read_phases()
+        ctx.profile_phases(False)
+        g2.free()
+    else:
+        eb_gu = 2 * shape.inter * shape.hidden * 34 // 32  # one expert's gate_up rows as stored
+        nbp = -(-(shape.hidden // 32) // 8) * 8
+        bytes_per_launch = (mean_u * eb_gu + args.batch * (shape.hidden + 4 * nbp)
+                            + args.batch * shape.topk * shape.inter * 4)
+        launch_us = stage_us["gate_up"]
+        kernel = f"expert_fast_kernel<{shape.fmt}, gate_up>"
+        phases = None
+    achieved = bytes_per_launch / (launch_us * 1e-6) / 1e9
+    whole = sum(step_bytes) / (ms_per_step * 1e-3) / 1e9
+    line["roofline"] = {
+        "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak_hbm, "unit": "GB/s",
+        "frac": achieved / peak_hbm, "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs)",
+        "frac_of_8TBs_nominal": achieved / 8000.0, "algorithmic_bytes_per_launch": bytes_per_launch,
+        "avg_launch_us": launch_us, "avg_launch_source": "timed region / launches in it" if one_kernel
+        else "CUDA events around each eager launch",
+        "eager_event_us": stage_us, "distinct_experts_per_layer": mean_u, "traffic": None,
+        "kernel_share_of_step": {k: v[0] / total_prof for k, v in prof.items() if v[1]},
+        "phase_us_cta0": phases,
+        "whole_step": {"algorithmic_bytes": sum(step_bytes), "achieved": whole, "frac": whole / peak_hbm},
+    }
+    line["clocks"] = clocks.summary()
+    graph.free()
+
+    if not args.headline_only:
+        t0 = time.time()
+        peak = ctx.int8_peak(50.0)
+        peak["vs_2x_measured_bf16"] = peak["pops"] / (2.0 * peak_bf16 / 1e3)
+        line["int8_peak"] = peak
+        line["decode_sweep"] = [decode_point(ctx, shape, layers, b, 100.0, 3, peak_hbm) for b in sweep_batches]
+        # One block at 4096 tokens (4 sequences x 1024): the 1b shape in int8, the 3b shape in 4 bits.
+        pre = {"1b-a400m-q8": block_point(ctx, cuda, shape, weights_host[0], 4096, None, peak["pops"], 60.0, 3)}
+        s3 = workloads.GRANITE_3B
+        pre["3b-a800m-q4"] = block_point(ctx, cuda, s3, q4_layer(s3, args.seed, host_threads), 4096, None,
+                                         peak["pops"], 60.0, 3)
+        line["prefill"] = pre
+        # The routing-skew shape: hidden 2048, 64 experts, intermediate 1024, Zipf(1.2) router bias.
+        sk = workloads.SKEW
+        lw = workloads.layer_weights(sk, seed=args.seed, threads=host_threads)
+        bias = synth.zipf_router_bias(args.seed, sk.experts)
+        line["skew"] = {"shape": "hidden 2048, 64 experts, top-8, intermediate 1024, int8, Zipf(1.2) router bias",
+                        "points": [block_point(ctx, cuda, sk, lw, t, bias, peak["pops"], 40.0, 3)
+                                   for t in (256, 4096)]}
+        line["setup_s"]["sections"] = time.time() - t0
+
+    if not args.no_cpu_baseline:
+        r = run_cpu(shape, weights_host, np.array(stack.x_host), steps=30, warmup=1, budget_s=20.0)
         line["cpu_baseline"] = {
             "value": r["tokens_per_s"], "unit": UNIT, "cores": r["threads"], "kind": "port",
-            "sample": f"{r['steps']} full steps of the same {args.layers}-layer stack at batch {args.batch} "
-                      f"(mean {r['ms_per_step']:.1f} ms/step); C++ restatement of Tachyon's AVX2 path",
+            "sample": f"best of {r['steps']} full steps of the same {args.layers}-layer stack at batch {args.batch} "
+                      f"(best {r['ms_per_step']:.1f} ms, mean {r['mean_ms']:.1f} ms per step); C++ restatement of "
+                      f"Tachyon's AVX2 path",
         }
     print(json.dumps(line))
+
+
+def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world, host_threads, peak_hbm, peak_kind,
+                       ms_per_step):
+    """Whole-job roofline, the expert-parallel block against one GPU, and prefill-size blocks."""
+    import torch
+
+    from tachyon_b200 import ep
+
+    out = {}
+    step_bytes = args.layers * workloads.decode_algorithmic_bytes(shape, args.batch * world, shape.experts)
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    out["roofline"] = {"bound": "hbm", "kernel": "whole step, all ranks", "achieved": achieved,
+                       "peak": peak_hbm * world, "unit": "GB/s", "frac": achieved / (peak_hbm * world),
+                       "peak_source": f"{peak_kind} (MEASURED_PEAKS.json hbm_gbs x {world} GPUs)", "traffic": None}
+
+    # ---- correctness where the driver can see it: layer 0 through the expert-parallel block on
+    # every rank's own tokens, against the same tokens through a single-GPU layer on rank 0.
+    x_local = np.array(stack.x_host)
+    y0_local = workloads.hidden_states(shape, args.batch, seed=1000 + rank)
+    xd, yd = ctx.to_device(x_local), ctx.to_device(y0_local)
+    dist.barrier()
+    layers[0].forward(xd, yd)
+    ctx.sync()
+    got = torch.from_numpy(yd.get())
+    gathered = [torch.empty_like(got) for _ in range(world)]
+    dist.all_gather(gathered, got)
+    if rank == 0:
+        lw = workloads.layer_weights(shape, seed=args.seed, layer=0, threads=host_threads)
+        full = cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, shape.topk, args.batch * world)
+        x_all = np.concatenate([workloads.hidden_states(shape, args.batch, seed=args.seed + r) for r in range(world)])
+        y_all = np.concatenate([workloads.hidden_states(shape, args.batch, seed=1000 + r) for r in range(world)])
+        xa, ya = ctx.to_device(x_all), ctx.to_device(y_all)
+        full.forward(xa, ya)
+        ctx.sync()
+        want = ya.get()
+        have = np.concatenate([g.numpy() for g in gathered])
+        out["ep_parity"] = "bit-equal" if np.array_equal(have, want) else \
+            {"max_abs": float(np.abs(have - want).max())}
+        for d in (xa, ya):
+            d.free()
+        full.free()
+    for d in (xd, yd):
+        d.free()
+    dist.barrier()
+
+    if args.headline_only:
+        return out
+    # ---- prefill-size expert-parallel blocks: the 3b-a800m shape with int8 weights, 8192 tokens per
+    # step over all ranks, 2 layers, variable-size all-to-all dispatch and combine.
+    s4 = workloads.GRANITE_3B_Q8
+    tokens = 8192 // world
+    first, count = ep.shard_range(s4.experts, rank, world)
+    l4 = []
+    for l in range(2):
+        lw = workloads.layer_weights_local(s4, first, count, seed=args.seed, layer=l, threads=host_threads)
+        l4.append(ep.EpMoeLayer(ctx, lw.router, lw.gate_up, lw.down, s4.experts, s4.topk, tokens))
+    st4 = Stack(ctx, s4, l4, tokens, seed=args.seed + rank)
+    dist.barrier()
+    for _ in range(3):
+        st4.enqueue()
+    ctx.sync()
+    k = 10
+    regs = []
+    for r in timed_regions(ctx, st4.enqueue, k, 3, barrier=dist.barrier):
+        tmax = torch.tensor([r], dtype=torch.float64)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        regs.append(float(tmax.item()))
+    ms4 = float(np.median(regs)) / k
+    c4 = {"workload": "granite-3b-a800m shape, int8 weights, 40 experts sharded, 8192 tokens per step over all ranks, "
+                      "2 MoE blocks, NCCL all-to-all-v dispatch and combine",
+          "tokens_per_rank": tokens, "ms_per_step": ms4, "ms_per_block": ms4 / 2,
+          "tokens_per_s": 8192 / (ms4 * 1e-3), "steps_per_region": k}
+    st4.free()
+    for layer in l4:
+        layer.free()
+    dist.barrier()
+    if rank == 0:
+        # The same two blocks on one GPU, for the ratio.
+        lws = [workloads.layer_weights(s4, seed=args.seed, layer=l, threads=host_threads) for l in range(2)]
+        full = [cuda.MoeLayer(ctx, lw.router, lw.gate_up, lw.down, s4.topk, 8192) for lw in lws]
+        st1 = Stack(ctx, s4, full, 8192, seed=args.seed)
+        for _ in range(3):
+            st1.enqueue()
+        ctx.sync()
+        ms1 = float(np.median(timed_regions(ctx, st1.enqueue, k, 3))) / k
+        c4["one_gpu_ms_per_step"] = ms1
+        c4["speedup_vs_one_gpu"] = ms1 / ms4
+        st1.free()
+        for layer in full:
+            layer.free()
+    dist.barrier()
+    out["config4"] = c4
+    return out
 
 
 if __name__ == "__main__":

@@ -200,6 +200,14 @@ tc_moe_layer *tc_moe_ep_layer_create(tc_ctx *ctx, int hidden, int experts, int e
 int tc_umma_selftest(tc_ctx *ctx, const int8_t *a_rows_host, const int8_t *b_rows_host, int n,
                      int32_t *d_out_host);
 
+/* The dense int8 rate of the tensor cores, measured (no counterpart in the reference):
+ * every SM issues `batches` batches of 32 tcgen05 MMAs (128 x 256 x 32, int8 -> int32,
+ * accumulating in tensor memory) from operands resident in shared memory. Returns the
+ * integer operations performed (multiply and add counted separately) and the kernel's
+ * duration in milliseconds (CUDA events): the denominator of the prefill-size kernels'
+ * tensor-pipe fraction. Allocates and frees one status word. */
+int tc_int8_peak(tc_ctx *ctx, int batches, double *ops_out, float *ms_out);
+
 /* ---- the pre-MoE norm: kernels::rmsnorm (src/kernels.rs:522-528) per row,
  * as src/model.rs:662-667 applies it. out may alias x. */
 int tc_rmsnorm(tc_ctx *ctx, const float *x_dev, const float *weight_dev, float eps, int t, int n,

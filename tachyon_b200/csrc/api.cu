@@ -910,6 +910,29 @@ int tc_umma_selftest(tc_ctx* ctx, const int8_t* a_rows, const int8_t* b_rows, in
     return 0;
 }
 
+int tc_int8_peak(tc_ctx* ctx, int batches, double* ops_out, float* ms_out) {
+    if (batches < 1) return fail(ctx, "tc_int8_peak: at least one batch");
+    cudaSetDevice(ctx->device);
+    int* status = nullptr;
+    if (!cuda_ok(ctx, cudaMalloc(reinterpret_cast<void**>(&status), sizeof(int)), "cudaMalloc")) return -1;
+    cudaMemsetAsync(status, 0, sizeof(int), ctx->stream);
+    cudaEventRecord(ctx->ev_start, ctx->stream);
+    const double ops = tc::launch_int8_peak(ctx->sms, batches, status, ctx->stream);
+    ctx->launches += 1;
+    cudaEventRecord(ctx->ev_stop, ctx->stream);
+    int st = 0;
+    float ms = 0.0f;
+    const bool ok = cuda_ok(ctx, cudaEventSynchronize(ctx->ev_stop), "int8 peak kernel") &&
+                    cuda_ok(ctx, cudaEventElapsedTime(&ms, ctx->ev_start, ctx->ev_stop), "cudaEventElapsedTime") &&
+                    cuda_ok(ctx, cudaMemcpy(&st, status, sizeof st, cudaMemcpyDeviceToHost), "status readback");
+    cudaFree(status);
+    if (!ok) return -1;
+    if (st) return fail(ctx, "tc_int8_peak: an MMA batch did not complete within the wait limit");
+    if (ops_out) *ops_out = ops;
+    if (ms_out) *ms_out = ms;
+    return 0;
+}
+
 int tc_rmsnorm(tc_ctx* ctx, const float* x, const float* w, float eps, int t, int n, float* out) {
     if (t <= 0 || n <= 0) return fail(ctx, "rmsnorm over nothing");
     ctx->launches += staged(ctx, 6, [&] { return tc::launch_rmsnorm(x, w, eps, t, n, out, ctx->stream); });

@@ -289,6 +289,10 @@ int launch_umma_selftest(const int8_t* a_tile, const int8_t* b_tile, int n, int*
 
 int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_t stream);
 
+// The dense int8 tensor-core rate: `batches` batches of MMAs on each of `sms` SMs; returns the
+// integer operations performed (int8_peak.cu).
+double launch_int8_peak(int sms, int batches, int* status, cudaStream_t stream);
+
 // ---- the whole block of a decode-size batch as one kernel (moe_decode.cu)
 void init_kernels_decode();
 // True if a block of t tokens of this shape can take the one-kernel path.

@@ -63,6 +63,7 @@ SYMBOLS = {
     "tc_ep_barrier": (_i, [_vp]),
     "tc_moe_ep_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "tc_umma_selftest": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "tc_int8_peak": (_i, [_vp, _i, C.POINTER(C.c_double), C.POINTER(C.c_float)]),
     "tc_dispatch_static": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "tc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp]),
     "tc_capture_begin": (_i, [_vp]),
@@ -248,6 +249,17 @@ class Context:
         self._check(self.lib.tc_dispatch_static(self.handle, ids.ptr, t, experts, topk, counts.ptr, offsets.ptr,
                                                 perm.ptr, pos.ptr, slot_token.ptr, active.ptr),
                     "tc_dispatch_static")
+
+    def int8_peak(self, min_ms: float = 50.0) -> dict:
+        """Dense int8 tensor-core rate in Pop/s, from a run of at least min_ms milliseconds."""
+        batches, ops, ms = 64, C.c_double(0.0), C.c_float(0.0)
+        while True:
+            self._check(self.lib.tc_int8_peak(self.handle, batches, C.byref(ops), C.byref(ms)), "tc_int8_peak")
+            if ms.value >= min_ms or batches >= (1 << 24):
+                break
+            batches = int(batches * max(2.0, 1.2 * min_ms / max(ms.value, 1e-3)))
+        return {"pops": ops.value / (ms.value * 1e-3) / 1e15, "ms": ms.value, "mma_per_sm": batches * 32,
+                "shape": "tcgen05.mma kind::i8 m128 n256 k32, cta_group::1, operands resident in shared memory"}
 
     def umma_selftest(self, a_rows: np.ndarray, b_rows: np.ndarray) -> np.ndarray:
         """a_rows i8[128, 32] x b_rows i8[n, 32]^T through one tcgen05 MMA; returns i32[128, n]."""
