@@ -215,7 +215,12 @@ def reference_arm(args, shape, world):
                                    f"Tachyon's AVX2 path, not the Rust binary"},
         "e2e": {"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    emit(line)
+
+
+def emit(line):
+    sys.stdout.write(json.dumps(line) + "\n")
+    sys.stdout.flush()
 
 
 # ---------------------------------------------------------------- timing helpers
@@ -396,6 +401,8 @@ def main():
         cuda_build.build()
     dist = None
     if world > 1:
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # (its banner would land on stdout beside the JSON line)
         import torch.distributed as dist  # plumbing only: barrier and max over ranks
 
         dist.init_process_group("gloo")
@@ -509,7 +516,8 @@ def main():
                                        peak_hbm, peak_kind, ms_per_step))
         if rank == 0:
             line["clocks"] = clocks.summary()
-            print(json.dumps(line))
+            emit(line)
+        dist.barrier()
         return
 
     # ---- roofline of the dominant kernel. At decode sizes the whole block is one kernel
@@ -590,7 +598,7 @@ def main():
                       f"(best {r['ms_per_step']:.1f} ms, mean {r['mean_ms']:.1f} ms per step); C++ restatement of "
                       f"Tachyon's AVX2 path",
         }
-    print(json.dumps(line))
+    emit(line)
 
 
 def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world, host_threads, peak_hbm, peak_kind,
