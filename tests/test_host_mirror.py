@@ -112,3 +112,28 @@ def test_no_device_fails_loudly():
     assert err.value
     with pytest.raises(cuda.TachyonCudaError):
         cuda.Context(0)
+
+
+def test_rust_glue_binds_only_declared_entry_points():
+    """The `extern "C"` block of the Rust glue (tachyon_b200/rust/src/gpu/cuda/mod.rs) names
+    entry points that the header declares and the ctypes mirror binds, and its build script
+    lists every .cu source of the library."""
+    import glob
+    import re
+
+    from tachyon_b200 import cuda
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    rust = open(os.path.join(root, "tachyon_b200", "rust", "src", "gpu", "cuda", "mod.rs")).read()
+    block = rust[rust.index('extern "C" {'):]
+    block = block[:block.index("\n}\n")]
+    bound = set(re.findall(r"fn (tc_\w+)\(", block))
+    assert len(bound) > 20
+    header = open(os.path.join(root, "include", "tachyon_cuda.h")).read()
+    for name in bound:
+        assert re.search(r"\b" + name + r"\(", header), name
+        assert name in cuda.SYMBOLS, name
+    build_rs = open(os.path.join(root, "tachyon_b200", "rust", "build_cuda.rs")).read()
+    listed = set(re.findall(r'^    "(\w+)",$', build_rs, flags=re.M))
+    have = {os.path.basename(p)[:-3] for p in glob.glob(os.path.join(root, "tachyon_b200", "csrc", "*.cu"))}
+    assert listed == have, (listed ^ have)
