@@ -89,6 +89,15 @@ void tc_host_free(tc_ctx *ctx, void *host);
  * cols must be a multiple of 32 (as src/gpu/mod.rs:241-243 requires). */
 tc_matrix *tc_matrix_upload(tc_ctx *ctx, int kind, size_t rows, size_t cols, const void *scales,
                             size_t scales_bytes, const void *data, size_t data_bytes);
+/* The same from f32 values: Matrix::from_f32 (src/weights.rs:82-105) on the device.
+ * Uploads data_host (f32[rows*cols]) and quantizes it there with Tachyon's own
+ * quantizers (f32_to_bf16 src/kernels.rs:21-28; quantize_q8_weights 135-149;
+ * quantize_q4_packed 180-242 with fit_q4_offset 438-495, no importance matrix):
+ * the bytes are those the host loader would have produced. */
+tc_matrix *tc_matrix_quantize(tc_ctx *ctx, int kind, size_t rows, size_t cols, const float *data_host);
+/* Copies a matrix's buffers back to the host (sizes as for tc_matrix_upload). */
+int tc_matrix_download(const tc_matrix *m, void *scales_host, size_t scales_bytes, void *data_host,
+                       size_t data_bytes);
 void tc_matrix_free(tc_matrix *m);
 
 /* ---- the MoE block: replaces GpuBackend::moe (src/gpu/mod.rs:651-702) with

@@ -489,6 +489,66 @@ tc_matrix* tc_matrix_upload(tc_ctx* ctx, int kind, size_t rows, size_t cols, con
     return m;
 }
 
+namespace {
+bool matrix_sizes(int kind, size_t rows, size_t cols, size_t* scales_bytes, size_t* data_bytes) {
+    switch (kind) {
+        case TC_BF16: *scales_bytes = 0, *data_bytes = rows * cols * 2; return true;
+        case TC_Q8: *scales_bytes = rows * (cols / 32) * 2, *data_bytes = rows * cols; return true;
+        case TC_Q4: *scales_bytes = rows * ((cols / 32 + 7) / 8 * 5) * 4, *data_bytes = rows * cols / 2; return true;
+        default: return false;
+    }
+}
+}  // namespace
+
+tc_matrix* tc_matrix_quantize(tc_ctx* ctx, int kind, size_t rows, size_t cols, const float* data_host) {
+    size_t want_scales = 0, want_data = 0;
+    if (!matrix_sizes(kind, rows, cols, &want_scales, &want_data)) {
+        fail(ctx, "unknown matrix kind %d", kind);
+        return nullptr;
+    }
+    if (cols % 32 != 0 || rows == 0 || cols == 0) {
+        fail(ctx, "GPU matrices need a positive multiple of 32 columns, not %zu x %zu", rows, cols);
+        return nullptr;
+    }
+    cudaSetDevice(ctx->device);
+    tc_matrix* m = new tc_matrix{ctx, {kind, rows, cols, nullptr, nullptr}, nullptr, nullptr};
+    float *src = nullptr, *scratch = nullptr;
+    const size_t n = rows * cols;
+    bool ok = cuda_ok(ctx, cudaMalloc(reinterpret_cast<void**>(&src), n * 4), "cudaMalloc(f32 weights)") &&
+              cuda_ok(ctx, cudaMemcpyAsync(src, data_host, n * 4, cudaMemcpyHostToDevice, ctx->stream), "f32 upload") &&
+              cuda_ok(ctx, cudaMalloc(&m->data_alloc, want_data + 256), "cudaMalloc(weights)");
+    if (ok && want_scales) ok = cuda_ok(ctx, cudaMalloc(&m->scales_alloc, want_scales + 256), "cudaMalloc(scales)");
+    if (ok && kind == TC_Q4)
+        ok = cuda_ok(ctx, cudaMalloc(reinterpret_cast<void**>(&scratch), (rows + 2 * (n / 32)) * 4), "cudaMalloc(fit)");
+    if (ok) {
+        ctx->launches += tc::launch_quantize(kind, src, rows, cols, m->scales_alloc, m->data_alloc, scratch, ctx->stream);
+        ok = cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "quantization");
+    }
+    if (src) cudaFree(src);
+    if (scratch) cudaFree(scratch);
+    if (!ok) {
+        tc_matrix_free(m);
+        return nullptr;
+    }
+    m->dev.scales = m->scales_alloc;
+    m->dev.data = m->data_alloc;
+    return m;
+}
+
+int tc_matrix_download(const tc_matrix* m, void* scales_host, size_t scales_bytes, void* data_host, size_t data_bytes) {
+    tc_ctx* ctx = m->ctx;
+    size_t want_scales = 0, want_data = 0;
+    matrix_sizes(m->dev.kind, m->dev.rows, m->dev.cols, &want_scales, &want_data);
+    if (scales_bytes != want_scales || data_bytes != want_data)
+        return fail(ctx, "tc_matrix_download: buffers of %zu+%zu bytes, the matrix holds %zu+%zu", scales_bytes,
+                    data_bytes, want_scales, want_data);
+    cudaSetDevice(ctx->device);
+    if (want_scales && !cuda_ok(ctx, cudaMemcpy(scales_host, m->dev.scales, want_scales, cudaMemcpyDeviceToHost),
+                                "scales download"))
+        return -1;
+    return cuda_ok(ctx, cudaMemcpy(data_host, m->dev.data, want_data, cudaMemcpyDeviceToHost), "weights download") ? 0 : -1;
+}
+
 void tc_matrix_free(tc_matrix* m) {
     if (!m) return;
     cudaSetDevice(m->ctx->device);

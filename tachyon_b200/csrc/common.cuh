@@ -293,6 +293,11 @@ int launch_combine(const MoeDims& d, int t, Workspace& ws, float* y, cudaStream_
 // integer operations performed (int8_peak.cu).
 double launch_int8_peak(int sms, int batches, int* status, cudaStream_t stream);
 
+// Tachyon's weight quantizers on the device (quantize.cu): x[rows, cols] f32 into the buffers of a
+// Matrix of `kind`; `scratch` holds rows * (1 + 2 * cols / 32) floats for the 4-bit fit.
+int launch_quantize(int kind, const float* x, size_t rows, size_t cols, void* scales, void* data, float* scratch,
+                    cudaStream_t stream);
+
 // ---- the whole block of a decode-size batch as one kernel (moe_decode.cu)
 void init_kernels_decode();
 // True if a block of t tokens of this shape can take the one-kernel path.

@@ -44,6 +44,8 @@ SYMBOLS = {
     "tc_profile_enable": (_i, [_vp, _i]),
     "tc_profile_read": (_i, [_vp, _vp, _vp]),
     "tc_matrix_upload": (_vp, [_vp, _i, _sz, _sz, _vp, _sz, _vp, _sz]),
+    "tc_matrix_quantize": (_vp, [_vp, _i, _sz, _sz, _vp]),
+    "tc_matrix_download": (_i, [_vp, _vp, _sz, _vp, _sz]),
     "tc_matrix_free": (None, [_vp]),
     "tc_moe_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "tc_moe_layer_free": (None, [_vp]),
@@ -359,6 +361,42 @@ class DeviceMatrix:
         if not self.handle:
             raise TachyonCudaError(f"tc_matrix_upload: {ctx.last_error()}")
 
+    @classmethod
+    def quantize(cls, ctx: Context, data: np.ndarray, rows: int, cols: int, fmt: str) -> "DeviceMatrix":
+        """``Matrix::from_f32`` (src/weights.rs:82-105) on the device: uploads the f32 values and
+        quantizes them there with Tachyon's own quantizers; same bytes as the host path."""
+        from .weights import KIND_Q4, KIND_Q8
+
+        kind = {"bf16": KIND_BF16, "q8": KIND_Q8, "int8": KIND_Q8, "q4": KIND_Q4, "int4": KIND_Q4}[fmt.lower()]
+        data = np.ascontiguousarray(data, np.float32).reshape(-1)
+        assert data.size == rows * cols
+        self = cls.__new__(cls)
+        self.ctx, self.kind, self.rows, self.cols = ctx, kind, rows, cols
+        self.handle = ctx.lib.tc_matrix_quantize(ctx.handle, kind, rows, cols, _ptr(data))
+        if not self.handle:
+            raise TachyonCudaError(f"tc_matrix_quantize: {ctx.last_error()}")
+        nb = cols // 32
+        self.nbytes = {KIND_BF16: rows * cols * 2, KIND_Q8: rows * cols + rows * nb * 2,
+                       KIND_Q4: rows * cols // 2 + rows * (-(-nb // 8) * 5) * 4}[kind]
+        return self
+
+    def to_host(self) -> Matrix:
+        """The matrix's buffers copied back: a host ``Matrix`` with the same bytes."""
+        from .weights import KIND_Q4, KIND_Q8
+
+        nb = self.cols // 32
+        if self.kind == KIND_BF16:
+            scales, data = None, np.empty(self.rows * self.cols, np.uint16)
+        elif self.kind == KIND_Q8:
+            scales, data = np.empty(self.rows * nb, np.uint16), np.empty(self.rows * self.cols, np.int8)
+        else:
+            scales = np.empty(self.rows * (-(-nb // 8) * 5), np.uint32)
+            data = np.empty(self.rows * self.cols // 2, np.uint8)
+        rc = self.ctx.lib.tc_matrix_download(self.handle, _ptr(scales), 0 if scales is None else scales.nbytes,
+                                             _ptr(data), data.nbytes)
+        self.ctx._check(rc, "tc_matrix_download")
+        return Matrix(self.kind, self.rows, self.cols, scales, data)
+
     def free(self):
         if self.handle and self.ctx.handle:
             self.ctx.lib.tc_matrix_free(self.handle)
@@ -381,9 +419,10 @@ class MoeLayer:
         self.hidden, self.experts = router.cols, router.rows
         self.inter, self.topk = down.cols, experts_per_token
         self.max_tokens = max_tokens
-        self.router = DeviceMatrix(ctx, router)
-        self.gate_up = DeviceMatrix(ctx, gate_up)
-        self.down = DeviceMatrix(ctx, down)
+        # (Matrices already on the device, e.g. quantized there, are taken as they are.)
+        self.router = router if isinstance(router, DeviceMatrix) else DeviceMatrix(ctx, router)
+        self.gate_up = gate_up if isinstance(gate_up, DeviceMatrix) else DeviceMatrix(ctx, gate_up)
+        self.down = down if isinstance(down, DeviceMatrix) else DeviceMatrix(ctx, down)
         self.weight_bytes = self.router.nbytes + self.gate_up.nbytes + self.down.nbytes
         self.handle = ctx.lib.tc_moe_layer_create(
             ctx.handle, self.hidden, self.experts, self.topk, self.inter, self.router.handle,

@@ -28,6 +28,7 @@ const SOURCES: &[&str] = &[
     "experts_prefill",
     "moe_decode",
     "int8_peak",
+    "quantize",
     "umma_selftest",
     "combine",
     "ep",

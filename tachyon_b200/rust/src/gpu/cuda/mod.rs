@@ -80,6 +80,14 @@ extern "C" {
         data: *const c_void,
         data_bytes: usize,
     ) -> *mut TcMatrix;
+    /// `Matrix::from_f32` on the device: same bytes as the host quantizers.
+    fn tc_matrix_quantize(
+        ctx: *mut TcCtx,
+        kind: c_int,
+        rows: usize,
+        cols: usize,
+        data: *const f32,
+    ) -> *mut TcMatrix;
     fn tc_matrix_free(m: *mut TcMatrix);
     #[allow(clippy::too_many_arguments)]
     fn tc_moe_layer_create(
@@ -406,6 +414,7 @@ fn _unused_entry_points() {
         tc_capture_end as usize,
         tc_graph_launch as usize,
         tc_graph_free as usize,
+        tc_matrix_quantize as usize,
     );
     let _ = DeviceBuf::len;
 }
