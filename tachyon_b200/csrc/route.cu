@@ -18,6 +18,8 @@
 // The softmax exponential is evaluated in double precision and rounded to
 // float; the CPU path calls libm's expf. The two agree except where expf
 // itself is not correctly rounded, hence the 1e-5 tolerance on gates.
+#include <algorithm>
+
 #include "dispatch_common.cuh"
 #include "experts_common.cuh"
 #include "route_common.cuh"
@@ -157,6 +159,141 @@ __global__ void __launch_bounds__(ROUTE_THREADS) route_kernel(const RouteArgs a)
     }
 }
 
+// Prefill-size batches: a CTA takes ROUTE_TILE tokens at a time (walking tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ...), so that every warp has work in every step: a warp per token for
+// the norm, the ranking and the quantization, four threads per (token, expert) pair for the
+// logits, with the router matrix staged once per CTA. Same arithmetic per token as route_kernel.
+constexpr int ROUTE_TILE = 8;
+
+// Shared memory of the tile kernel before the staged router matrix: padded rows, logits, norm weight.
+__host__ __device__ inline size_t route_tile_bytes(int hidden, int experts) {
+    return (size_t(ROUTE_TILE) * (hidden / QK * ROW_PAD_BLOCK + experts) * 4 + size_t(hidden) * 4 + 127) / 128 * 128;
+}
+
+__global__ void __launch_bounds__(ROUTE_THREADS) route_tile_kernel(const RouteArgs a) {
+    extern __shared__ __align__(128) float smem[];
+    const int hidden = a.hidden, experts = a.experts, topk = a.topk;
+    const int rstride = hidden / QK * ROW_PAD_BLOCK;  // floats per padded row
+    float* xrows = smem;                              // [ROUTE_TILE] padded rows
+    float* slog = xrows + ROUTE_TILE * rstride;       // [ROUTE_TILE][experts]
+    float* snw = slog + ROUTE_TILE * experts;         // [hidden] the norm's weight
+    __shared__ __align__(8) uint64_t s_wbar;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    grid_launch_dependents();
+    const int wstride = 2 * hidden + 32;
+    uint8_t* wsm = reinterpret_cast<uint8_t*>(smem) + route_tile_bytes(hidden, experts);
+    if (a.norm_w)
+        for (int c = tid; c < hidden; c += ROUTE_THREADS) snw[c] = a.norm_w[c];  // (a constant: before the wait)
+    if (a.stage_router) {
+        if (tid == 0) {
+            mbar_init(&s_wbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&s_wbar, uint32_t(experts) * 2u * uint32_t(hidden));
+        }
+        __syncthreads();
+        if (warp == 0)
+            for (int e = lane; e < experts; e += 32)
+                bulk_copy(wsm + size_t(e) * wstride, a.router + size_t(e) * hidden, 2 * hidden, &s_wbar);
+    }
+    grid_dependency_wait();
+    bool w_landed = true, w_waited = false;
+    const int padded = (hidden / QK + SUPER - 1) / SUPER * SUPER;
+    const int tiles = (a.t + ROUTE_TILE - 1) / ROUTE_TILE;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int t0 = tile * ROUTE_TILE, nt = min(ROUTE_TILE, a.t - t0);
+        __syncthreads();  // the previous tile's rows and logits are no longer read
+        const int vec_per_row = hidden / 4;
+        for (int k = 0; k < nt; k++) {
+            const float4* src = reinterpret_cast<const float4*>(a.x + size_t(t0 + k) * hidden);
+            for (int i = tid; i < vec_per_row; i += ROUTE_THREADS)
+                *reinterpret_cast<float4*>(xrows + k * rstride + padded_at(4 * i)) = src[i];
+        }
+        __syncthreads();
+        if (a.norm_w && warp < nt) {  // a warp per token
+            float* xr = xrows + warp * rstride;
+            const float ss = __fdiv_rn(sum_squares_padded_row(xr, hidden, lane), float(hidden));
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(ss + a.eps));
+            __syncwarp();
+#pragma unroll 4
+            for (int k = 0; k < hidden / QK; k++)
+                xr[k * ROW_PAD_BLOCK + lane] = xr[k * ROW_PAD_BLOCK + lane] * inv * snw[k * QK + lane];
+        }
+        if (a.stage_router && !w_waited) {
+            w_landed = mbar_wait_bounded(&s_wbar, 0);
+            w_waited = true;
+        }
+        __syncthreads();
+        // Logits: four threads per (expert, group of ROUTE_TG tokens): the expert's row is read from
+        // shared memory once for the group's tokens (the row reads, distinct per expert, are what
+        // the shared-memory pipe is busy with; the tokens' reads are broadcasts). Each (token,
+        // expert) logit keeps its own accumulators: the same sums as one token at a time.
+        constexpr int ROUTE_TG = 4;
+        const int groups = (nt + ROUTE_TG - 1) / ROUTE_TG, tasks = groups * experts;
+        for (int p0 = 0; p0 < tasks; p0 += ROUTE_THREADS / 4) {
+            const int p = p0 + (tid >> 2), q = tid & 3;
+            const bool valid = p < tasks;
+            const int grp = valid ? p / experts : 0, e = valid ? p - grp * experts : 0;
+            float acc[ROUTE_TG][4];
+#pragma unroll
+            for (int k = 0; k < ROUTE_TG; k++) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.0f;
+            if (p0 + ((tid >> 5) << 3) < tasks) {  // (a warp without work skips the loop)
+                const bool staged = a.stage_router && w_landed;
+                const uint8_t* ws = wsm + size_t(e) * wstride + q * 8;
+                const uint16_t* wg = a.router + size_t(e) * hidden + q * 4;
+                const float* xr = xrows + size_t(grp * ROUTE_TG) * rstride + q * 4;
+#pragma unroll 2
+                for (int c = 0; c < hidden; c += 16) {
+                    const uint2 wv = staged ? *reinterpret_cast<const uint2*>(ws + 2 * c)
+                                            : __ldg(reinterpret_cast<const uint2*>(wg + c));
+                    const float w0 = bf16_lo(wv.x), w1 = bf16_hi(wv.x), w2 = bf16_lo(wv.y), w3 = bf16_hi(wv.y);
+#pragma unroll
+                    for (int k = 0; k < ROUTE_TG; k++) {
+                        if (grp * ROUTE_TG + k < nt) {
+                            const float4 xv = *reinterpret_cast<const float4*>(xr + k * rstride + padded_at(c));
+                            acc[k][0] = fmaf(w0, xv.x, acc[k][0]);
+                            acc[k][1] = fmaf(w1, xv.y, acc[k][1]);
+                            acc[k][2] = fmaf(w2, xv.z, acc[k][2]);
+                            acc[k][3] = fmaf(w3, xv.w, acc[k][3]);
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < ROUTE_TG; k++) {
+                // As route_dot_quad: the two 8-lane accumulators added lane-wise, then the hsum tree.
+                float v[4], sv[4];
+#pragma unroll
+                for (int l = 0; l < 4; l++) v[l] = acc[k][l] + __shfl_xor_sync(0xffffffffu, acc[k][l], 2);
+#pragma unroll
+                for (int l = 0; l < 4; l++) sv[l] = v[l] + __shfl_xor_sync(0xffffffffu, v[l], 1);
+                float y = (sv[0] + sv[2]) + (sv[1] + sv[3]);
+                y = y + 0.0f;  // the dot's scalar tail is an empty sum
+                const int token = grp * ROUTE_TG + k;
+                if (valid && q == 0 && token < nt) {
+                    if (a.bias) y = y + a.bias[e];
+                    slog[token * experts + e] = y;
+                    if (a.logits) a.logits[size_t(t0 + token) * experts + e] = y;
+                }
+            }
+        }
+        __syncthreads();
+        if (warp < nt) {  // a warp per token: ranking and gates, then the row's 8-bit blocks
+            const size_t token = size_t(t0 + warp);
+            route_topk_gates(slog + warp * experts, experts, topk, a.ids + token * topk, a.gates + token * topk, lane);
+            route_quantize_padded_row(xrows + warp * rstride, hidden, a.xq + token * hidden, a.xs + token * padded,
+                                      a.xsum + token * padded, lane);
+        }
+    }
+    if (a.stage_router && (!w_waited || !w_landed)) {
+        // Not waited for (a CTA without tiles) or not arrived in time: a last bounded chance for the
+        // copy to land before this shared memory is released; a late copy is reported.
+        const bool late = w_waited && !w_landed;
+        mbar_wait_bounded(&s_wbar, 0);
+        if (late && tid == 0) atomicExch(a.status, ERR_COPY_WAIT_TIMEOUT);
+    }
+}
+
 // One warp per row.
 __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, float eps, int t, int n,
                                float* out) {
@@ -175,6 +312,7 @@ __global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w, floa
 
 void init_kernels_route() {
     cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ROUTE_SMEM_LIMIT));
+    cudaFuncSetAttribute(route_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ROUTE_SMEM_LIMIT));
 }
 
 int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, const float* x,
@@ -210,12 +348,21 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
     a.stage_router = staged <= ROUTE_SMEM_LIMIT;
     if (a.stage_router) smem = staged;
     if (smem < sizeof(DispatchSmem)) smem = sizeof(DispatchSmem);
-    // One CTA per token while that is at most three CTAs per SM (short CTAs overlap best);
-    // beyond that a fixed grid whose CTAs walk several tokens each, so that a prefill-size
-    // batch stages the router matrix a few hundred times instead of once per token.
     const int sms = ws.sms > 0 ? ws.sms : 148;
-    const int grid = a.fuse_dispatch || t <= 3 * sms ? t : 3 * sms;
-    launch_overlapped(route_kernel, dim3(grid), dim3(ROUTE_THREADS), smem, stream, a);
+    if (a.fuse_dispatch) {
+        // Up to one CTA's worth of tokens: a CTA per token; the last one to finish runs the dispatch.
+        launch_overlapped(route_kernel, dim3(t), dim3(ROUTE_THREADS), smem, stream, a);
+    } else {
+        // Larger batches: CTAs that walk tiles of ROUTE_TILE tokens with every warp busy, as many as
+        // stay resident (the staged router matrix is then read a few hundred times, not once per token).
+        size_t tsmem = route_tile_bytes(d.hidden, d.experts);
+        const size_t tstaged = tsmem + size_t(d.experts) * (2 * size_t(d.hidden) + 32);
+        a.stage_router = tstaged <= ROUTE_SMEM_LIMIT;
+        if (a.stage_router) tsmem = tstaged;
+        const int per_sm = int(std::max<size_t>(1, std::min<size_t>(4, (220 * 1024) / (tsmem + 1024))));
+        const int tiles = (t + ROUTE_TILE - 1) / ROUTE_TILE;
+        launch_overlapped(route_tile_kernel, dim3(std::min(tiles, per_sm * sms)), dim3(ROUTE_THREADS), tsmem, stream, a);
+    }
     int launched = 1;
     if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
     return launched;

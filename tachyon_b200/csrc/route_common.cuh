@@ -85,71 +85,80 @@ __device__ __forceinline__ void route_norm_row(float* xrow, int hidden, const fl
     __syncthreads();
 }
 
-// Router logits of one token, experts e_lo..e_hi-1, into slog[e] (and, when given, a global row).
-// Four threads per expert, each holding four of the dot's sixteen float lanes: thread q
-// owns elements 16j+4q..16j+4q+3, so q = 0,1 hold the first 8-lane accumulator and
-// q = 2,3 the second. `staged`: the router matrix in shared memory with rows `wstride`
-// bytes apart and row 0 holding expert e_lo, or null to read it from global memory (a whole
-// batch of steps is requested before the chains run, so the loads overlap instead of each
-// waiting for the previous fma). Called by every thread; the caller puts a CTA barrier
-// after it.
-__device__ __forceinline__ void route_logits(const uint16_t* router, const uint8_t* staged, int wstride,
-                                             const float* xrow, const float* bias, int hidden, int e_lo, int e_hi,
-                                             float* slog, float* logits_row, int tid, int nthreads) {
+// One router logit: dot(bf16 row of expert e, xrow) by FOUR threads (q = 0..3 of an aligned
+// quad), each holding four of the dot's sixteen float lanes: thread q owns elements
+// 16j+4q..16j+4q+3, so q = 0,1 hold the first 8-lane accumulator of the AVX2 dot and q = 2,3
+// the second. `staged`: the router matrix in shared memory with rows `wstride` bytes apart (row
+// index e_staged), or null to read expert e's row from global memory (a whole batch of steps
+// is requested before the chains run, so the loads overlap instead of each waiting for the
+// previous fma). A warp none of whose quads has work passes busy = false and skips the loop (it
+// would only take shared-memory bandwidth from the warps that have work) but still takes part
+// in the shuffles. The value is complete in every thread of the quad.
+__device__ __forceinline__ float route_dot_quad(const uint16_t* router, const uint8_t* staged, int wstride,
+                                                const float* xrow, int hidden, int e, int q, bool busy,
+                                                int e_staged = -1) {
     constexpr int BATCH = 8;
-    for (int e0 = e_lo; e0 < e_hi; e0 += nthreads / 4) {
-        const int e = e0 + (tid >> 2), q = tid & 3;
-        const bool valid = e < e_hi;
-        const uint16_t* w = router + size_t(valid ? e : e_lo) * hidden + q * 4;
-        const float* xr = xrow + q * 4;
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        // A warp none of whose eight experts exists skips the dot: it would only take
-        // shared-memory bandwidth from the warps that have work.
-        if (e0 + ((tid >> 5) << 3) >= e_hi) {
-        } else if (staged) {
-            const uint8_t* ws = staged + size_t(valid ? e - e_lo : 0) * wstride + q * 8;
+    const uint16_t* w = router + size_t(e) * hidden + q * 4;
+    const float* xr = xrow + q * 4;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (!busy) {
+    } else if (staged) {
+        const uint8_t* ws = staged + size_t(e_staged >= 0 ? e_staged : e) * wstride + q * 8;
 #pragma unroll 4
-            for (int c = 0; c < hidden; c += 16) {
-                const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
-                const float4 xv = *reinterpret_cast<const float4*>(xr + c);
-                acc[0] = fmaf(bf16_lo(wv.x), xv.x, acc[0]);
-                acc[1] = fmaf(bf16_hi(wv.x), xv.y, acc[1]);
-                acc[2] = fmaf(bf16_lo(wv.y), xv.z, acc[2]);
-                acc[3] = fmaf(bf16_hi(wv.y), xv.w, acc[3]);
-            }
-        } else {
-            for (int c0 = 0; c0 < hidden; c0 += 16 * BATCH) {
-                uint2 wv[BATCH];
+        for (int c = 0; c < hidden; c += 16) {
+            const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
+            const float4 xv = *reinterpret_cast<const float4*>(xr + c);
+            acc[0] = fmaf(bf16_lo(wv.x), xv.x, acc[0]);
+            acc[1] = fmaf(bf16_hi(wv.x), xv.y, acc[1]);
+            acc[2] = fmaf(bf16_lo(wv.y), xv.z, acc[2]);
+            acc[3] = fmaf(bf16_hi(wv.y), xv.w, acc[3]);
+        }
+    } else {
+        for (int c0 = 0; c0 < hidden; c0 += 16 * BATCH) {
+            uint2 wv[BATCH];
 #pragma unroll
-                for (int u = 0; u < BATCH; u++)
-                    wv[u] = c0 + 16 * u < hidden ? __ldg(reinterpret_cast<const uint2*>(w + c0 + 16 * u))
-                                                 : make_uint2(0u, 0u);
+            for (int u = 0; u < BATCH; u++)
+                wv[u] = c0 + 16 * u < hidden ? __ldg(reinterpret_cast<const uint2*>(w + c0 + 16 * u))
+                                             : make_uint2(0u, 0u);
 #pragma unroll
-                for (int u = 0; u < BATCH; u++) {
-                    if (c0 + 16 * u < hidden) {
-                        const float4 xv = *reinterpret_cast<const float4*>(xr + c0 + 16 * u);
-                        acc[0] = fmaf(bf16_lo(wv[u].x), xv.x, acc[0]);
-                        acc[1] = fmaf(bf16_hi(wv[u].x), xv.y, acc[1]);
-                        acc[2] = fmaf(bf16_lo(wv[u].y), xv.z, acc[2]);
-                        acc[3] = fmaf(bf16_hi(wv[u].y), xv.w, acc[3]);
-                    }
+            for (int u = 0; u < BATCH; u++) {
+                if (c0 + 16 * u < hidden) {
+                    const float4 xv = *reinterpret_cast<const float4*>(xr + c0 + 16 * u);
+                    acc[0] = fmaf(bf16_lo(wv[u].x), xv.x, acc[0]);
+                    acc[1] = fmaf(bf16_hi(wv[u].x), xv.y, acc[1]);
+                    acc[2] = fmaf(bf16_lo(wv[u].y), xv.z, acc[2]);
+                    acc[3] = fmaf(bf16_hi(wv[u].y), xv.w, acc[3]);
                 }
             }
         }
-        // acc0 + acc1 lane-wise: lane l of the first accumulator (q = l/4) plus
-        // lane l of the second (q = 2 + l/4): the thread two to the right.
-        float v[4];
+    }
+    // acc0 + acc1 lane-wise: lane l of the first accumulator (q = l/4) plus
+    // lane l of the second (q = 2 + l/4): the thread two to the right.
+    float v[4];
 #pragma unroll
-        for (int l = 0; l < 4; l++) v[l] = acc[l] + __shfl_xor_sync(0xffffffffu, acc[l], 2);
-        // Now q = 0 holds v0..v3 and q = 1 holds v4..v7 (q = 2,3 hold copies).
-        // hsum: (v0+v4, v1+v5, v2+v6, v3+v7) -> (s0+s2, s1+s3) -> sum.
-        float sv[4];
+    for (int l = 0; l < 4; l++) v[l] = acc[l] + __shfl_xor_sync(0xffffffffu, acc[l], 2);
+    // Now q = 0 holds v0..v3 and q = 1 holds v4..v7 (q = 2,3 hold copies).
+    // hsum: (v0+v4, v1+v5, v2+v6, v3+v7) -> (s0+s2, s1+s3) -> sum.
+    float sv[4];
 #pragma unroll
-        for (int l = 0; l < 4; l++) sv[l] = v[l] + __shfl_xor_sync(0xffffffffu, v[l], 1);
-        float y = (sv[0] + sv[2]) + (sv[1] + sv[3]);
-        if (valid && q == 0) {
-            // The dot's scalar tail is an empty sum (hidden is a multiple of 32): hsum + 0.0.
-            y = y + 0.0f;
+    for (int l = 0; l < 4; l++) sv[l] = v[l] + __shfl_xor_sync(0xffffffffu, v[l], 1);
+    const float y = (sv[0] + sv[2]) + (sv[1] + sv[3]);
+    // The dot's scalar tail is an empty sum (hidden is a multiple of 32): hsum + 0.0.
+    return y + 0.0f;
+}
+
+// Router logits of one token, experts e_lo..e_hi-1, into slog[e] (and, when given, a global
+// row), by every thread of the CTA, four per expert. `staged`: rows e_lo.. of the router
+// matrix in shared memory, or null. The caller puts a CTA barrier after it.
+__device__ __forceinline__ void route_logits(const uint16_t* router, const uint8_t* staged, int wstride,
+                                             const float* xrow, const float* bias, int hidden, int e_lo, int e_hi,
+                                             float* slog, float* logits_row, int tid, int nthreads) {
+    for (int e0 = e_lo; e0 < e_hi; e0 += nthreads / 4) {
+        const int e = e0 + (tid >> 2);
+        const bool valid = e < e_hi;
+        float y = route_dot_quad(router, staged, wstride, xrow, hidden, valid ? e : e_lo, tid & 3,
+                                 e0 + ((tid >> 5) << 3) < e_hi, valid ? e - e_lo : 0);
+        if (valid && (tid & 3) == 0) {
             if (bias) y = y + bias[e];
             slog[e] = y;
             if (logits_row) logits_row[e] = y;
@@ -293,6 +302,75 @@ __device__ __forceinline__ void route_quantize_row(const float* xrow, int hidden
             xs_row[b] = d;
             xsum_row[b] = d * float(qsum);
         }
+    }
+}
+
+// Rows kept in shared memory with four floats of padding after every 32-element block
+// (element c at c + 4 * (c / 32)): lanes that each walk their own block then spread over the
+// banks instead of all hitting the same one, and 16-byte vector accesses stay aligned.
+constexpr int ROW_PAD_BLOCK = QK + 4;
+__device__ __forceinline__ int padded_at(int c) { return c + ((c >> 5) << 2); }
+
+// sum_squares_avx_order over such a padded row (n a multiple of 32): lane L owns elements
+// L, L + 32, ... as there; the same additions in the same order.
+__device__ __forceinline__ float sum_squares_padded_row(const float* xr, int n, int lane) {
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int k = 0; k < n / QK; k++) {
+        const float v = xr[k * ROW_PAD_BLOCK + lane];
+        acc = fmaf(v, v, acc);
+    }
+    float s = acc + __shfl_down_sync(0xffffffffu, acc, 8);
+    s = s + __shfl_down_sync(0xffffffffu, s, 16);
+    s = hsum8(s, 0xffffffffu);
+    s = s + 0.0f;  // the scalar tail is an empty sum
+    return __shfl_sync(0xffffffffu, s, 0);
+}
+
+// The row quantization by ONE warp with a lane per 32-block (32 blocks at a time) over a
+// padded row: each lane runs its block's 32 elements itself, so the warp spends a few
+// hundred instructions on the row instead of a shuffle reduction per block. Same values:
+// the maximum does not depend on the order, the sum of the quants is an integer.
+__device__ __forceinline__ void route_quantize_padded_row(const float* xrow, int hidden, int8_t* xq_row, float* xs_row,
+                                                          float* xsum_row, int lane) {
+    const int nb = hidden / QK;
+    const int padded = (nb + SUPER - 1) / SUPER * SUPER;
+    for (int b0 = 0; b0 < padded; b0 += 32) {
+        const int b = b0 + lane;
+        if (b >= padded) continue;
+        if (b >= nb) {  // zero padding up to whole super-blocks
+            xs_row[b] = 0.0f;
+            xsum_row[b] = 0.0f;
+            continue;
+        }
+        const float4* xb = reinterpret_cast<const float4*>(xrow + b * ROW_PAD_BLOCK);
+        float4 v[QK / 4];
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < QK / 4; i++) {
+            v[i] = xb[i];
+            amax = fmaxf(fmaxf(fmaxf(fmaxf(amax, fabsf(v[i].x)), fabsf(v[i].y)), fabsf(v[i].z)), fabsf(v[i].w));
+        }
+        const float d = __fdiv_rn(amax, 127.0f);
+        const float id = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        auto q8 = [&](float x) {
+            const float r = roundf(x * id);
+            return (r != r) ? 0 : int(fminf(127.0f, fmaxf(-128.0f, r)));
+        };
+        int qsum = 0;
+        uint32_t words[QK / 4];
+#pragma unroll
+        for (int i = 0; i < QK / 4; i++) {
+            const int q0 = q8(v[i].x), q1 = q8(v[i].y), q2 = q8(v[i].z), q3 = q8(v[i].w);
+            qsum += q0 + q1 + q2 + q3;
+            words[i] = uint32_t(q0 & 0xFF) | (uint32_t(q1 & 0xFF) << 8) | (uint32_t(q2 & 0xFF) << 16) |
+                       (uint32_t(q3 & 0xFF) << 24);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(xq_row + b * QK);
+        dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+        dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+        xs_row[b] = d;
+        xsum_row[b] = d * float(qsum);
     }
 }
 
