@@ -753,7 +753,8 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
         const char* why = tc::ep_forward_peer(ctx->ep, layer->epb, d,
                                               static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
                                               layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
-                                              layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
+                                              layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n,
+                                              ctx->decode_block && ctx->arith == tc::ARITH_FAST, ctx->phase_stamps);
         ctx->launches += n;
         layer->last_t = t;
         if (why) return fail(ctx, "expert-parallel block: %s", why);

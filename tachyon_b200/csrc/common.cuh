@@ -299,16 +299,36 @@ int launch_quantize(int kind, const float* x, size_t rows, size_t cols, void* sc
                     cudaStream_t stream);
 
 // ---- the whole block of a decode-size batch as one kernel (moe_decode.cu)
+// Expert parallelism inside the one-kernel block (ranks > 0). Every rank runs this kernel on
+// its own GPU with its own t tokens and its own contiguous range of experts; the ranks'
+// windows are mapped into one another (CUDA IPC). The router phase stores each token's 8-bit
+// row, scales and expert ids into EVERY rank's window and announces it there with a
+// system-scope reduction on a counter word; the expert phases then run over all ranks' tokens
+// for this rank's experts; the down phase stores each output row into its home rank's window
+// and announces itself the same way; the combine waits for every rank's CTAs. The counters
+// only grow (a block is complete when they reach (blocks so far + 1) x arrivals per block), so
+// nothing is reset across GPUs. Every wait is bounded.
+struct DecodeEp {
+    int ranks = 0, me = 0, first = 0, local = 0;  // this rank; its first expert and how many it holds
+    uint8_t* base[8] = {};                // every rank's window as mapped here
+    size_t off_xq = 0, off_xs = 0, off_xsum = 0, off_ids = 0, off_out = 0, off_flags = 0;
+    uint32_t* epoch = nullptr;                    // blocks this rank has completed on this path
+    int mute = 0;                                 // testing: rows are sent but not announced
+};
 void init_kernels_decode();
-// True if a block of t tokens of this shape can take the one-kernel path.
-bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t);
+// True if a block of t tokens (per rank, when expert-parallel over `ranks` ranks) of this shape can
+// take the one-kernel path.
+bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t, int ranks = 0);
 // y[t, hidden] += moe(x) (or moe(rmsnorm(x)) when norm_w is set). Leaves the routing in
-// ws.ids / ws.gates / ws.logits and the 8-bit rows in ws.xq / ws.xs; builds no dispatch.
+// ws.ids / ws.gates / ws.logits (and, on one GPU, the 8-bit rows in ws.xq / ws.xs); builds no dispatch.
 // stamps: null, or 8 words that CTA 0 fills with the wall clock at its phase boundaries.
+// ep: null, or the expert-parallel set-up (gate_up_tiled / down_tiled then hold this rank's experts
+// and hidden_f_all is scratch for every rank's slots: ranks * t * topk rows of `inter` floats).
 int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
                         const float* norm_w, float eps, int t, float* y, const uint8_t* gate_up_tiled,
                         const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit,
-                        unsigned long long* stamps, cudaStream_t stream);
+                        unsigned long long* stamps, cudaStream_t stream, const DecodeEp* ep = nullptr,
+                        float* hidden_f_all = nullptr);
 
 int launch_rmsnorm(const float* x, const float* w, float eps, int t, int n, float* out,
                    cudaStream_t stream);

@@ -405,14 +405,15 @@ const char* ep_peer_enable(EpState& st, int hidden, int topk, int max_tokens) {
     size_t o = 0;
     p.off_xq = o, o = up(o + G * hidden);
     p.off_xs = o, o = up(o + G * nbp * 4);
+    p.off_xsum = o, o = up(o + G * nbp * 4);
     p.off_ids = o, o = up(o + G * topk * 4);
     p.off_out = o, o = up(o + size_t(max_tokens) * topk * hidden * 4);
-    p.off_flags = o, o = up(o + 2 * 8 * 4);
+    p.off_flags = o, o = up(o + 3 * 8 * 4);  // two sets of per-rank flags, then the one-kernel path's counters
     p.bytes = o;
     if (cudaMalloc(reinterpret_cast<void**>(&p.window), p.bytes) != cudaSuccess) return "cudaMalloc(window) failed";
     cudaMemset(p.window, 0, p.bytes);
-    if (cudaMalloc(reinterpret_cast<void**>(&p.epoch), 16) != cudaSuccess) return "cudaMalloc failed";
-    cudaMemset(p.epoch, 0, 16);
+    if (cudaMalloc(reinterpret_cast<void**>(&p.epoch), 32) != cudaSuccess) return "cudaMalloc failed";
+    cudaMemset(p.epoch, 0, 32);
     cudaIpcMemHandle_t mine;
     if (cudaIpcGetMemHandle(&mine, p.window) != cudaSuccess) return "cudaIpcGetMemHandle failed";
     // Every rank's handle, through the communicator that already exists.
@@ -452,11 +453,29 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
                             const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                             const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                             const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
-                            cudaStream_t stream, int* launches) {
+                            cudaStream_t stream, int* launches, bool one_kernel, unsigned long long* stamps) {
     EpUniform& u = st.uni;
     EpPeer& p = st.peer;
     const int R = st.size, G = R * t;
     const int nbp = (d.hidden / QK + 7) / 8 * 8;
+    if (one_kernel && decode_block_applies(d, gate_up.kind, down.kind, t, R)) {
+        // Decode-size batch: the whole block, both exchanges included, is one kernel per rank.
+        DecodeEp e;
+        e.ranks = R, e.me = st.rank, e.first = b.first, e.local = b.local;
+        for (int r = 0; r < R; r++) e.base[r] = p.base[r];
+        e.off_xq = p.off_xq, e.off_xs = p.off_xs, e.off_xsum = p.off_xsum, e.off_ids = p.off_ids;
+        e.off_out = p.off_out, e.off_flags = p.off_flags;
+        e.epoch = p.epoch + 4;
+        if (p.mute_next > 0) {
+            e.mute = 1;
+            p.mute_next--;
+        }
+        const int n = launch_decode_block(d, gate_up.kind, router, bias, x, norm_w, eps, t, y, gate_up_tiled, down_tiled,
+                                          ws, sms, p.wait_limit, stamps, stream, &e, u.hidden_f);
+        if (n < 0) return "the one-kernel block does not fit this shape";
+        *launches += n;
+        return nullptr;
+    }
     PeerPlan plan{};
     for (int r = 0; r < R; r++) plan.base[r] = p.base[r];
     plan.off_xq = p.off_xq, plan.off_xs = p.off_xs, plan.off_ids = p.off_ids, plan.off_flags = p.off_flags;

@@ -37,11 +37,12 @@ struct EpPeer {
     int tokens = 0, hidden = 0, topk = 0;      // per-rank token capacity and row shape
     uint8_t* window = nullptr;                 // this rank's
     uint8_t* base[8] = {};                     // every rank's window as mapped here (base[rank] == window)
-    size_t off_xq = 0, off_xs = 0, off_ids = 0, off_out = 0, off_flags = 0, bytes = 0;
+    size_t off_xq = 0, off_xs = 0, off_xsum = 0, off_ids = 0, off_out = 0, off_flags = 0, bytes = 0;
     uint32_t wait_limit = 1u << 23;            // polls a kernel spends on another rank's flag before giving up
     int mute_next = 0;                         // testing: this many coming blocks send rows without announcing them
     uint32_t* epoch = nullptr;                 // [0], [1]: this rank's signal counters (rows sent, outputs
-                                               // sent); [2]: arrival counter of the down kernel's CTAs
+                                               // sent); [2]: arrival counter of the down kernel's CTAs;
+                                               // [4]: blocks completed by the one-kernel path
 };
 
 struct EpState {
@@ -88,7 +89,8 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
                             const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                             const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                             const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
-                            cudaStream_t stream, int* launches);
+                            cudaStream_t stream, int* launches, bool one_kernel = false,
+                            unsigned long long* stamps = nullptr);
 const char* ep_barrier(EpState& st, cudaStream_t stream);
 const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,

@@ -51,7 +51,9 @@ constexpr int D_TOK = 8 * D_GMAX;  // tokens per block this kernel takes; rows s
 constexpr int D_NORM_HELD = 8;     // elements of the norm's weight a thread holds (rows of up to 8 x 256 floats)
 constexpr int D_ROUTE_VEC = 10;    // 16-byte pieces of the router matrix a thread holds at a time
 constexpr int D_NSEG = 4;          // experts of a CTA's range whose slot lists are held at a time
-constexpr size_t D_SMEM_LIMIT = 227 * 1024 - 2048;  // dynamic part: the kernel also has about 1.2 KB of static shared memory
+constexpr size_t D_SMEM_LIMIT = 227 * 1024 - 3072;  // dynamic part: the kernel also has up to 2.5 KB of static shared memory
+
+constexpr int DECODE_EP_FLAG_ROUTE = 16, DECODE_EP_FLAG_DOWN = 17;  // words of the window's flag area
 
 struct DecodeArgs {
     // router phase
@@ -77,6 +79,8 @@ struct DecodeArgs {
     int route_rows;           // rows of the router matrix staged at a time in the router phase
     int dense;
     uint32_t* sync;           // [GRID_SYNC_WORDS], zero between launches
+    DecodeEp ep;              // ranks > 0: experts sharded over the GPUs of one node (see DecodeEp)
+    int ids_slots;            // (token, pick) slots the block's ids take in shared memory
     uint32_t spin_limit;
     int* status;
     unsigned long long* stamps;  // when set: CTA 0 stores the wall clock (ns) at its phase boundaries [8]
@@ -94,19 +98,22 @@ struct DLayout {
     }
     __host__ __device__ static int route_base(int hidden, int experts) { return ((hidden + experts) * 4 + 127) / 128 * 128; }
     __host__ __device__ DLayout(int nwarps, int stages, int xcap, int route_rows, int hidden, int inter, int experts,
-                                int topk) {
+                                int topk, int ids_slots) {
         int o = nwarps * stages * Rec<KIND>::BYTES;
         ring = 0;
         o = (o + 127) / 128 * 128;
         x0 = o;
         xbytes = token_bytes(xcap, hidden, inter);
         // The router phase keeps the token's row, its logits and route_rows rows of the router matrix here.
-        const int route_bytes = route_base(hidden, experts) + route_rows * (2 * hidden + 32) + 64;
+        // (or, once the logits are done, the token's 8-bit row and scales on their way to the other ranks)
+        const int row_bytes = hidden + 2 * 4 * ((hidden / QK + 7) / 8 * 8);
+        const int staged = route_rows * (2 * hidden + 32);
+        const int route_bytes = route_base(hidden, experts) + (staged > row_bytes ? staged : row_bytes) + 64;
         if (xbytes < route_bytes) xbytes = route_bytes;
         xbytes = (xbytes + 127) / 128 * 128;
         o += xbytes;
         ids = o;
-        o += D_TOK * topk * 4;
+        o += ids_slots * 4;
         lists = o;
         o += D_NSEG * D_TOK * 2 * 2;
         o = (o + 15) / 16 * 16;
@@ -165,7 +172,21 @@ struct Phase {
     int first, n;      // this warp's first unit and how many it owns (stride nwarps)
 };
 
-template <int KIND>
+__device__ __forceinline__ void arrive_on_peer(uint32_t* flag) {
+    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+}
+// One thread: waits until the counter (written by other GPUs) has reached target, wrap-safe.
+__device__ __forceinline__ bool peer_count_wait(const uint32_t* ctr, uint32_t target, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; i++) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(ctr) : "memory");
+        if (int32_t(seen - target) >= 0) return true;
+        __nanosleep(i < 64 ? 32 : 256);
+    }
+    return false;
+}
+
+template <int KIND, bool EP>
 __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const DecodeArgs a) {
     using R = Rec<KIND>;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -174,7 +195,10 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     __shared__ int s_nactive;
     __shared__ int s_seg_count[D_NSEG];
     __shared__ uint8_t s_picked[MAX_EXPERTS];
-    __shared__ uint16_t s_active[MAX_EXPERTS];
+    __shared__ uint16_t s_active[MAX_EXPERTS];  // walk index -> expert (sparse walk); EP: -> the run's expert
+    __shared__ uint16_t s_skip[EP ? MAX_EXPERTS : 1];   // EP: slots of that expert in earlier runs
+    __shared__ uint32_t s_cnt[EP ? MAX_EXPERTS : 1];    // EP: slots per local expert
+    __shared__ uint32_t s_rids[MAX_TOPK];               // the routed token's picks, on their way out
     __shared__ uint32_t s_cpos[MAX_TOPK];
     __shared__ float s_cgate[MAX_TOPK];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -182,8 +206,18 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     const int bid = blockIdx.x, nctas = gridDim.x;
     const int STAGES = a.stages;
     const int t = a.t, hidden = a.hidden, experts = a.experts, topk = a.topk, inter = a.inter;
-    const int slots = t * topk;
-    const DLayout<KIND> L(nwarps, STAGES, a.xcap, a.route_rows, hidden, inter, experts, topk);
+    // Expert parallel: the expert phases see every rank's tokens (gathered in this rank's window).
+    const int ranks = EP ? a.ep.ranks : 1, own = EP ? a.ep.me * t : 0;  // own: this rank's first token among all
+    const int slots = ranks * t * topk;
+    uint8_t* window = EP ? a.ep.base[a.ep.me] : nullptr;
+    const int8_t* xq_all = EP ? reinterpret_cast<const int8_t*>(window + a.ep.off_xq) : a.xq;
+    const float* xs_all = EP ? reinterpret_cast<const float*>(window + a.ep.off_xs) : a.xs;
+    const float* xsum_all = EP ? reinterpret_cast<const float*>(window + a.ep.off_xsum) : a.xsum;
+    const uint32_t* ids_all = EP ? reinterpret_cast<const uint32_t*>(window + a.ep.off_ids) : a.ids;
+    const float* out_own = EP ? reinterpret_cast<const float*>(window + a.ep.off_out) : a.out;
+    const uint32_t* flags = EP ? reinterpret_cast<const uint32_t*>(window + a.ep.off_flags) : nullptr;
+    uint32_t epoch0 = 0;  // EP: blocks completed before this one
+    const DLayout<KIND> L(nwarps, STAGES, a.xcap, a.route_rows, hidden, inter, experts, topk, a.ids_slots);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * D_MAX_STAGES;
     uint32_t* s_ids = reinterpret_cast<uint32_t*>(smem + L.ids);
@@ -222,7 +256,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     // the picked ones (then the expert comes from the list made after the router phase).
     auto unit_ptr = [&](const Phase& P, int wu) {
         size_t flat = size_t(wu);
-        if (!a.dense) flat = size_t(s_active[wu / P.upe]) * P.upe + wu % P.upe;
+        if (!a.dense) flat = size_t(s_active[wu / P.upe] - (EP ? a.ep.first : 0)) * P.upe + wu % P.upe;
         return P.tiled + flat * P.nchunks * R::BYTES;
     };
     // Producer state: the next record's address, and what is left of its unit and phase.
@@ -365,21 +399,92 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 __syncthreads();  // the staged rows are no longer read; slog is complete up to here
             }
             if (warp == 0)
-                route_topk_gates(slog, experts, topk, a.ids + size_t(bid) * topk, a.gates + size_t(bid) * topk, lane);
-            route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * P0.nbp,
-                               a.xsum + size_t(bid) * P0.nbp, warp, lane, 1, nwarps - 1);
-            __syncthreads();
-            if (tid == 0) grid_arrive(a.sync + 0);
+                route_topk_gates(slog, experts, topk, EP ? s_rids : a.ids + size_t(bid) * topk,
+                                 a.gates + size_t(bid) * topk, lane);
+            if (!EP) {
+                route_quantize_row(xrow, hidden, a.xq + size_t(bid) * hidden, a.xs + size_t(bid) * P0.nbp,
+                                   a.xsum + size_t(bid) * P0.nbp, warp, lane, 1, nwarps - 1);
+                __syncthreads();
+                if (tid == 0) grid_arrive(a.sync + 0);
+            } else {
+                // The row is quantized into shared memory (where the router matrix was), then stored
+                // into every rank's window, this rank's included, and announced there.
+                int8_t* sq = reinterpret_cast<int8_t*>(wsm);
+                float* ss = reinterpret_cast<float*>(wsm + hidden);
+                float* ssum = ss + P0.nbp;
+                route_quantize_row(xrow, hidden, sq, ss, ssum, warp, lane, 1, nwarps - 1);
+                __syncthreads();
+                const size_t g = size_t(own + bid);  // this token among all ranks' tokens
+                const int vq = hidden / 16, vs = P0.nbp / 4, per_rank = vq + 2 * vs + topk;
+#pragma unroll 1
+                for (int i = tid; i < ranks * per_rank; i += nthreads) {
+                    const int r = i / per_rank, j = i - r * per_rank;
+                    uint8_t* w = a.ep.base[r];
+                    if (j < vq)
+                        reinterpret_cast<uint4*>(w + a.ep.off_xq + g * hidden)[j] = reinterpret_cast<const uint4*>(sq)[j];
+                    else if (j < vq + vs)
+                        reinterpret_cast<uint4*>(w + a.ep.off_xs + g * P0.nbp * 4)[j - vq] = reinterpret_cast<const uint4*>(ss)[j - vq];
+                    else if (j < vq + 2 * vs)
+                        reinterpret_cast<uint4*>(w + a.ep.off_xsum + g * P0.nbp * 4)[j - vq - vs] =
+                            reinterpret_cast<const uint4*>(ssum)[j - vq - vs];
+                    else
+                        reinterpret_cast<uint32_t*>(w + a.ep.off_ids)[g * topk + (j - vq - 2 * vs)] = s_rids[j - vq - 2 * vs];
+                }
+                if (tid < topk) a.ids[size_t(bid) * topk + tid] = s_rids[tid];  // (the routing taps read these)
+                __syncthreads();
+                if (tid < ranks && !a.ep.mute)
+                    arrive_on_peer(reinterpret_cast<uint32_t*>(a.ep.base[tid] + a.ep.off_flags) + DECODE_EP_FLAG_ROUTE);
+            }
         }
-        if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) s_abort = 1;
+        if (EP) {
+            epoch0 = *a.ep.epoch;
+            if (tid == 0 && !peer_count_wait(flags + DECODE_EP_FLAG_ROUTE, (epoch0 + 1u) * uint32_t(ranks * t), a.spin_limit))
+                s_abort = 4;
+        } else if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) {
+            s_abort = 1;
+        }
         __syncthreads();
         if (stamping) a.stamps[2] = wall_clock_ns();
 
         // ---- the batch's expert ids; for small batches the experts that were picked
         if (!s_abort) {
 #pragma unroll 1
-            for (int i = tid; i < slots; i += nthreads) s_ids[i] = __ldcg(a.ids + i);
-            if (!a.dense) {
+            for (int i = tid; i < slots; i += nthreads) s_ids[i] = __ldcg(ids_all + i);
+            if (EP) {
+                // Runs: each local expert's slots in pieces of up to D_TOK; (run, unit) pairs are what the
+                // CTAs and warps share out, so an expert with many tokens spreads over many warps.
+#pragma unroll 1
+                for (int e = tid; e < a.ep.local; e += nthreads) s_cnt[e] = 0;
+                __syncthreads();
+#pragma unroll 1
+                for (int i = tid; i < slots; i += nthreads) {
+                    const uint32_t e = s_ids[i] - uint32_t(a.ep.first);
+                    if (e < uint32_t(a.ep.local)) atomicAdd(&s_cnt[e], 1u);
+                }
+                __syncthreads();
+                if (warp == 0) {  // a lane per local expert, 32 at a time: the expert's runs after those before it
+                    int n = 0;
+#pragma unroll 1
+                    for (int e0 = 0; e0 < a.ep.local; e0 += 32) {
+                        const int e = e0 + lane;
+                        const int mine = e < a.ep.local ? int(s_cnt[e] + D_TOK - 1) / D_TOK : 0;
+                        int before = mine;
+#pragma unroll
+                        for (int o = 1; o < 32; o <<= 1) {
+                            const int up = __shfl_up_sync(0xffffffffu, before, o);
+                            if (lane >= o) before += up;
+                        }
+                        const int total = __shfl_sync(0xffffffffu, before, 31);
+                        before -= mine;
+                        for (int j = 0; j < mine; j++) {
+                            s_active[n + before + j] = uint16_t(a.ep.first + e);
+                            s_skip[n + before + j] = uint16_t(j * D_TOK);
+                        }
+                        n += total;
+                    }
+                    if (lane == 0) s_nactive = n;
+                }
+            } else if (!a.dense) {
 #pragma unroll 1
                 for (int e = tid; e < experts; e += nthreads) s_picked[e] = 0;
                 __syncthreads();
@@ -430,6 +535,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
             if (warp < nseg) {
                 const int walk = sb + warp;
                 const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
+                const int skip = EP ? int(s_skip[walk]) : 0;  // the expert's slots that earlier runs took
                 int count = 0, token = 0, pick = lane;  // slot base + lane = token * topk + pick
                 while (pick >= topk) pick -= topk, token++;
 #pragma unroll 1
@@ -437,15 +543,17 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     const bool hit = base + lane < slots && s_ids[base + lane] == e;
                     const unsigned ballot = __ballot_sync(0xffffffffu, hit);
                     if (hit) {
-                        const int at = warp * D_TOK + count + __popc(ballot & ((1u << lane) - 1u));
-                        s_slot[at] = uint16_t(base + lane);
-                        s_tok[at] = uint16_t(token);
+                        const int ord = count + __popc(ballot & ((1u << lane) - 1u)) - skip;
+                        if (ord >= 0 && ord < D_TOK) {
+                            s_slot[warp * D_TOK + ord] = uint16_t(base + lane);
+                            s_tok[warp * D_TOK + ord] = uint16_t(token);
+                        }
                     }
                     count += __popc(ballot);
                     pick += 32;
                     while (pick >= topk) pick -= topk, token++;
                 }
-                if (lane == 0) s_seg_count[warp] = count;
+                if (lane == 0) s_seg_count[warp] = min(D_TOK, max(0, count - skip));
             }
             if (sb == seg_first && p == 1) {
                 // The lists depend on the ids only: they were made while the other CTAs finished
@@ -494,7 +602,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     const int vec_per_row = P.cols / 16;
 #pragma unroll 1
                     for (int r = warp; r < rows; r += nwarps) {
-                        const uint4* src = reinterpret_cast<const uint4*>(a.xq + size_t(s_tok[entry_of_row(r)]) * P.cols);
+                        const uint4* src = reinterpret_cast<const uint4*>(xq_all + size_t(s_tok[entry_of_row(r)]) * P.cols);
                         uint8_t* dst = smem + L.x0 + r * P.x_stride;
 #pragma unroll 2
                         for (int v = lane; v < vec_per_row; v += 32) *reinterpret_cast<uint4*>(dst + v * 16) = __ldcg(src + v);
@@ -503,8 +611,8 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                         const size_t src = size_t(s_tok[entry_of_row(lane)]) * P.nbp;
 #pragma unroll 2
                         for (int b = warp; b < P.nb; b += nwarps) {
-                            xsT[b * D_TOK + lane] = __ldcg(a.xs + src + b);
-                            if (KIND == 2) xsumT[b * D_TOK + lane] = __ldcg(a.xsum + src + b);
+                            xsT[b * D_TOK + lane] = __ldcg(xs_all + src + b);
+                            if (KIND == 2) xsumT[b * D_TOK + lane] = __ldcg(xsum_all + src + b);
                         }
                     }
                 } else {
@@ -610,8 +718,13 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                                     }
                                 } else {
                                     const int r0 = u * F_ROWS + g;
-                                    if (r0 < hidden) a.out[slot * hidden + r0] = y0;
-                                    if (r0 + 8 < hidden) a.out[slot * hidden + r0 + 8] = y1;
+                                    float* dst = a.out + slot * hidden;
+                                    if (EP) {  // the row's place in its home rank's window, over NVLink
+                                        const size_t per_rank = size_t(t) * topk, home = slot / per_rank;
+                                        dst = reinterpret_cast<float*>(a.ep.base[home] + a.ep.off_out) + (slot - home * per_rank) * hidden;
+                                    }
+                                    if (r0 < hidden) dst[r0] = y0;
+                                    if (r0 + 8 < hidden) dst[r0 + 8] = y1;
                                 }
                             }
                         }
@@ -629,23 +742,34 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         // ---- every CTA's part of this phase is in global memory before anyone reads it
         __syncthreads();
         arrived = p + 1;
-        if (tid == 0) grid_arrive(a.sync + 1 + p);
+        if (EP && p == 1) {
+            if (tid < ranks)
+                arrive_on_peer(reinterpret_cast<uint32_t*>(a.ep.base[tid] + a.ep.off_flags) + DECODE_EP_FLAG_DOWN);
+        } else if (tid == 0) {
+            grid_arrive(a.sync + 1 + p);
+        }
     }
     if (!ok && tid == 0 && !s_abort) s_abort = 3;
 
     // ---- weighted combine + residual add: CTA i < t takes token i (src/model.rs:513-519, 681),
     // once every CTA's part of the down phase is in global memory.
     if (ok && bid < t) {
-        if (tid == 0 && !grid_wait(a.sync + 2, uint32_t(nctas), a.spin_limit)) s_abort = 2;
+        if (tid == 0) {
+            const bool came = EP ? peer_count_wait(flags + DECODE_EP_FLAG_DOWN, (epoch0 + 1u) * uint32_t(ranks * nctas),
+                                                   a.spin_limit)
+                                 : grid_wait(a.sync + 2, uint32_t(nctas), a.spin_limit);
+            if (!came) s_abort = EP ? 4 : 2;
+        }
         __syncthreads();
         ok = !s_abort;
         if (stamping) a.stamps[4] = wall_clock_ns();
     }
     if (ok && bid < t) {
         if (tid < topk) {
-            const uint32_t mine = s_ids[bid * topk + tid];
+            const uint32_t* my_ids = s_ids + (own + bid) * topk;
+            const uint32_t mine = my_ids[tid];
             int rank = 0;
-            for (int j = 0; j < topk; j++) rank += s_ids[bid * topk + j] < mine ? 1 : 0;
+            for (int j = 0; j < topk; j++) rank += my_ids[j] < mine ? 1 : 0;
             s_cpos[rank] = uint32_t(bid * topk + tid);
             s_cgate[rank] = __ldcg(a.gates + size_t(bid) * topk + tid);
         }
@@ -657,7 +781,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
 #pragma unroll 8
             for (int j = 0; j < topk; j++) {
                 const float gt = s_cgate[j];
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(a.out + size_t(s_cpos[j]) * hidden + c));
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(out_own + size_t(s_cpos[j]) * hidden + c));
                 proj.x = proj.x + gt * v.x;
                 proj.y = proj.y + gt * v.y;
                 proj.z = proj.z + gt * v.z;
@@ -674,13 +798,14 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         // has passed its waits on them by now (all arrived at the last one).
         if (tid == 0 && atomicAdd(a.sync + 3, 1u) == uint32_t(t) - 1) {
             a.sync[0] = a.sync[1] = a.sync[2] = a.sync[3] = 0;
+            if (EP) *a.ep.epoch = epoch0 + 1u;
             __threadfence();
         }
     }
     if (stamping) a.stamps[5] = wall_clock_ns();
     if (!ok) {
         if (tid == 0) {
-            atomicExch(a.status, s_abort == 3 ? ERR_COPY_WAIT_TIMEOUT : ERR_GRID_WAIT_TIMEOUT);
+            atomicExch(a.status, s_abort == 3 ? ERR_COPY_WAIT_TIMEOUT : s_abort == 4 ? ERR_PEER_WAIT_TIMEOUT : ERR_GRID_WAIT_TIMEOUT);
             // Announce the phases this CTA will not run, so that nobody waits for it in vain.
             for (int p = arrived; p < 2; p++) atomicAdd(a.sync + 1 + p, 1u);
         }
@@ -712,11 +837,14 @@ int decode_route_rows(const MoeDims& d, int t, int xcap, int nthreads) {
 // Warps per CTA, ring depth and staged rows: as many warps as possible while each still
 // gets a ring of at least three stages; then the deepest ring that fits.
 template <int KIND>
-bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap, int& route_rows) {
-    xcap = min(D_TOK, (t + 7) / 8 * 8);
+bool decode_config(const MoeDims& d, int t, int ids_slots, int& nwarps, int& stages, int& xcap, int& route_rows) {
+    // Rows staged at a time: an expert's tokens, up to D_TOK of them, out of all the tokens the expert
+    // phases see (every rank's when expert-parallel: ids_slots / topk).
+    xcap = min(D_TOK, (ids_slots / d.topk + 7) / 8 * 8);
     auto deepest = [&](int w, int rr) {
         for (int k = D_MAX_STAGES; k >= 2; k--)
-            if (size_t(DLayout<KIND>(w, k, xcap, rr, d.hidden, d.inter, d.experts, d.topk).total) <= D_SMEM_LIMIT) return k;
+            if (size_t(DLayout<KIND>(w, k, xcap, rr, d.hidden, d.inter, d.experts, d.topk, ids_slots).total) <= D_SMEM_LIMIT)
+                return k;
         return 0;
     };
     int best_w = 0, best_s = 0, best_r = 0;
@@ -737,45 +865,52 @@ bool decode_config(const MoeDims& d, int t, int& nwarps, int& stages, int& xcap,
 
 void init_kernels_decode() {
     const int lim = int(D_SMEM_LIMIT);
-    cudaFuncSetAttribute(moe_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
-    cudaFuncSetAttribute(moe_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(moe_decode_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(moe_decode_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(moe_decode_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+    cudaFuncSetAttribute(moe_decode_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
 }
 
-bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t) {
+// `ranks` > 1 (or an expert-parallel layer of one rank): t is the tokens per rank.
+bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t, int ranks) {
     if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK || d.hidden > D_NORM_HELD * 256)
         return false;
+    const int slots = (ranks > 0 ? ranks : 1) * t * d.topk;
+    if (slots > 65535 / 16 || d.experts > MAX_EXPERTS) return false;  // (slot lists are 16-bit; ids live in shared memory)
     int w, s, x, r;
-    return kind_gate_up == 1 ? decode_config<1>(d, t, w, s, x, r) : decode_config<2>(d, t, w, s, x, r);
+    return kind_gate_up == 1 ? decode_config<1>(d, t, slots, w, s, x, r) : decode_config<2>(d, t, slots, w, s, x, r);
 }
 
 int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
                         const float* norm_w, float eps, int t, float* y, const uint8_t* gate_up_tiled,
                         const uint8_t* down_tiled, Workspace& ws, int sms, uint32_t spin_limit,
-                        unsigned long long* stamps, cudaStream_t stream) {
+                        unsigned long long* stamps, cudaStream_t stream, const DecodeEp* ep, float* hidden_f_all) {
     DecodeArgs a{};
     a.stamps = stamps;
     a.router = router, a.bias = bias, a.x = x, a.norm_w = norm_w, a.eps = eps, a.y = y;
     a.t = t, a.hidden = d.hidden, a.experts = d.experts, a.topk = d.topk, a.inter = d.inter;
     a.logits = ws.logits, a.ids = ws.ids, a.gates = ws.gates, a.xq = ws.xq, a.xs = ws.xs, a.xsum = ws.xsum;
     a.gu_tiled = gate_up_tiled, a.dn_tiled = down_tiled;
-    a.hidden_f = ws.hidden_f, a.out = ws.out;
-    a.dense = dense_walk(d, t) ? 1 : 0;
+    a.hidden_f = ep ? hidden_f_all : ws.hidden_f, a.out = ws.out;
+    a.dense = !ep && dense_walk(d, t) ? 1 : 0;
+    if (ep) a.ep = *ep;
+    a.ids_slots = (ep ? ep->ranks : 1) * t * d.topk;
     a.sync = ws.grid_sync;
     a.spin_limit = spin_limit;
     a.status = ws.status;
     int nwarps = 0;
-    const bool fits = kind == 1 ? decode_config<1>(d, t, nwarps, a.stages, a.xcap, a.route_rows)
-                                : decode_config<2>(d, t, nwarps, a.stages, a.xcap, a.route_rows);
+    const bool fits = kind == 1 ? decode_config<1>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows)
+                                : decode_config<2>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows);
     if (!fits) return -1;
     // One CTA per SM, all resident at once (they wait for one another): never more CTAs than SMs.
     const int grid = sms;
-    if (kind == 1) {
-        const DLayout<1> L(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts, d.topk);
-        launch_overlapped(moe_decode_kernel<1>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
-    } else {
-        const DLayout<2> L(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts, d.topk);
-        launch_overlapped(moe_decode_kernel<2>, dim3(grid), dim3(nwarps * 32), size_t(L.total), stream, a);
-    }
+    const size_t smem = kind == 1 ? size_t(DLayout<1>(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts,
+                                                      d.topk, a.ids_slots).total)
+                                  : size_t(DLayout<2>(nwarps, a.stages, a.xcap, a.route_rows, d.hidden, d.inter, d.experts,
+                                                      d.topk, a.ids_slots).total);
+    auto kernel = kind == 1 ? (ep ? moe_decode_kernel<1, true> : moe_decode_kernel<1, false>)
+                            : (ep ? moe_decode_kernel<2, true> : moe_decode_kernel<2, false>);
+    launch_overlapped(kernel, dim3(grid), dim3(nwarps * 32), smem, stream, a);
     return 1;
 }
 

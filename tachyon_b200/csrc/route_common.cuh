@@ -104,7 +104,7 @@ __device__ __forceinline__ float route_dot_quad(const uint16_t* router, const ui
     if (!busy) {
     } else if (staged) {
         const uint8_t* ws = staged + size_t(e_staged >= 0 ? e_staged : e) * wstride + q * 8;
-#pragma unroll 4
+#pragma unroll 8
         for (int c = 0; c < hidden; c += 16) {
             const uint2 wv = *reinterpret_cast<const uint2*>(ws + 2 * c);
             const float4 xv = *reinterpret_cast<const float4*>(xr + c);

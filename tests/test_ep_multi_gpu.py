@@ -196,7 +196,7 @@ def test_fixed_size_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_path
                        start_method="spawn")
 
 
-@pytest.mark.parametrize("fmt,tokens", [("q8", 64), ("q4", 36), ("q8", 1024)])
+@pytest.mark.parametrize("fmt,tokens", [("q8", 64), ("q4", 36), ("q8", 1024), ("q8", 16), ("q4", 128)])
 def test_peer_memory_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_path, fmt, tokens):
     """Rows and expert outputs stored straight into the other ranks' windows over NVLink,
     announced with flags; no collective call inside the block."""
@@ -214,7 +214,7 @@ def test_peer_memory_exchange_equals_single_gpu_and_replays_from_a_graph(tmp_pat
 
 
 @pytest.mark.parametrize("mode", ["alltoallv", "fixed", "peer"])
-@pytest.mark.parametrize("fmt,tokens", [("q8", 40), ("q4", 37), ("q8", 300)])
+@pytest.mark.parametrize("fmt,tokens", [("q8", 40), ("q4", 37), ("q8", 300), ("q8", 24), ("q4", 32)])
 def test_one_rank_runs_every_exchange(tmp_path, fmt, tokens, mode):
     """A communicator of one rank on one GPU: the same kernels and buffers as with
     several ranks (the window is the rank's own), so the three exchanges are covered
