@@ -645,6 +645,21 @@ def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world,
         d.free()
     dist.barrier()
 
+    # ---- where a block's time goes on rank 0 (wall-clock stamps of CTA 0 inside the one-kernel block)
+    try:
+        ctx.profile_phases(True)
+        g2 = stack.capture()
+        dist.barrier()
+        for _ in range(3):
+            g2.launch()
+        out["phase_us_cta0"] = ctx.read_phases()
+        dist.barrier()
+        ctx.profile_phases(False)
+        g2.free()
+    except Exception as e:  # (a path without phase stamps: the four-kernel exchanges)
+        out["phase_us_cta0"] = str(e)
+    dist.barrier()
+
     if args.headline_only:
         return out
     # ---- prefill-size expert-parallel blocks: the 3b-a800m shape with int8 weights, 8192 tokens per

@@ -195,8 +195,10 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     __shared__ int s_nactive;
     __shared__ int s_seg_count[D_NSEG];
     __shared__ uint8_t s_picked[MAX_EXPERTS];
-    __shared__ uint16_t s_active[MAX_EXPERTS];  // walk index -> expert (sparse walk); EP: -> the run's expert
-    __shared__ uint16_t s_skip[EP ? MAX_EXPERTS : 1];   // EP: slots of that expert in earlier runs
+    constexpr int MAX_RUNS = EP ? MAX_EXPERTS + 4096 / 8 / 8 : MAX_EXPERTS;  // (experts + slots / shortest run)
+    __shared__ uint16_t s_active[MAX_RUNS];     // walk index -> expert (sparse walk); EP: -> the run's expert
+    __shared__ uint16_t s_skip[EP ? MAX_RUNS : 1];      // EP: slots of that expert in earlier runs
+    __shared__ int s_run_len;                           // EP: slots per run (32, 16 or 8)
     __shared__ uint32_t s_cnt[EP ? MAX_EXPERTS : 1];    // EP: slots per local expert
     __shared__ uint32_t s_rids[MAX_TOPK];               // the routed token's picks, on their way out
     __shared__ uint32_t s_cpos[MAX_TOPK];
@@ -346,6 +348,24 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
             streaming = true;
         }
         if (pass == 1) break;
+        if (EP && (long long)slots >= 4LL * experts) {
+            // Expert parallel, and every local expert will very probably be picked: which records a
+            // warp needs is only known after the router phase, but this rank's share of the layer is
+            // small, so all of it is asked into L2 now (every CTA a slice), and the copies into shared
+            // memory that follow the router phase find it there.
+            const Phase* Ps[2] = {&P0, &P1};
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const size_t bytes = size_t(a.ep.local) * Ps[q]->upe * Ps[q]->nchunks * R::BYTES;
+                const size_t piece = 4096, pieces = (bytes + piece - 1) / piece;
+                for (size_t i = size_t(bid) * nthreads + tid; i < pieces; i += size_t(nctas) * nthreads) {
+                    const size_t at = i * piece, n = min(piece, bytes - at) & ~size_t(15);
+                    if (n)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(Ps[q]->tiled + at), "r"(uint32_t(n))
+                                     : "memory");
+                }
+            }
+        }
         if (routing) {
             // Part 0 of the router matrix goes all the way into shared memory before the wait,
             // part 1 (if any) into registers.
@@ -462,12 +482,30 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     if (e < uint32_t(a.ep.local)) atomicAdd(&s_cnt[e], 1u);
                 }
                 __syncthreads();
-                if (warp == 0) {  // a lane per local expert, 32 at a time: the expert's runs after those before it
+                if (warp == 0) {
+                    // Runs as long as possible (fewer passes over an expert's weights) while there are
+                    // enough (run, unit) pairs to give every second warp of the grid one.
+                    int pairs[3] = {0, 0, 0};  // with runs of 32, 16, 8 slots
+#pragma unroll 1
+                    for (int e = lane; e < a.ep.local; e += 32) {
+                        const int c = int(s_cnt[e]);
+#pragma unroll
+                        for (int k = 0; k < 3; k++) pairs[k] += (c + (D_TOK >> k) - 1) / (D_TOK >> k);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 3; k++) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) pairs[k] += __shfl_xor_sync(0xffffffffu, pairs[k], o);
+                        pairs[k] *= P0.upe;
+                    }
+                    const int want = nctas * nwarps / 2;
+                    const int run_len = pairs[0] >= want ? D_TOK : pairs[1] >= want ? D_TOK / 2 : D_TOK / 4;
+                    // A lane per local expert, 32 at a time: the expert's runs after those before it.
                     int n = 0;
 #pragma unroll 1
                     for (int e0 = 0; e0 < a.ep.local; e0 += 32) {
                         const int e = e0 + lane;
-                        const int mine = e < a.ep.local ? int(s_cnt[e] + D_TOK - 1) / D_TOK : 0;
+                        const int mine = e < a.ep.local ? (int(s_cnt[e]) + run_len - 1) / run_len : 0;
                         int before = mine;
 #pragma unroll
                         for (int o = 1; o < 32; o <<= 1) {
@@ -476,13 +514,16 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                         }
                         const int total = __shfl_sync(0xffffffffu, before, 31);
                         before -= mine;
-                        for (int j = 0; j < mine; j++) {
+                        for (int j = 0; j < mine && n + before + j < MAX_RUNS; j++) {
                             s_active[n + before + j] = uint16_t(a.ep.first + e);
-                            s_skip[n + before + j] = uint16_t(j * D_TOK);
+                            s_skip[n + before + j] = uint16_t(j * run_len);
                         }
                         n += total;
                     }
-                    if (lane == 0) s_nactive = n;
+                    if (lane == 0) {
+                        s_nactive = min(n, MAX_RUNS);
+                        s_run_len = run_len;
+                    }
                 }
             } else if (!a.dense) {
 #pragma unroll 1
@@ -536,6 +577,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 const int walk = sb + warp;
                 const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
                 const int skip = EP ? int(s_skip[walk]) : 0;  // the expert's slots that earlier runs took
+                const int run_len = EP ? s_run_len : D_TOK;
                 int count = 0, token = 0, pick = lane;  // slot base + lane = token * topk + pick
                 while (pick >= topk) pick -= topk, token++;
 #pragma unroll 1
@@ -544,7 +586,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     const unsigned ballot = __ballot_sync(0xffffffffu, hit);
                     if (hit) {
                         const int ord = count + __popc(ballot & ((1u << lane) - 1u)) - skip;
-                        if (ord >= 0 && ord < D_TOK) {
+                        if (ord >= 0 && ord < run_len) {
                             s_slot[warp * D_TOK + ord] = uint16_t(base + lane);
                             s_tok[warp * D_TOK + ord] = uint16_t(token);
                         }
@@ -553,7 +595,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                     pick += 32;
                     while (pick >= topk) pick -= topk, token++;
                 }
-                if (lane == 0) s_seg_count[warp] = min(D_TOK, max(0, count - skip));
+                if (lane == 0) s_seg_count[warp] = min(run_len, max(0, count - skip));
             }
             if (sb == seg_first && p == 1) {
                 // The lists depend on the ids only: they were made while the other CTAs finished
