@@ -312,7 +312,7 @@ struct DecodeEp {
     int ranks = 0, me = 0, first = 0, local = 0;  // this rank; its first expert and how many it holds
     uint8_t* base[8] = {};                // every rank's window as mapped here
     size_t off_xq = 0, off_xs = 0, off_xsum = 0, off_ids = 0, off_out = 0, off_flags = 0;
-    uint32_t* epoch = nullptr;                    // blocks this rank has completed on this path
+    uint32_t* epoch = nullptr;                    // two words: blocks this rank has completed on this path, and their router-phase arrivals
     int mute = 0;                                 // testing: rows are sent but not announced
 };
 void init_kernels_decode();

@@ -219,6 +219,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     const float* out_own = EP ? reinterpret_cast<const float*>(window + a.ep.off_out) : a.out;
     const uint32_t* flags = EP ? reinterpret_cast<const uint32_t*>(window + a.ep.off_flags) : nullptr;
     uint32_t epoch0 = 0;  // EP: blocks completed before this one
+    uint32_t routed0 = 0; // EP: router-phase arrivals of those blocks (ranks x tokens each; the batch size may change)
     const DLayout<KIND> L(nwarps, STAGES, a.xcap, a.route_rows, hidden, inter, experts, topk, a.ids_slots);
     uint8_t* ring = smem + L.ring + size_t(warp) * STAGES * R::BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bars) + warp * D_MAX_STAGES;
@@ -457,8 +458,9 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
             }
         }
         if (EP) {
-            epoch0 = *a.ep.epoch;
-            if (tid == 0 && !peer_count_wait(flags + DECODE_EP_FLAG_ROUTE, (epoch0 + 1u) * uint32_t(ranks * t), a.spin_limit))
+            epoch0 = a.ep.epoch[0];
+            routed0 = a.ep.epoch[1];
+            if (tid == 0 && !peer_count_wait(flags + DECODE_EP_FLAG_ROUTE, routed0 + uint32_t(ranks * t), a.spin_limit))
                 s_abort = 4;
         } else if (tid == 0 && !grid_wait(a.sync + 0, uint32_t(t), a.spin_limit)) {
             s_abort = 1;
@@ -840,7 +842,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         // has passed its waits on them by now (all arrived at the last one).
         if (tid == 0 && atomicAdd(a.sync + 3, 1u) == uint32_t(t) - 1) {
             a.sync[0] = a.sync[1] = a.sync[2] = a.sync[3] = 0;
-            if (EP) *a.ep.epoch = epoch0 + 1u;
+            if (EP) a.ep.epoch[0] = epoch0 + 1u, a.ep.epoch[1] = routed0 + uint32_t(ranks * t);
             __threadfence();
         }
     }
@@ -913,9 +915,12 @@ void init_kernels_decode() {
     cudaFuncSetAttribute(moe_decode_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
 }
 
-// `ranks` > 1 (or an expert-parallel layer of one rank): t is the tokens per rank.
+// `ranks` > 1 (or an expert-parallel layer of one rank): t is the tokens per rank. A token's router
+// phase and combine take a CTA each; the expert-parallel form walks an expert's tokens in runs, so
+// with one rank (nothing crosses a link) it takes up to 128 tokens.
 bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int t, int ranks) {
-    if (t < 1 || t > D_TOK || kind_gate_up != kind_down || d.topk > MAX_TOPK || d.hidden > D_NORM_HELD * 256)
+    const int most = ranks == 1 ? 4 * D_TOK : D_TOK;
+    if (t < 1 || t > most || kind_gate_up != kind_down || d.topk > MAX_TOPK || d.hidden > D_NORM_HELD * 256)
         return false;
     const int slots = (ranks > 0 ? ranks : 1) * t * d.topk;
     if (slots > 65535 / 16 || d.experts > MAX_EXPERTS) return false;  // (slot lists are 16-bit; ids live in shared memory)

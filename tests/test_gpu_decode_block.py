@@ -83,6 +83,53 @@ def test_one_kernel_block_meets_the_oracle_bars(oracle, ctx, fmt, t):
     check_block(oracle, ctx, shape, lw, x, arith="fast")
 
 
+@pytest.mark.parametrize("shape", SHAPES[:4] + SHAPES[5:], ids=lambda s: s.name)
+def test_one_kernel_block_from_33_to_128_tokens(oracle, ctx, shape):
+    """Above 32 tokens the one-kernel block runs in its expert-parallel form with the GPU as the
+    only rank (an expert's tokens in runs of up to 32, rows and outputs through a local window):
+    same bits as the four-kernel path, whatever the batch before it was."""
+    lw = layer_weights(oracle, shape, 17)
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    ctx.set_prefill_threshold(1 << 30)  # the comparison path stays on the bandwidth kernels
+    layer = make_layer(ctx, lw, shape.topk, 128)
+    bias = synth.zipf_router_bias(17, shape.experts)
+    try:
+        for t in [33, 64, 5, 100, 128, 47]:
+            for b in (None, bias):
+                layer.set_router_bias(b)
+                x = workloads.hidden_states(shape, t, seed=140 + t)
+                y0 = workloads.hidden_states(shape, t, seed=180 + t)
+                one, four = both_paths(ctx, layer, x, y0)
+                assert np.array_equal(one, four), (shape.name, t, b is not None, np.abs(one - four).max())
+    finally:
+        ctx.set_prefill_threshold(32)
+        layer.free()
+
+
+def test_64_token_block_meets_the_oracle_bars_and_replays_from_a_graph(oracle, ctx):
+    shape = MoeShape("1b", 1024, 32, 8, 512, fmt="q8")
+    lw = layer_weights(oracle, shape, 0)
+    x = workloads.hidden_states(shape, 64, seed=3)
+    ctx.set_decode_block(True)
+    check_block(oracle, ctx, shape, lw, x, arith="fast")
+    layer = make_layer(ctx, lw, shape.topk, 64)
+    y0 = workloads.hidden_states(shape, 64, seed=4)
+    xd, yd = ctx.to_device(x), ctx.to_device(y0)
+    layer.forward(xd, yd)
+    ctx.sync()
+    want = yd.get()
+    ctx.capture_begin()
+    layer.forward(xd, yd)
+    g = ctx.capture_end()
+    for _ in range(3):
+        ctx.upload(yd.ptr, y0)
+        g.launch()
+        ctx.sync()
+        assert np.array_equal(yd.get(), want)
+    g.free()
+    layer.free()
+
+
 def test_blocks_chained_in_a_graph_with_the_norm_fused(oracle, ctx):
     """Six blocks back to back on the residual stream, captured and replayed: each kernel
     starts under the previous one's tail, and the grid-wide counters must be back at
