@@ -111,6 +111,12 @@ tc_moe_layer *tc_moe_layer_create(tc_ctx *ctx, int hidden, int experts, int expe
                                   int inter, const tc_matrix *router, const tc_matrix *gate_up,
                                   const tc_matrix *down, int max_tokens);
 void tc_moe_layer_free(tc_moe_layer *layer);
+/* A layer keeps its own re-tiled copies of the expert matrices; the matrices as uploaded are
+ * only read again by TC_ARITH_CPU_LANES. After this call the layer no longer refers to them, so
+ * the caller may tc_matrix_free gate_up and down (a third of the layer's expert memory); blocks
+ * in TC_ARITH_CPU_LANES are then refused for this layer. (The Metal backend keeps one copy,
+ * src/gpu/mod.rs:222-251; no counterpart there.) */
+int tc_moe_layer_detach_experts(tc_moe_layer *layer);
 /* A bias added to every token's router logits before top-k (NULL clears it).
  * Tachyon's router has none (src/model.rs:473); the routing-skew workload
  * adds one on both the CPU and the GPU side. bias_host: f32[experts]. */

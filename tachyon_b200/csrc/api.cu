@@ -60,7 +60,7 @@ struct tc_matrix {
 struct tc_moe_layer {
     tc_ctx* ctx;
     tc::MoeDims dims;
-    const tc_matrix *router, *gate_up, *down;
+    const tc_matrix *router, *gate_up, *down;  // (gate_up / down: null once the experts are detached)
     float* bias = nullptr;
     int max_tokens;
     int last_t = 0;
@@ -71,6 +71,7 @@ struct tc_moe_layer {
     std::vector<void*> pw_allocs;
     bool ep = false;                   // expert-parallel layer: gate_up/down hold this rank's experts only
     tc::EpLayerBuffers epb;
+    tc::MatrixDev gu, dn;              // the expert matrices as uploaded (pointers null once detached)
 };
 
 struct tc_graph {
@@ -711,6 +712,7 @@ tc_moe_layer* layer_create(tc_ctx* ctx, int hidden, int experts, int k, int inte
     if (!tc::fast_path_fits(d, gate_up->dev, down->dev)) return bad("hidden or intermediate size too large for the staged-token buffers");
     tc_moe_layer* l = new tc_moe_layer{ctx, d, router, gate_up, down, nullptr, max_tokens, 0};
     l->ep = ep;
+    l->gu = gate_up->dev, l->dn = down->dev;
     tc::MoeDims dl = d;  // the shape of the matrices held here
     dl.experts = local;
     if (ep && ctx->ep.uni.on && !tc::ep_uniform_reserve(ctx->ep, d, max_tokens)) {
@@ -778,6 +780,16 @@ void tc_moe_layer_free(tc_moe_layer* layer) {
     delete layer;
 }
 
+int tc_moe_layer_detach_experts(tc_moe_layer* layer) {
+    tc_ctx* ctx = layer->ctx;
+    // Anything still reading the uploaded copies (a layer being created, an exact-order block) is done first.
+    if (!cuda_ok(ctx, cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize")) return -1;
+    layer->gu.data = layer->gu.scales = nullptr;
+    layer->dn.data = layer->dn.scales = nullptr;
+    layer->gate_up = layer->down = nullptr;
+    return 0;
+}
+
 int tc_moe_set_router_bias(tc_moe_layer* layer, const float* bias_host) {
     tc_ctx* ctx = layer->ctx;
     if (!bias_host) {
@@ -801,6 +813,8 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     tc_ctx* ctx = layer->ctx;
     if (t <= 0) return fail(ctx, "empty batch");
     if (t > layer->max_tokens) return fail(ctx, "%d tokens, layer was created for %d", t, layer->max_tokens);
+    if (ctx->arith == tc::ARITH_CPU_LANES && !layer->gu.data)
+        return fail(ctx, "TC_ARITH_CPU_LANES reads the expert matrices as uploaded, and this layer's were detached");
     const tc::MoeDims& d = layer->dims;
     tc::Workspace& ws = ctx->ws;
     cudaStream_t s = ctx->stream;
@@ -808,7 +822,7 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     if (layer->ep && tc::ep_peer_applies(ctx->ep, d, t)) {
         const char* why = tc::ep_forward_peer(ctx->ep, layer->epb, d,
                                               static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
-                                              layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                              layer->gu, layer->gate_up_tiled, layer->dn,
                                               layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n,
                                               ctx->decode_block && ctx->arith == tc::ARITH_FAST, ctx->phase_stamps);
         ctx->launches += n;
@@ -820,7 +834,7 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     if (layer->ep && tc::ep_uniform_applies(ctx->ep, d, t)) {
         const char* why = tc::ep_forward_uniform(ctx->ep, layer->epb, d,
                                                  static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
-                                                 layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                                 layer->gu, layer->gate_up_tiled, layer->dn,
                                                  layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n);
         ctx->launches += n;
         layer->last_t = t;
@@ -831,7 +845,7 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     if (layer->ep) {
         if (ctx->capturing) return fail(ctx, "the expert-parallel block reads exchange sizes on the host: it cannot be captured");
         const char* why = tc::ep_forward(ctx->ep, layer->epb, d, static_cast<const uint16_t*>(layer->router->dev.data),
-                                         layer->bias, layer->gate_up->dev, layer->gate_up_tiled, layer->down->dev,
+                                         layer->bias, layer->gu, layer->gate_up_tiled, layer->dn,
                                          layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n,
                                          ctx->arith == tc::ARITH_CPU_LANES ? nullptr : &layer->pw, &ctx->pre,
                                          ctx->prefill_min_avg);
@@ -844,10 +858,10 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     const bool lanes = ctx->arith == tc::ARITH_CPU_LANES;
     layer->dispatch_stale = false;
     if (!lanes && ctx->decode_block &&
-        tc::decode_block_applies(d, layer->gate_up->dev.kind, layer->down->dev.kind, t)) {
+        tc::decode_block_applies(d, layer->gu.kind, layer->dn.kind, t)) {
         // Decode-size batch: the whole block is one kernel (no dispatch is built).
         n += staged(ctx, 7, [&] {
-            return tc::launch_decode_block(d, layer->gate_up->dev.kind,
+            return tc::launch_decode_block(d, layer->gu.kind,
                                            static_cast<const uint16_t*>(layer->router->dev.data), layer->bias, x,
                                            norm_w, eps, t, y, layer->gate_up_tiled, layer->down_tiled, ws, ctx->sms,
                                            ctx->grid_spin_limit, ctx->phase_stamps, s);
@@ -864,7 +878,7 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     if (!lanes && !prefill && ctx->decode_block && t > 32 && t <= ctx->decode_block_tokens && t <= ctx->sms &&
         ctx->self_window &&
         self_window_layout(d, t, &self) <= ctx->self_bytes &&
-        tc::decode_block_applies(d, layer->gate_up->dev.kind, layer->down->dev.kind, t, 1)) {
+        tc::decode_block_applies(d, layer->gu.kind, layer->dn.kind, t, 1)) {
         // Up to 128 tokens, below the tensor-core kernels' threshold: still one kernel, in its
         // expert-parallel form with this GPU as the only rank (an expert's tokens in runs of up to
         // 32; rows and outputs through the local window). Measured at the 1b-a400m shape, 24 blocks:
@@ -873,7 +887,7 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
         self.base[0] = ctx->self_window;
         self.epoch = ctx->self_epoch + 4;
         n += staged(ctx, 7, [&] {
-            return tc::launch_decode_block(d, layer->gate_up->dev.kind,
+            return tc::launch_decode_block(d, layer->gu.kind,
                                            static_cast<const uint16_t*>(layer->router->dev.data), layer->bias, x,
                                            norm_w, eps, t, y, layer->gate_up_tiled, layer->down_tiled, ws, ctx->sms,
                                            ctx->grid_spin_limit, ctx->phase_stamps, s, &self, ws.hidden_f);
@@ -891,11 +905,11 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     if (prefill) {
         const int slots = t * d.topk;
         n += staged(ctx, 2, [&] {
-            return tc::launch_prefill(d, true, layer->gate_up->dev.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
+            return tc::launch_prefill(d, true, layer->gu.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
                                       ws.hidden_f, nullptr, s);
         });
         n += staged(ctx, 4, [&] {
-            return tc::launch_prefill(d, false, layer->down->dev.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
+            return tc::launch_prefill(d, false, layer->dn.kind == TC_Q4, layer->pw, ctx->pre, ws, slots,
                                       ws.out, nullptr, s);
         });
         n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
@@ -905,13 +919,13 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
         return 0;
     }
     n += staged(ctx, 2, [&] {
-        return lanes ? tc::launch_gate_up_exact(d, layer->gate_up->dev, t, ws, ctx->sms, s)
-                     : tc::launch_gate_up_fast(d, layer->gate_up->dev, layer->gate_up_tiled, t, ws, ctx->sms, s);
+        return lanes ? tc::launch_gate_up_exact(d, layer->gu, t, ws, ctx->sms, s)
+                     : tc::launch_gate_up_fast(d, layer->gu, layer->gate_up_tiled, t, ws, ctx->sms, s);
     });
     if (lanes) n += staged(ctx, 3, [&] { return tc::launch_quant_hidden(d, t, ws, s); });
     n += staged(ctx, 4, [&] {
-        return lanes ? tc::launch_down_exact(d, layer->down->dev, t, ws, ctx->sms, s)
-                     : tc::launch_down_fast(d, layer->down->dev, layer->down_tiled, t, ws, ctx->sms, s);
+        return lanes ? tc::launch_down_exact(d, layer->dn, t, ws, ctx->sms, s)
+                     : tc::launch_down_fast(d, layer->dn, layer->down_tiled, t, ws, ctx->sms, s);
     });
     n += staged(ctx, 5, [&] { return tc::launch_combine(d, t, ws, y, s); });
     ctx->launches += n;

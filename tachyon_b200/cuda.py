@@ -49,6 +49,7 @@ SYMBOLS = {
     "tc_matrix_free": (None, [_vp]),
     "tc_moe_layer_create": (_vp, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i]),
     "tc_moe_layer_free": (None, [_vp]),
+    "tc_moe_layer_detach_experts": (_i, [_vp]),
     "tc_moe_set_router_bias": (_i, [_vp, _vp]),
     "tc_moe_forward": (_i, [_vp, _vp, _i, _vp]),
     "tc_moe_block": (_i, [_vp, _vp, _f, _i, _vp]),
@@ -429,6 +430,13 @@ class MoeLayer:
             self.gate_up.handle, self.down.handle, max_tokens)
         if not self.handle:
             raise TachyonCudaError(f"tc_moe_layer_create: {ctx.last_error()}")
+
+    def detach_experts(self):
+        """Drops the expert matrices as uploaded (the layer computes from its own re-tiled copies;
+        only ``ARITH_CPU_LANES`` reads the uploaded ones again, and is refused from here on)."""
+        self.ctx._check(self.ctx.lib.tc_moe_layer_detach_experts(self.handle), "tc_moe_layer_detach_experts")
+        for m in (self.gate_up, self.down):
+            m.free()
 
     def set_router_bias(self, bias):
         b = None if bias is None else np.ascontiguousarray(bias, np.float32)

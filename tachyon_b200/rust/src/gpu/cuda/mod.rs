@@ -102,6 +102,7 @@ extern "C" {
         max_tokens: c_int,
     ) -> *mut TcMoeLayer;
     fn tc_moe_layer_free(layer: *mut TcMoeLayer);
+    fn tc_moe_layer_detach_experts(layer: *mut TcMoeLayer) -> c_int;
     fn tc_moe_forward(layer: *mut TcMoeLayer, x: *const f32, t: c_int, y: *mut f32) -> c_int;
     fn tc_moe_block(
         layer: *mut TcMoeLayer,
@@ -272,8 +273,8 @@ struct MoeLayer {
     handle: *mut TcMoeLayer,
     mlp_norm: DeviceBuf,
     _router: DeviceMatrix,
-    _gate_up: DeviceMatrix,
-    _down: DeviceMatrix,
+    gate_up: Option<DeviceMatrix>,
+    down: Option<DeviceMatrix>,
 }
 
 impl Drop for MoeLayer {
@@ -352,8 +353,8 @@ impl CudaMoe {
             handle,
             mlp_norm: DeviceBuf::from_slice(ctx, &layer.mlp_norm)?,
             _router: router,
-            _gate_up: gate_up,
-            _down: down,
+            gate_up: Some(gate_up),
+            down: Some(down),
         })
     }
 
@@ -392,6 +393,21 @@ impl CudaMoe {
             // As the Metal backend does for a failed command buffer (src/gpu/mod.rs:1049-1053).
             panic!("CUDA MoE block failed: {}", self.ctx.last_error());
         }
+    }
+
+    /// Frees the expert matrices as uploaded (a third of the experts' device
+    /// memory): the layers compute from their own re-tiled copies. Afterwards
+    /// `exact_cpu_order(true)` blocks are refused by the library.
+    pub fn release_uploaded_experts(&mut self) -> Result<()> {
+        for layer in self.layers.iter_mut().flatten() {
+            // SAFETY: the layer is live; the matrices are dropped only after it lets go of them.
+            if unsafe { tc_moe_layer_detach_experts(layer.handle) } != 0 {
+                bail!("CUDA backend: {}", self.ctx.last_error());
+            }
+            layer.gate_up = None;
+            layer.down = None;
+        }
+        Ok(())
     }
 
     /// Switches the expert products to the CPU path's own eight-lane order

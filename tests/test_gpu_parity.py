@@ -335,3 +335,45 @@ def test_launch_overlap_does_not_change_results(oracle, ctx):
     assert np.array_equal(outs[0], outs[2]) and np.array_equal(outs[0], outs[4])
     assert np.array_equal(outs[1], outs[3]) and np.array_equal(outs[1], outs[5])
     assert np.all(np.isfinite(outs[1]))
+
+
+@pytest.mark.parametrize("fmt", ["q8", "q4"])
+def test_layer_without_the_uploaded_expert_matrices(oracle, ctx, fmt):
+    """The layer computes from its re-tiled copies: once detached, the matrices as uploaded
+    can be freed, every default-arithmetic path still gives the same bits, and the
+    CPU-lane mode (the one reader of the uploaded copies) is refused."""
+    from tachyon_b200 import cuda
+
+    shape = MoeShape("detach", 512, 16, 4, 128, fmt=fmt)
+    lw = layer_weights(oracle, shape, 6)
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    layer = make_layer(ctx, lw, shape.topk, 600)
+    sizes = [5, 40, 600]  # one kernel, one kernel through the window, tensor-core kernels
+    xs = [workloads.hidden_states(shape, t, seed=50 + t) for t in sizes]
+
+    def run():
+        outs = []
+        for x in xs:
+            xd, yd = ctx.to_device(x), ctx.to_device(np.zeros_like(x))
+            layer.forward(xd, yd)
+            ctx.sync()
+            outs.append(yd.get())
+            xd.free()
+            yd.free()
+        return outs
+
+    before = run()
+    layer.detach_experts()
+    assert layer.gate_up.handle is None and layer.down.handle is None
+    scratch = ctx.to_device(np.full(1 << 22, 7, np.uint8))  # something else may now live where they were
+    after = run()
+    for a, b in zip(before, after):
+        assert np.array_equal(a, b)
+    ctx.set_arithmetic(ctx.ARITH_CPU_LANES)
+    xd, yd = ctx.to_device(xs[0]), ctx.to_device(np.zeros_like(xs[0]))
+    with pytest.raises(cuda.TachyonCudaError, match="detached"):
+        layer.forward(xd, yd)
+    ctx.set_arithmetic(ctx.ARITH_FAST)
+    for d in (xd, yd, scratch):
+        d.free()
+    layer.free()
