@@ -663,34 +663,55 @@ def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world,
     if args.headline_only:
         return out
     # ---- prefill-size expert-parallel blocks: the 3b-a800m shape with int8 weights, 8192 tokens per
-    # step over all ranks, 2 layers, variable-size all-to-all dispatch and combine.
+    # step over all ranks, 2 layers. Twice: rows and expert outputs stored into the other ranks'
+    # windows over NVLink by the kernels that produce them (a second context whose windows are sized
+    # for these blocks), and the variable-size all-to-all over NCCL.
     s4 = workloads.GRANITE_3B_Q8
     tokens = 8192 // world
     first, count = ep.shard_range(s4.experts, rank, world)
-    l4 = []
-    for l in range(2):
-        lw = workloads.layer_weights_local(s4, first, count, seed=args.seed, layer=l, threads=host_threads)
-        l4.append(ep.EpMoeLayer(ctx, lw.router, lw.gate_up, lw.down, s4.experts, s4.topk, tokens))
-    st4 = Stack(ctx, s4, l4, tokens, seed=args.seed + rank)
-    dist.barrier()
-    for _ in range(3):
-        st4.enqueue()
-    ctx.sync()
+    lws4 = [workloads.layer_weights_local(s4, first, count, seed=args.seed, layer=l, threads=host_threads)
+            for l in range(2)]
     k = 10
-    regs = []
-    for r in timed_regions(ctx, st4.enqueue, k, 3, barrier=dist.barrier):
-        tmax = torch.tensor([r], dtype=torch.float64)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        regs.append(float(tmax.item()))
-    ms4 = float(np.median(regs)) / k
+
+    def time_config4(c):
+        l4 = [ep.EpMoeLayer(c, lw.router, lw.gate_up, lw.down, s4.experts, s4.topk, tokens) for lw in lws4]
+        st4 = Stack(c, s4, l4, tokens, seed=args.seed + rank)
+        dist.barrier()
+        for _ in range(3):
+            st4.enqueue()
+        c.sync()
+        regs = []
+        for r in timed_regions(c, st4.enqueue, k, 3, barrier=dist.barrier):
+            tmax = torch.tensor([r], dtype=torch.float64)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            regs.append(float(tmax.item()))
+        st4.free()
+        for layer in l4:
+            layer.free()
+        dist.barrier()
+        return float(np.median(regs)) / k
+
+    def fresh_context(peer):
+        c = cuda.Context(ctx.device)
+        box = [ep.unique_id(c) if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        ep.init(c, box[0], rank, world, uniform_batch=peer)
+        if peer:
+            ep.enable_peer_exchange(c, s4.hidden, s4.topk, tokens)
+        return c
+
+    c_nccl = fresh_context(False)
+    ms4_nccl = time_config4(c_nccl)
+    c_nccl.close()
+    c_peer = fresh_context(True)
+    ms4 = time_config4(c_peer)
+    c_peer.close()
     c4 = {"workload": "granite-3b-a800m shape, int8 weights, 40 experts sharded, 8192 tokens per step over all ranks, "
-                      "2 MoE blocks, NCCL all-to-all-v dispatch and combine",
+                      "2 MoE blocks; rows and expert outputs stored into the other ranks' windows over NVLink "
+                      "(tcgen05 expert kernels on the local experts)",
           "tokens_per_rank": tokens, "ms_per_step": ms4, "ms_per_block": ms4 / 2,
-          "tokens_per_s": 8192 / (ms4 * 1e-3), "steps_per_region": k}
-    st4.free()
-    for layer in l4:
-        layer.free()
-    dist.barrier()
+          "tokens_per_s": 8192 / (ms4 * 1e-3), "steps_per_region": k,
+          "nccl_all_to_all_v": {"ms_per_step": ms4_nccl, "tokens_per_s": 8192 / (ms4_nccl * 1e-3)}}
     if rank == 0:
         # The same two blocks on one GPU, for the ratio.
         lws = [workloads.layer_weights(s4, seed=args.seed, layer=l, threads=host_threads) for l in range(2)]

@@ -824,14 +824,16 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
                                               static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
                                               layer->gu, layer->gate_up_tiled, layer->dn,
                                               layer->down_tiled, x, norm_w, eps, t, y, ws, ctx->sms, s, &n,
-                                              ctx->decode_block && ctx->arith == tc::ARITH_FAST, ctx->phase_stamps);
+                                              ctx->decode_block && ctx->arith == tc::ARITH_FAST, ctx->phase_stamps,
+                                              ctx->arith == tc::ARITH_CPU_LANES ? nullptr : &layer->pw, &ctx->pre,
+                                              ctx->prefill_min_avg);
         ctx->launches += n;
         layer->last_t = t;
         if (why) return fail(ctx, "expert-parallel block: %s", why);
         if (!ctx->capturing && !cuda_ok(ctx, cudaGetLastError(), "MoE launch")) return -1;
         return 0;
     }
-    if (layer->ep && tc::ep_uniform_applies(ctx->ep, d, t)) {
+    if (layer->ep && tc::ep_uniform_applies(ctx->ep, d, t) && ctx->ep.uni.big) {
         const char* why = tc::ep_forward_uniform(ctx->ep, layer->epb, d,
                                                  static_cast<const uint16_t*>(layer->router->dev.data), layer->bias,
                                                  layer->gu, layer->gate_up_tiled, layer->dn,

@@ -280,8 +280,11 @@ int prefill_max_token_tiles(int slots, int experts);
 int prefill_token_tile();  // tokens per tile
 void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, int8_t* wt, float* wd, float* wc,
                           cudaStream_t stream);
+// peer_out (down only): null, or every rank's window for expert outputs; a row whose number in
+// out_rows' numbering is p then goes to rank p / peer_rows, row p % peer_rows.
 int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights& w, const PrefillScratch& s,
-                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream);
+                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream,
+                   float* const* peer_out = nullptr, int peer_ranks = 0, uint32_t peer_rows = 0);
 
 // One 128 x n x 32 int8 tcgen05 MMA (n = 64 or 128) through TMEM: a self-check of the encodings.
 int launch_umma_selftest(const int8_t* a_tile, const int8_t* b_tile, int n, int* d_out, int* status,

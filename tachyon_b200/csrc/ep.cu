@@ -253,7 +253,7 @@ __global__ void iota_kernel(uint32_t* out, size_t n) {
 bool ep_uniform_reserve(EpState& st, const MoeDims& d, int max_tokens) {
     EpUniform& u = st.uni;
     const int G = max_tokens * st.size;
-    if (size_t(G) * d.topk * d.hidden * 4 > UNIFORM_MAX_BYTES || G > 16384) return true;  // not for this size
+    if (G > 16384) return true;  // not for this size
     if (u.tokens >= G && u.hidden >= d.hidden && u.experts >= d.experts && u.topk >= d.topk && u.inter >= d.inter)
         return true;
     cudaDeviceSynchronize();
@@ -274,7 +274,9 @@ bool ep_uniform_reserve(EpState& st, const MoeDims& d, int max_tokens) {
                     get(u.ids, slots) && get(u.counts, size_t(E) + 1) && get(u.offsets, size_t(E) + 2) &&
                     get(u.perm, slots) && get(u.pos, slots) && get(u.slot_token, slots) &&
                     get(u.active, size_t(E) + 2) && get(u.block_hist, size_t((T + 255) / 256) * E) &&
-                    get(u.hidden_f, slots * I) && get(u.big, slots * H) && get(u.identity, slots) &&
+                    get(u.hidden_f, slots * I) && get(u.identity, slots) &&
+                    // (the reduce-scatter buffer of the exchange over NCCL; the peer windows do without it)
+                    (slots * H * 4 > UNIFORM_MAX_BYTES ? (u.big = nullptr, true) : get(u.big, slots * H)) &&
                     get(u.runs.expert, size_t(E) + slots / 16 + 2) && get(u.runs.count, size_t(E) + slots / 16 + 2) &&
                     get(u.runs.offset, size_t(E) + slots / 16 + 2) && get(u.runs.n, size_t(2));
     if (!ok) {
@@ -376,11 +378,58 @@ __global__ void __launch_bounds__(1024) peer_scatter_signal_kernel(const PeerPla
     peer_scatter_signal(a, &s_epoch);
 }
 
+// The same for batches too large for one CTA to copy: every CTA copies a share of this rank's rows,
+// scales and ids into every window; peer_rows_sent_kernel, next in the stream, announces them.
+__global__ void __launch_bounds__(256) peer_scatter_rows_kernel(const PeerPlan a) {
+    const size_t xq_vec = size_t(a.t) * a.hidden / 16, xs_vec = size_t(a.t) * a.nbp / 4;
+    const size_t ids_n = size_t(a.t) * a.topk;
+    const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, n = size_t(gridDim.x) * blockDim.x;
+    for (int r = 0; r < a.ranks; r++) {
+        uint8_t* w = a.base[r];
+        uint4* dq = reinterpret_cast<uint4*>(w + a.off_xq + size_t(a.me) * a.t * a.hidden);
+        const uint4* sq = reinterpret_cast<const uint4*>(a.xq);
+        for (size_t i = tid; i < xq_vec; i += n) dq[i] = sq[i];
+        uint4* ds = reinterpret_cast<uint4*>(w + a.off_xs + size_t(a.me) * a.t * a.nbp * 4);
+        const uint4* ss = reinterpret_cast<const uint4*>(a.xs);
+        for (size_t i = tid; i < xs_vec; i += n) ds[i] = ss[i];
+        uint32_t* di = reinterpret_cast<uint32_t*>(w + a.off_ids) + size_t(a.me) * ids_n;
+        for (size_t i = tid; i < ids_n; i += n) di[i] = a.ids[i];
+    }
+}
+
+__global__ void peer_rows_sent_kernel(const PeerPlan a) {
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t e = a.epoch[a.flag_set] + 1;
+        a.epoch[a.flag_set] = e;
+        for (int r = 0; r < a.ranks && !a.mute; r++) {
+            uint32_t* flag = reinterpret_cast<uint32_t*>(a.base[r] + a.off_flags) + a.flag_set * 8 + a.me;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(e) : "memory");
+        }
+    }
+}
+
 // The signal alone (t = 0 rows): after the down kernel, whose stores into the other
 // ranks' windows are complete when this kernel starts.
 __global__ void peer_wait_kernel(const PeerWait pw) {
     if (int(threadIdx.x) < pw.ranks) peer_wait(pw, threadIdx.x);
     __syncwarp();
+}
+
+struct PeerFlags {
+    uint32_t* p[8];
+};
+
+// After a kernel that stored expert outputs into the other ranks' windows (complete when this
+// one starts): this rank's next counter value, release-stored into every rank's flag.
+__global__ void peer_announce_kernel(uint32_t* epoch, PeerFlags flags, int ranks) {
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t e = *epoch + 1;
+        *epoch = e;
+        for (int r = 0; r < ranks; r++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[r]), "r"(e) : "memory");
+    }
 }
 
 const char* ep_barrier(EpState& st, cudaStream_t stream) {
@@ -453,7 +502,8 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
                             const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,
                             const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                             const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
-                            cudaStream_t stream, int* launches, bool one_kernel, unsigned long long* stamps) {
+                            cudaStream_t stream, int* launches, bool one_kernel, unsigned long long* stamps,
+                            const PrefillWeights* pw, const PrefillScratch* ps, int prefill_min_avg) {
     EpUniform& u = st.uni;
     EpPeer& p = st.peer;
     const int R = st.size, G = R * t;
@@ -490,9 +540,15 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     Workspace rw = ws;
     rw.route_scatter = plan;  // batches of up to one CTA's worth of tokens: sent by the router's last CTA
     *launches += launch_route(d, router, bias, x, norm_w, eps, t, rw, stream);
-    if (t > 256) {  // larger ones: the router ran its own multi-CTA dispatch; send with a kernel
-        peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
-        *launches += 1;
+    if (t > 256) {  // larger ones: sent by kernels of their own
+        if (t > 1024) {
+            peer_scatter_rows_kernel<<<2 * sms, 256, 0, stream>>>(plan);
+            peer_rows_sent_kernel<<<1, 32, 0, stream>>>(plan);
+            *launches += 2;
+        } else {
+            peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
+            *launches += 1;
+        }
     }
 
     Workspace gw = ws;  // the view over every rank's tokens, gathered in this rank's window
@@ -531,11 +587,25 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     lw.out = nullptr;
     float* outs[8] = {};
     for (int r = 0; r < R; r++) outs[r] = reinterpret_cast<float*>(p.base[r] + p.off_out);
-    *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
     uint32_t* flags2[8] = {};
     for (int r = 0; r < R; r++) flags2[r] = reinterpret_cast<uint32_t*>(p.base[r] + p.off_flags) + 8 + st.rank;
-    *launches += launch_down_fast_rows(ld, down, down_tiled, lw, u.perm, sms, stream, outs, R,
-                                       uint32_t(t) * d.topk, flags2, p.epoch + 1, p.epoch + 2);
+    if (pw && ps && pw->gu_t && (long long)G * d.topk >= (long long)prefill_min_avg * d.experts) {
+        // Prefill-size groups: the tcgen05 kernels on this rank's tiles. How many slots this rank
+        // gets is only known on the device, so the grids are sized for all of them; the down
+        // kernel's epilogue stores each row into its home rank's window, then one thread announces.
+        const int slots = G * d.topk;
+        *launches += launch_prefill(ld, true, gate_up.kind == 2, *pw, *ps, lw, slots, u.hidden_f, nullptr, stream);
+        *launches += launch_prefill(ld, false, down.kind == 2, *pw, *ps, lw, slots, nullptr, u.perm, stream, outs, R,
+                                    uint32_t(t) * d.topk);
+        PeerFlags pf{};
+        for (int r = 0; r < R; r++) pf.p[r] = flags2[r];
+        peer_announce_kernel<<<1, 32, 0, stream>>>(p.epoch + 1, pf, R);
+        *launches += 1;
+    } else {
+        *launches += launch_gate_up_fast(ld, gate_up, gate_up_tiled, G, lw, sms, stream);
+        *launches += launch_down_fast_rows(ld, down, down_tiled, lw, u.perm, sms, stream, outs, R,
+                                           uint32_t(t) * d.topk, flags2, p.epoch + 1, p.epoch + 2);
+    }
 
     Workspace cw = ws;
     cw.out = reinterpret_cast<float*>(p.window + p.off_out);

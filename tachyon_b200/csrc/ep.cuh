@@ -90,7 +90,8 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
                             const MatrixDev& down, const uint8_t* down_tiled, const float* x,
                             const float* norm_w, float eps, int t, float* y, Workspace& ws, int sms,
                             cudaStream_t stream, int* launches, bool one_kernel = false,
-                            unsigned long long* stamps = nullptr);
+                            unsigned long long* stamps = nullptr, const PrefillWeights* pw = nullptr,
+                            const PrefillScratch* ps = nullptr, int prefill_min_avg = 32);
 const char* ep_barrier(EpState& st, cudaStream_t stream);
 const char* ep_forward(EpState& st, EpLayerBuffers& b, const MoeDims& d, const uint16_t* router,
                        const float* bias, const MatrixDev& gate_up, const uint8_t* gate_up_tiled,

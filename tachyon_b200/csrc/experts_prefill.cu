@@ -61,6 +61,11 @@ struct PrefillArgs {
     int nb, row_tiles, rows_per_expert, out_cols;
     float* out;
     const uint32_t* out_rows;
+    // Expert parallel (down only): row p of out_rows' numbering belongs to rank p / peer_rows and goes
+    // straight into that rank's window, at row p % peer_rows.
+    float* peer_out[MAX_PEERS];
+    uint32_t peer_rows;
+    int peer_ranks;
     int* status;
 };
 
@@ -333,7 +338,13 @@ __global__ void __launch_bounds__(P_THREADS, 1) expert_prefill_kernel(const Pref
                     if (n < tile_n && r < a.out_cols) {
                         size_t p = p0 + n;
                         if (a.out_rows) p = a.out_rows[p];
-                        a.out[p * a.out_cols + r] = y;
+                        float* dst = a.out;
+                        if (a.peer_ranks) {
+                            const uint32_t home = uint32_t(p) / a.peer_rows;
+                            p -= size_t(home) * a.peer_rows;
+                            dst = a.peer_out[home];
+                        }
+                        dst[p * a.out_cols + r] = y;
                     }
                 }
             }
@@ -552,7 +563,8 @@ void tile_prefill_weights(const MoeDims& d, const MatrixDev& m, bool gate_up, in
 // activations come from: 8-bit rows through row_of_slot (gate_up), or f32 rows
 // in slot order to quantize (down).
 int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights& w, const PrefillScratch& s,
-                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream) {
+                   const Workspace& ws, int slots, float* out, const uint32_t* out_rows, cudaStream_t stream,
+                   float* const* peer_out, int peer_ranks, uint32_t peer_rows) {
     const int cols = gate_up ? d.hidden : d.inter;
     const int nb = cols / QK, nbp = (nb + 7) / 8 * 8;
     const int max_tiles = prefill_max_token_tiles(slots, d.experts);
@@ -589,6 +601,11 @@ int launch_prefill(const MoeDims& d, bool gate_up, bool q4, const PrefillWeights
     a.out_cols = gate_up ? d.inter : d.hidden;
     a.out = out;
     a.out_rows = out_rows;
+    if (peer_out && !gate_up) {
+        for (int r = 0; r < peer_ranks && r < MAX_PEERS; r++) a.peer_out[r] = peer_out[r];
+        a.peer_ranks = peer_ranks;
+        a.peer_rows = peer_rows;
+    }
     a.status = ws.status;
     const dim3 grid(a.row_tiles, max_tiles);
     const size_t smem = prefill_smem(nb, q4);

@@ -364,7 +364,8 @@ int launch_route(const MoeDims& d, const uint16_t* router, const float* bias, co
         launch_overlapped(route_tile_kernel, dim3(std::min(tiles, per_sm * sms)), dim3(ROUTE_THREADS), tsmem, stream, a);
     }
     int launched = 1;
-    if (!a.fuse_dispatch) launched += launch_dispatch(d, t, ws, stream);
+    // (Expert parallel over peer windows: the dispatch runs later, over every rank's tokens.)
+    if (!a.fuse_dispatch && ws.route_scatter.ranks == 0) launched += launch_dispatch(d, t, ws, stream);
     return launched;
 }
 
