@@ -251,8 +251,22 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     derive(P0), derive(P1);
     auto share = [&](Phase& P, unsigned walk_experts) {  // (bid + 1) * total stays far below 2^32
         const unsigned total = walk_experts * unsigned(P.upe);
-        P.lo = int(unsigned(bid) * total / unsigned(nctas));
-        P.hi = int(unsigned(bid + 1) * total / unsigned(nctas));
+        if (EP && walk_experts > 0 && walk_experts <= unsigned(nctas)) {
+            // Runs: every CTA stays inside one run (a CTA whose units span two runs lists and stages
+            // tokens twice, and the whole grid then waits for it): the run's units are cut into as
+            // many equal parts as there are whole CTAs per run; the CTAs left over stay idle.
+            const unsigned per_run = unsigned(nctas) / walk_experts, run = unsigned(bid) / per_run,
+                           part = unsigned(bid) % per_run;
+            if (run < walk_experts) {
+                P.lo = int(run * unsigned(P.upe) + part * unsigned(P.upe) / per_run);
+                P.hi = int(run * unsigned(P.upe) + (part + 1) * unsigned(P.upe) / per_run);
+            } else {
+                P.lo = P.hi = 0;
+            }
+        } else {
+            P.lo = int(unsigned(bid) * total / unsigned(nctas));
+            P.hi = int(unsigned(bid + 1) * total / unsigned(nctas));
+        }
         P.first = P.lo + warp;
         P.n = P.first < P.hi ? (P.hi - P.first + nwarps - 1) / nwarps : 0;
     };
@@ -486,23 +500,29 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
                 }
                 __syncthreads();
                 if (warp == 0) {
-                    // Runs as long as possible (fewer passes over an expert's weights) while there are
-                    // enough (run, unit) pairs to give every second warp of the grid one.
-                    int pairs[3] = {0, 0, 0};  // with runs of 32, 16, 8 slots
+                    // Run length 32, 16 or 8: the one with the least work on the busiest warp. A run's
+                    // units go to nctas / runs CTAs (share()); a warp takes its CTA's units in waves
+                    // of nwarps, and a unit costs about 3 + (tiles of 8 tokens) in units of a tile.
+                    int runs[3] = {0, 0, 0}, most = 0;
 #pragma unroll 1
                     for (int e = lane; e < a.ep.local; e += 32) {
                         const int c = int(s_cnt[e]);
+                        most = max(most, c);
 #pragma unroll
-                        for (int k = 0; k < 3; k++) pairs[k] += (c + (D_TOK >> k) - 1) / (D_TOK >> k);
+                        for (int k = 0; k < 3; k++) runs[k] += (c + (D_TOK >> k) - 1) / (D_TOK >> k);
                     }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) most = max(most, __shfl_xor_sync(0xffffffffu, most, o));
+                    int run_len = D_TOK, best = 0x7fffffff;
 #pragma unroll
                     for (int k = 0; k < 3; k++) {
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) pairs[k] += __shfl_xor_sync(0xffffffffu, pairs[k], o);
-                        pairs[k] *= P0.upe;
+                        for (int o = 16; o > 0; o >>= 1) runs[k] += __shfl_xor_sync(0xffffffffu, runs[k], o);
+                        const int len = D_TOK >> k, r = max(1, runs[k]);
+                        const int per_cta = r <= nctas ? (P0.upe + nctas / r - 1) / (nctas / r) : (r * P0.upe + nctas - 1) / nctas;
+                        const int cost = (per_cta + nwarps - 1) / nwarps * (3 + (min(len, most) + 7) / 8);
+                        if (cost < best) best = cost, run_len = len;
                     }
-                    const int want = nctas * nwarps / 2;
-                    const int run_len = pairs[0] >= want ? D_TOK : pairs[1] >= want ? D_TOK / 2 : D_TOK / 4;
                     // A lane per local expert, 32 at a time: the expert's runs after those before it.
                     int n = 0;
 #pragma unroll 1
@@ -882,7 +902,8 @@ int decode_route_rows(const MoeDims& d, int t, int xcap, int nthreads) {
 // Warps per CTA, ring depth and staged rows: as many warps as possible while each still
 // gets a ring of at least three stages; then the deepest ring that fits.
 template <int KIND>
-bool decode_config(const MoeDims& d, int t, int ids_slots, int& nwarps, int& stages, int& xcap, int& route_rows) {
+bool decode_config(const MoeDims& d, int t, int ids_slots, int& nwarps, int& stages, int& xcap, int& route_rows,
+                   bool runs = false) {
     // Rows staged at a time: an expert's tokens, up to D_TOK of them, out of all the tokens the expert
     // phases see (every rank's when expert-parallel: ids_slots / topk).
     xcap = min(D_TOK, (ids_slots / d.topk + 7) / 8 * 8);
@@ -896,7 +917,9 @@ bool decode_config(const MoeDims& d, int t, int ids_slots, int& nwarps, int& sta
     for (int w = D_MAX_WARPS; w >= 8; w -= 2) {
         const int rr = decode_route_rows<KIND>(d, t, xcap, w * 32);
         const int s = deepest(w, rr);
-        if (s >= 3) {
+        // (Walking runs, nothing is copied before the router phase and a run's units are cut into
+        // parts of 16 or fewer: more warps matter more there than a third stage.)
+        if (s >= (runs ? 2 : 3)) {
             nwarps = w, stages = s, route_rows = rr;
             return true;
         }
@@ -926,7 +949,8 @@ bool decode_block_applies(const MoeDims& d, int kind_gate_up, int kind_down, int
     const int slots = (ranks > 0 ? ranks : 1) * t * d.topk;
     if (slots > 65535 / 16 || d.experts > MAX_EXPERTS) return false;  // (slot lists are 16-bit; ids live in shared memory)
     int w, s, x, r;
-    return kind_gate_up == 1 ? decode_config<1>(d, t, slots, w, s, x, r) : decode_config<2>(d, t, slots, w, s, x, r);
+    return kind_gate_up == 1 ? decode_config<1>(d, t, slots, w, s, x, r, ranks > 0)
+                             : decode_config<2>(d, t, slots, w, s, x, r, ranks > 0);
 }
 
 int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, const float* bias, const float* x,
@@ -951,8 +975,8 @@ int launch_decode_block(const MoeDims& d, int kind, const uint16_t* router, cons
     a.spin_limit = spin_limit;
     a.status = ws.status;
     int nwarps = 0;
-    const bool fits = kind == 1 ? decode_config<1>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows)
-                                : decode_config<2>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows);
+    const bool fits = kind == 1 ? decode_config<1>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows, ep != nullptr)
+                                : decode_config<2>(d, t, a.ids_slots, nwarps, a.stages, a.xcap, a.route_rows, ep != nullptr);
     if (!fits) return -1;
     // One CTA per SM, all resident at once (they wait for one another): never more CTAs than SMs.
     const int grid = sms;
