@@ -65,8 +65,7 @@ int tc_set_prefill_threshold(tc_ctx *ctx, int avg_tokens_per_expert);
 /* Decode-size blocks (8-bit or 4-bit experts, default arithmetic) run as ONE kernel whose
  * CTAs meet at grid-wide counters (no counterpart in the reference, whose Metal backend
  * encodes a dispatch per step: src/gpu/mod.rs:651-702): up to 32 tokens directly, and up to
- * 128 tokens, while the batch is below the tensor-core kernels' threshold, with an expert's
- * tokens walked in runs of up to 32. on = 1: the default; on = 0: the four-kernel path;
+ * 128 tokens with an expert's tokens walked in runs of up to 32. on = 1: the default; on = 0: the four-kernel path;
  * on > 1: one kernel up to that many tokens (at most 128). All give the same values. */
 int tc_set_decode_block(tc_ctx *ctx, int on);
 

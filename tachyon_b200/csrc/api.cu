@@ -877,14 +877,14 @@ int moe_enqueue(tc_moe_layer* layer, const float* x, const float* norm_w, float 
     const bool prefill = !lanes && layer->pw.gu_t &&
                          (long long)t * d.topk >= (long long)ctx->prefill_min_avg * d.experts;
     tc::DecodeEp self;
-    if (!lanes && !prefill && ctx->decode_block && t > 32 && t <= ctx->decode_block_tokens && t <= ctx->sms &&
+    if (!lanes && ctx->decode_block && t > 32 && t <= ctx->decode_block_tokens && t <= ctx->sms &&
         ctx->self_window &&
         self_window_layout(d, t, &self) <= ctx->self_bytes &&
         tc::decode_block_applies(d, layer->gu.kind, layer->dn.kind, t, 1)) {
-        // Up to 128 tokens, below the tensor-core kernels' threshold: still one kernel, in its
-        // expert-parallel form with this GPU as the only rank (an expert's tokens in runs of up to
-        // 32; rows and outputs through the local window). Measured at the 1b-a400m shape, 24 blocks:
-        // 1.54 ms against 1.82 at 64 tokens, 1.76 against 2.17 at 96; at 128 the tcgen05 kernels win.
+        // Up to 128 tokens: still one kernel, in its expert-parallel form with this GPU as the only
+        // rank (an expert's tokens in runs of up to 32; rows and outputs through the local window).
+        // Measured at the 1b-a400m shape, 24 blocks: 1.14 ms against 1.82 at 64 tokens, 1.24 against
+        // 2.17 at 96, 1.56 at 127 against 1.82 for the tcgen05 kernels at 128.
         self.ranks = 1, self.me = 0, self.first = 0, self.local = d.experts;
         self.base[0] = ctx->self_window;
         self.epoch = ctx->self_epoch + 4;

@@ -201,6 +201,7 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
     __shared__ uint16_t s_skip[EP ? MAX_RUNS : 1];      // EP: slots of that expert in earlier runs
     __shared__ int s_run_len;                           // EP: slots per run (32, 16 or 8)
     __shared__ uint32_t s_cnt[EP ? MAX_EXPERTS : 1];    // EP: slots per local expert
+    __shared__ int s_part[EP ? D_NSEG * D_MAX_WARPS : 1];  // EP: a segment's hits per warp's slice of the ids
     __shared__ uint32_t s_rids[MAX_TOPK];               // the routed token's picks, on their way out
     __shared__ uint32_t s_cpos[MAX_TOPK];
     __shared__ float s_cgate[MAX_TOPK];
@@ -604,8 +605,53 @@ __global__ void __launch_bounds__(D_MAX_WARPS * 32, 1) moe_decode_kernel(const D
         for (int sb = seg_first; sb <= seg_last && ok; sb += D_NSEG) {
             const int nseg = min(D_NSEG, seg_last - sb + 1);
             if (sb != seg_first) __syncthreads();  // the previous lists and staged rows are no longer read
-            // ---- the slots that named each expert of this batch of segments, ascending: a warp per segment
-            if (warp < nseg) {
+            // ---- the slots that named each expert of this batch of segments, ascending
+            if (EP && slots > 8 * 32) {
+                // Many slots (every rank's): all warps scan, each a slice of the ids. First the hits per
+                // slice and segment, then, from the counts of the slices before it, where each hit goes.
+                const int slice = ((slots + nwarps - 1) / nwarps + 31) & ~31;
+                const int lo = min(slots, warp * slice), hi = min(slots, lo + slice);
+                const int run_len = s_run_len;
+#pragma unroll 1
+                for (int k = 0; k < nseg; k++) {
+                    const uint32_t e = uint32_t(s_active[sb + k]);
+                    int count = 0;
+#pragma unroll 1
+                    for (int base = lo; base < hi; base += 32)
+                        count += __popc(__ballot_sync(0xffffffffu, base + lane < hi && s_ids[base + lane] == e));
+                    if (lane == 0) s_part[k * D_MAX_WARPS + warp] = count;
+                }
+                __syncthreads();
+#pragma unroll 1
+                for (int k = 0; k < nseg; k++) {
+                    const uint32_t e = uint32_t(s_active[sb + k]);
+                    const int skip = int(s_skip[sb + k]);
+                    const int part = lane < nwarps ? s_part[k * D_MAX_WARPS + lane] : 0;
+                    int before = lane < warp ? part : 0, total = part;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) {
+                        before += __shfl_xor_sync(0xffffffffu, before, o);
+                        total += __shfl_xor_sync(0xffffffffu, total, o);
+                    }
+                    int count = before, token = (lo + lane) / topk, pick = (lo + lane) - token * topk;
+#pragma unroll 1
+                    for (int base = lo; base < hi; base += 32) {
+                        const bool hit = base + lane < hi && s_ids[base + lane] == e;
+                        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+                        if (hit) {
+                            const int ord = count + __popc(ballot & ((1u << lane) - 1u)) - skip;
+                            if (ord >= 0 && ord < run_len) {
+                                s_slot[k * D_TOK + ord] = uint16_t(base + lane);
+                                s_tok[k * D_TOK + ord] = uint16_t(token);
+                            }
+                        }
+                        count += __popc(ballot);
+                        pick += 32;
+                        while (pick >= topk) pick -= topk, token++;
+                    }
+                    if (tid == 0) s_seg_count[k] = min(run_len, max(0, total - skip));
+                }
+            } else if (warp < nseg) {
                 const int walk = sb + warp;
                 const uint32_t e = uint32_t(a.dense ? walk : int(s_active[walk]));
                 const int skip = EP ? int(s_skip[walk]) : 0;  // the expert's slots that earlier runs took
