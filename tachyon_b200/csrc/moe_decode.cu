@@ -1,4 +1,5 @@
-// The whole MoE block of a decode-size batch (up to 32 tokens) as ONE kernel:
+// The whole MoE block of a decode-size batch (up to 32 tokens; up to 128 in the run-walking
+// form described further down) as ONE kernel:
 // [RMSNorm +] router + top-k + gates + row quantization, gate_up + SwiGLU, down,
 // weighted combine + residual add, by persistent CTAs (one per SM) that meet at
 // three grid-wide arrival counters instead of at kernel boundaries.
@@ -20,6 +21,22 @@
 //  - The router phase runs on CTAs 0..t-1 (a token each); the others only stream.
 //    The combine runs on the same CTAs; the rest have exited by then, which lets the
 //    next block's kernel start streaming its weights under this block's combine.
+//
+// Partition. The 16-row units of the walked experts are cut over the CTAs so that a CTA stays
+// inside one expert wherever that costs no extra wave of units per warp (an expert's units over
+// nctas / experts CTAs, the CTAs left over idle): a CTA whose units span two experts lists and
+// stages two experts' tokens, and every phase waits for its slowest CTA. A CTA's units go round
+// its warps; 16 warps per CTA where each still gets a ring of two stages.
+//
+// Run-walking form (template parameter EP): experts sharded over the GPUs of one node, or one
+// GPU with 33 to 128 tokens. An expert's slots are cut into runs of up to 32, 16 or 8 tokens
+// (the length with the least work on the busiest warp), the (run, unit) pairs are what CTAs and
+// warps share out, every CTA stays inside one run, and the run's slot list is built by all
+// warps of the CTA. Rows, ids and expert outputs travel through per-rank windows (peer memory
+// over NVLink, or local memory when there is one rank) and the rendezvous are system-scope
+// counters in those windows that only grow. Which records a warp needs depends on the routing
+// there, so nothing is copied into shared memory before the router phase; the rank's share of
+// the layer is asked into L2 instead.
 //
 // No token -> expert permutation is built: with at most 32 tokens every CTA keeps
 // the batch's expert ids in shared memory and lists, per expert of its range, the
