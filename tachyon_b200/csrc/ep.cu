@@ -360,26 +360,22 @@ const char* ep_forward_uniform(EpState& st, EpLayerBuffers& b, const MoeDims& d,
 // The exchange over peer memory. Same plan as the fixed-size exchange, with the
 // two collectives replaced by stores into the destination rank's window:
 //   1. route (own tokens);
-//   2. peer_scatter_signal_kernel: this rank's 8-bit rows, scales and expert ids into
-//      every rank's window (NVLink stores), then a release-store of this rank's block
-//      counter into every rank's flag word;
-//   3. peer_wait_kernel: all ranks' rows have arrived here;
+//   2. this rank's 8-bit rows, scales and expert ids into every rank's window (NVLink
+//      stores), then a release-store of this rank's block counter into every rank's flag
+//      word: by the router kernel's last CTA up to 256 tokens, else by
+//      peer_scatter_rows_kernel + peer_rows_sent_kernel;
+//   3. the dispatch kernel waits (bounded) until all ranks' rows have arrived here;
 //   4. dispatch over all ranks' tokens, gate_up + SwiGLU, down on this rank's experts;
 //      the down kernel stores each output row into its home rank's window at
-//      (token, pick);
-//   5. peer_signal_kernel; the combine kernel waits for every rank's signal and reads
-//      the rows in place.
+//      (token, pick) and announces it (its last CTA, or peer_announce_kernel after the
+//      tcgen05 kernels);
+//   5. the combine kernel waits for every rank's announcement and reads the rows in place.
 // Every wait is bounded (peer_wait) and leaves an error status instead of hanging.
 // Ordering across blocks needs no second buffer: a rank can only reach step 2 of block
 // n+1 after its combine of block n, which waited for every rank's step 5 of block n,
 // i.e. for every reader of the rows of block n.
-__global__ void __launch_bounds__(1024) peer_scatter_signal_kernel(const PeerPlan a) {
-    __shared__ uint32_t s_epoch;
-    peer_scatter_signal(a, &s_epoch);
-}
-
-// The same for batches too large for one CTA to copy: every CTA copies a share of this rank's rows,
-// scales and ids into every window; peer_rows_sent_kernel, next in the stream, announces them.
+// Step 2 for batches of more than 256 tokens: every CTA copies a share of this rank's rows, scales
+// and ids into every window; peer_rows_sent_kernel, next in the stream, announces them.
 __global__ void __launch_bounds__(256) peer_scatter_rows_kernel(const PeerPlan a) {
     const size_t xq_vec = size_t(a.t) * a.hidden / 16, xs_vec = size_t(a.t) * a.nbp / 4;
     const size_t ids_n = size_t(a.t) * a.topk;
@@ -540,15 +536,10 @@ const char* ep_forward_peer(EpState& st, EpLayerBuffers& b, const MoeDims& d, co
     Workspace rw = ws;
     rw.route_scatter = plan;  // batches of up to one CTA's worth of tokens: sent by the router's last CTA
     *launches += launch_route(d, router, bias, x, norm_w, eps, t, rw, stream);
-    if (t > 256) {  // larger ones: sent by kernels of their own
-        if (t > 1024) {
-            peer_scatter_rows_kernel<<<2 * sms, 256, 0, stream>>>(plan);
-            peer_rows_sent_kernel<<<1, 32, 0, stream>>>(plan);
-            *launches += 2;
-        } else {
-            peer_scatter_signal_kernel<<<1, 1024, 0, stream>>>(plan);
-            *launches += 1;
-        }
+    if (t > 256) {  // larger ones: sent by kernels of their own (many CTAs copy, one thread announces)
+        peer_scatter_rows_kernel<<<2 * sms, 256, 0, stream>>>(plan);
+        peer_rows_sent_kernel<<<1, 32, 0, stream>>>(plan);
+        *launches += 2;
     }
 
     Workspace gw = ws;  // the view over every rank's tokens, gathered in this rank's window
