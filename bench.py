@@ -27,6 +27,7 @@ cores, same config and metric.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -405,7 +406,7 @@ def main():
             os.environ["NCCL_DEBUG"] = "WARN"  # (its banner would land on stdout beside the JSON line)
         import torch.distributed as dist  # plumbing only: barrier and max over ranks
 
-        dist.init_process_group("gloo")
+        dist.init_process_group("gloo", timeout=datetime.timedelta(minutes=5))
         dist.barrier()
     ctx = cuda.Context(local_rank)
     if args.no_overlap:
@@ -662,6 +663,16 @@ def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world,
 
     if args.headline_only:
         return out
+    # (Measured last and on its own: whatever goes wrong in it must not cost the line its headline.)
+    try:
+        out["config4"] = config4_section(args, ctx, cuda, dist, ep, torch, rank, world, host_threads)
+    except Exception as e:  # noqa: BLE001
+        out["config4"] = {"error": f"{type(e).__name__}: {e}"}
+    return out
+
+
+def config4_section(args, ctx, cuda, dist, ep, torch, rank, world, host_threads):
+    """Prefill-size expert-parallel blocks (the 3b-a800m shape in int8, 8192 tokens per step over all ranks)."""
     # ---- prefill-size expert-parallel blocks: the 3b-a800m shape with int8 weights, 8192 tokens per
     # step over all ranks, 2 layers. Twice: rows and expert outputs stored into the other ranks'
     # windows over NVLink by the kernels that produce them (a second context whose windows are sized
@@ -727,8 +738,7 @@ def multi_gpu_sections(args, ctx, cuda, dist, shape, layers, stack, rank, world,
         for layer in full:
             layer.free()
     dist.barrier()
-    out["config4"] = c4
-    return out
+    return c4
 
 
 if __name__ == "__main__":
