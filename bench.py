@@ -571,24 +571,41 @@ def main():
     graph.free()
 
     if not args.headline_only:
+        # (Each section on its own: whatever goes wrong in one must not cost the line its headline.)
         t0 = time.time()
-        peak = ctx.int8_peak(50.0)
-        peak["vs_2x_measured_bf16"] = peak["pops"] / (2.0 * peak_bf16 / 1e3)
-        line["int8_peak"] = peak
-        line["decode_sweep"] = [decode_point(ctx, shape, layers, b, 100.0, 3, peak_hbm) for b in sweep_batches]
-        # One block at 4096 tokens (4 sequences x 1024): the 1b shape in int8, the 3b shape in 4 bits.
-        pre = {"1b-a400m-q8": block_point(ctx, cuda, shape, weights_host[0], 4096, None, peak["pops"], 60.0, 3)}
-        s3 = workloads.GRANITE_3B
-        pre["3b-a800m-q4"] = block_point(ctx, cuda, s3, q4_layer(s3, args.seed, host_threads), 4096, None,
-                                         peak["pops"], 60.0, 3)
-        line["prefill"] = pre
-        # The routing-skew shape: hidden 2048, 64 experts, intermediate 1024, Zipf(1.2) router bias.
-        sk = workloads.SKEW
-        lw = workloads.layer_weights(sk, seed=args.seed, threads=host_threads)
-        bias = synth.zipf_router_bias(args.seed, sk.experts)
-        line["skew"] = {"shape": "hidden 2048, 64 experts, top-8, intermediate 1024, int8, Zipf(1.2) router bias",
-                        "points": [block_point(ctx, cuda, sk, lw, t, bias, peak["pops"], 40.0, 3)
-                                   for t in (256, 4096)]}
+        peak = {"pops": None}
+
+        def section(name, fn):
+            try:
+                line[name] = fn()
+            except Exception as e:  # noqa: BLE001
+                line[name] = {"error": f"{type(e).__name__}: {e}"}
+
+        def int8_peak():
+            peak.update(ctx.int8_peak(50.0))
+            peak["vs_2x_measured_bf16"] = peak["pops"] / (2.0 * peak_bf16 / 1e3)
+            return dict(peak)
+
+        def prefill():
+            # One block at 4096 tokens (4 sequences x 1024): the 1b shape in int8, the 3b shape in 4 bits.
+            pre = {"1b-a400m-q8": block_point(ctx, cuda, shape, weights_host[0], 4096, None, peak["pops"], 60.0, 3)}
+            s3 = workloads.GRANITE_3B
+            pre["3b-a800m-q4"] = block_point(ctx, cuda, s3, q4_layer(s3, args.seed, host_threads), 4096, None,
+                                             peak["pops"], 60.0, 3)
+            return pre
+
+        def skew():
+            # The routing-skew shape: hidden 2048, 64 experts, intermediate 1024, Zipf(1.2) router bias.
+            sk = workloads.SKEW
+            lw = workloads.layer_weights(sk, seed=args.seed, threads=host_threads)
+            bias = synth.zipf_router_bias(args.seed, sk.experts)
+            return {"shape": "hidden 2048, 64 experts, top-8, intermediate 1024, int8, Zipf(1.2) router bias",
+                    "points": [block_point(ctx, cuda, sk, lw, t, bias, peak["pops"], 40.0, 3) for t in (256, 4096)]}
+
+        section("int8_peak", int8_peak)
+        section("decode_sweep", lambda: [decode_point(ctx, shape, layers, b, 100.0, 3, peak_hbm) for b in sweep_batches])
+        section("prefill", prefill)
+        section("skew", skew)
         line["setup_s"]["sections"] = time.time() - t0
 
     if not args.no_cpu_baseline:
