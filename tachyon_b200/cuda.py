@@ -161,7 +161,7 @@ class Context:
         self._check(self.lib.tc_set_launch_overlap(self.handle, int(on)), "tc_set_launch_overlap")
 
     def set_decode_block(self, on: bool):
-        """Decode-size blocks (up to 32 tokens) as one kernel (default on) or as four."""
+        """Decode-size blocks (up to 128 tokens) as one kernel (default on) or as four."""
         self._check(self.lib.tc_set_decode_block(self.handle, int(on)), "tc_set_decode_block")
 
     def profile_phases(self, on: bool):
@@ -210,6 +210,10 @@ class Context:
     def copy(self, dst: "DeviceArray", src: "DeviceArray"):
         assert dst.nbytes == src.nbytes
         self._check(self.lib.tc_copy(self.handle, dst.ptr, src.ptr, src.nbytes), "tc_copy")
+
+    def copy_bytes(self, dst: int, src: int, nbytes: int):
+        """Device to device on the context's stream (can be captured)."""
+        self._check(self.lib.tc_copy(self.handle, dst, src, nbytes), "tc_copy")
 
     def pinned(self, shape, dtype=np.float32) -> np.ndarray:
         """A numpy array over page-locked host memory (kept alive by the context)."""
