@@ -204,10 +204,11 @@ def reference_arm(args, shape, world):
     weights_host, _ = build_weights(shape, args.layers, args.seed, threads)
     tokens = args.batch * world
     x0 = np.concatenate([workloads.hidden_states(shape, args.batch, seed=args.seed + r) for r in range(world)])
-    r = run_cpu(shape, weights_host, x0, min(args.steps, 200), max(1, min(args.warmup, 5)), budget_s=120.0)
+    warm = max(1, min(args.warmup, 5))
+    r = run_cpu(shape, weights_host, x0, min(args.steps, 200), warm, budget_s=120.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
-        "steps": r["steps"], "warmup": 1, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+        "steps": r["steps"], "warmup": warm, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": config_dict(args, shape, world),
         "cpu_baseline": {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["threads"], "kind": "port",
